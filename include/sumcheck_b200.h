@@ -1,0 +1,174 @@
+/*
+ * sumcheck_b200.h -- C ABI of libsumcheck_b200.so: the sumcheck prover rounds on a B200.
+ *
+ * The reference (Exacta, Common Lisp) has no foreign-function interface; its operator for this
+ * path is the Lisp function
+ *
+ *   (exacta.sumcheck:prove tr n statement tables &key eq constants label block-weights degree)
+ *                                                             src/sumcheck.lisp:512-571
+ *
+ * The functions below are what a Lisp PROVE binds (through sb-alien) to run its rounds on the
+ * device: each one names the reference code it stands in for.  Part 1 is the device layer (the
+ * transcript and the statement compiler stay with the caller, as in the reference).  Part 2 is a
+ * host layer in C++ behind the same ABI, for callers without a Lisp: the transcript, the
+ * statement compiler and PROVE itself, with the reference's argument meaning.
+ *
+ * Conventions.  Every function returns 0 or a negative SC_E* code and never throws or aborts.
+ * Field values cross this boundary as canonical u32 residues in [0, p), p = 2^31 - 2^24 + 1; an
+ * extension element is D consecutive u32 in the reference's tower order (src/field.lisp:8-11).
+ * Input values >= p are reduced, as COERCE-EXT does (src/field.lisp:115-117).  A context belongs
+ * to one device and one host thread at a time; calls are synchronous unless stated.  The library
+ * installs no signal handler and calls nothing back.
+ */
+#ifndef SUMCHECK_B200_H
+#define SUMCHECK_B200_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define SC_OK 0
+#define SC_EINVAL (-1)      /* bad argument (the reference signals INVALID-PARAMETER, src/conditions.lisp:94-122) */
+#define SC_ECUDA (-2)       /* a CUDA call failed; sc_last_error() has the text */
+#define SC_ENOMEM (-3)      /* device or host memory exhausted, or over the context's memory budget */
+#define SC_EUNSUPPORTED (-4)/* a shape no kernel is instantiated for (degree, table count, extension degree) */
+#define SC_ESTATE (-5)      /* calls out of order (round before begin, challenge before round ...) */
+#define SC_ECOMM (-6)       /* the collective layer failed or timed out */
+#define SC_ESTATEMENT (-7)  /* malformed statement, or a variable that is neither a table nor a constant */
+
+#define SC_MAX_TABLES 8
+#define SC_MAX_TERMS 16
+#define SC_MAX_FACTORS 8
+#define SC_MAX_POINTS 4
+
+typedef struct sc_ctx sc_ctx;
+
+/* ------------------------------------------------------------------ part 1: the device layer */
+
+/* A prover context on CUDA device DEVICE (an ordinal of this process).  It owns every device
+   buffer it makes: tables, folded tables, weights, partial sums.  No reference counterpart (the
+   reference allocates fresh Lisp vectors per round, src/sumcheck.lisp:92). */
+int sc_create(int device, sc_ctx **ctx);
+int sc_destroy(sc_ctx *ctx);
+
+/* A cap, in bytes, on the device memory the context may hold (0 = no cap).  Exceeding it makes
+   the allocating call return SC_ENOMEM before any CUDA allocation is tried. */
+int sc_set_memory_budget(sc_ctx *ctx, uint64_t bytes);
+
+const char *sc_strerror(int code);
+const char *sc_last_error(const sc_ctx *ctx);
+
+/* The statement as a term table: sum over terms of coefficient * product of tables.  This is
+   what EXPAND (src/forms.lisp:57-78) gives once the constants' values are multiplied into each
+   monomial's coefficient; it replaces the compiled round kernel of the reference
+   (ROUND-KERNEL-CODE, src/sumcheck.lisp:190-258, and STATEMENT-FUNCTION, :108-110).
+     D          extension degree, 4 or 8 (TRANSCRIPT-DEGREE)
+     points     max(degree, 1): the round message has POINTS rows, X = 0, 2, .., POINTS (:186-188)
+     ntables    number of table slots; tables that occur in no term are still folded (:528, :562)
+     coeffs     nterms * D canonical words
+     term_ptr   nterms + 1 offsets into term_tables (CSR); term t multiplies tables
+                term_tables[term_ptr[t] .. term_ptr[t+1]), repeated indices for powers */
+int sc_set_statement(sc_ctx *ctx, int D, int points, int ntables, int nterms, const uint32_t *coeffs,
+                     const int32_t *term_ptr, const int32_t *term_tables);
+
+/* Table SLOT from host memory: ENTRIES entries of STRIDE words, stride 1 (base field) or D.
+   Stands in for MAKE-TABLE (src/sumcheck.lisp:61-70).  The host array is only read. */
+int sc_upload_table(sc_ctx *ctx, int slot, const uint32_t *host, uint64_t entries, int stride);
+
+/* Table SLOT filled on the device by the seeded generator of the benchmarks:
+   word c of entry i = splitmix64(seed ^ table_id << 56 ^ c << 48 ^ (first + i)) mod p;
+   with NONZERO an all-zero entry gets word 0 = 1.  No reference counterpart. */
+int sc_generate_table(sc_ctx *ctx, int slot, uint64_t seed, int table_id, uint64_t first, uint64_t entries,
+                      int stride, int nonzero);
+
+/* The current (folded) contents of table SLOT as canonical extension elements, for tests.
+   Writes min(entries, CAP) entries of D words; *ENTRIES gets the table's size. */
+int sc_download_table(sc_ctx *ctx, int slot, uint32_t *host, uint64_t cap, uint64_t *entries);
+
+/* Start a proof of N rounds over the uploaded tables (each K * 2^N entries, K = 1 when
+   BLOCK_WEIGHTS is NULL).  EQ: N extension elements or NULL (weights 1).  Builds the eq weight
+   tables of every round on the device (WEIGHTS and SPLIT-WEIGHTS, src/sumcheck.lisp:37-49; the
+   split point is chosen per round by the library, which does not change any sum). */
+int sc_begin(sc_ctx *ctx, int n, const uint32_t *eq, int K, const uint32_t *block_weights);
+
+/* Round j: the sums g_j(X) at X = 0, 2, .., POINTS over the pairs of the current tables, as
+   POINTS * D canonical words, row-major (what ROUND-MESSAGE sends, src/sumcheck.lisp:313-317).
+   For j > 0 the fold by the previous challenge (FOLD-FLAT-TABLE, :84-104) happens inside the
+   same kernel, on the way in.  With a communicator (sc_comm_init) the sums are the whole job's. */
+int sc_round(sc_ctx *ctx, uint32_t *sums);
+
+/* The challenge of the round just computed, D canonical words (CHALLENGE, src/transcript.lisp:174).
+   It is applied by the next sc_round or by sc_finish. */
+int sc_challenge(sc_ctx *ctx, const uint32_t *r);
+
+/* After the last challenge: every table folded to K entries, written as ntables * K * D canonical
+   words (the third value of PROVE, src/sumcheck.lisp:567-571; its second value, the finals, is
+   entry 0 of each).  With N = 0 these are the tables' own entries. */
+int sc_finish(sc_ctx *ctx, uint32_t *folded);
+
+/* Timing of the rounds of the last proof, measured with CUDA events on the context's stream. */
+typedef struct sc_round_stat {
+    float kernel_ms;        /* the round kernel (fold + sums) */
+    uint64_t bytes;         /* algorithmic bytes: tables read once + folded tables written once */
+    uint64_t pairs;         /* pairs summed in the round */
+} sc_round_stat;
+int sc_enable_timing(sc_ctx *ctx, int on);
+int sc_round_stats(sc_ctx *ctx, sc_round_stat *stats, int cap, int *count);
+/* Kernels launched by this context since it was created. */
+uint64_t sc_launch_count(const sc_ctx *ctx);
+
+/* Several GPUs: the hypercube is cut on its top log2(WORLD) variables, rank RANK holding entries
+   [RANK * 2^N / WORLD, (RANK + 1) * 2^N / WORLD) of every table.  Each round's sums are combined
+   with an NCCL all-gather of POINTS * D words and a sum mod p; when fewer than log2(WORLD)
+   variables would remain per rank the tables are gathered and every rank finishes alike.
+   NCCL_ID is the 128-byte ncclUniqueId made by rank 0 (sc_comm_unique_id) and handed to the
+   others by the caller.  sc_begin's N stays the whole job's.  No reference counterpart. */
+int sc_comm_unique_id(void *nccl_id128);
+int sc_comm_init(sc_ctx *ctx, const void *nccl_id128, int rank, int world);
+
+/* ------------------------------------------------------------------ part 2: the host layer */
+
+typedef struct sc_transcript sc_transcript;
+
+/* MAKE-TRANSCRIPT (src/transcript.lisp:75-84), prover side: B3S over "LLM-SUMCHECK-v6-O|" | label. */
+sc_transcript *sc_transcript_new(const uint8_t *label, size_t label_len, int degree);
+void sc_transcript_free(sc_transcript *tr);
+/* ABSORB (:95-100), SEND of a field array (:133-135), CHALLENGE-BASE (:166-172), B3S-DIGEST of the state */
+int sc_transcript_absorb(sc_transcript *tr, const uint8_t *data, uint64_t len);
+int sc_transcript_send(sc_transcript *tr, const uint32_t *values, int rows, int cols);
+int sc_transcript_challenge_base(sc_transcript *tr, int k, uint32_t *out);
+int sc_transcript_challenge_bits(sc_transcript *tr, int nbits, int k, uint64_t *out);
+int sc_transcript_digest(const sc_transcript *tr, uint8_t *out, size_t n);
+/* TRANSCRIPT-MESSAGES (:69), TRANSCRIPT-SENT-BYTES (:73) */
+int sc_transcript_message_count(const sc_transcript *tr);
+int sc_transcript_message(const sc_transcript *tr, int index, uint64_t dims[2], uint32_t *values);
+uint64_t sc_transcript_sent_bytes(const sc_transcript *tr);
+/* ENCODE-PROOF (src/proofio.lisp:44-49) of the recorded messages: returns the size; writes when CAP allows. */
+uint64_t sc_transcript_encode(const sc_transcript *tr, const char magic[8], uint8_t *out, uint64_t cap);
+
+/* EXPAND + the lowering to a term table (src/forms.lisp:57-78; STATEMENT-DEGREE,
+   src/sumcheck.lisp:33-35).  STATEMENT is the form as text, e.g. "(+ (* alpha t0 t1) (* 3 t1))".
+   Outputs as for sc_set_statement; *DEGREE gets the degree in the tables.  Capacities:
+   SC_MAX_TERMS terms, SC_MAX_TERMS * SC_MAX_FACTORS table indices. */
+int sc_lower_statement(const char *statement, int D, int ntables, const char *const *table_names, int nconstants,
+                       const char *const *constant_names, const uint32_t *constant_values, int *degree, int *nterms,
+                       uint32_t *coeffs, int32_t *term_ptr, int32_t *term_tables);
+
+/* PROVE (src/sumcheck.lisp:512-571) with the reference's argument meaning.  TABLES[t] is host
+   memory of K * 2^N entries of STRIDES[t] words, or NULL for a table already on the device in
+   slot t (sc_upload_table, sc_generate_table).  DEGREE < 0 takes the statement's degree.
+   Outputs (any may be NULL): CHALLENGES n * D, FINALS ntables * D, FOLDED ntables * max(K,1) * D.
+   TR ends in the state, and with the recorded messages, the reference leaves it in. */
+int sc_prove(sc_ctx *ctx, sc_transcript *tr, int n, const char *statement, int ntables,
+             const char *const *table_names, const uint32_t *const *tables, const int *strides, const uint32_t *eq,
+             int nconstants, const char *const *constant_names, const uint32_t *constant_values, const char *label,
+             int K, const uint32_t *block_weights, int degree, uint32_t *challenges, uint32_t *finals,
+             uint32_t *folded);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* SUMCHECK_B200_H */

@@ -1,0 +1,672 @@
+// context.cu -- part 1 of the C ABI: the device layer behind the reference's PROVE
+// (src/sumcheck.lisp:512-571).  A context owns the tables, the ping-pong buffers of the folded
+// tables, the eq weights of every round and the buffers of the partial sums, and runs one round
+// kernel per sc_round.  The transcript stays with the caller: per round POINTS * D words go to
+// the host and D words come back.
+#include <dlfcn.h>
+
+#include <cstdarg>
+#include <cstdio>
+#include <cstdlib>
+#include <cstring>
+#include <string>
+#include <vector>
+
+#include "device.h"
+
+using namespace sc;
+using namespace scf;
+
+// ------------------------------------------------------------------ NCCL, loaded on first use
+// Only the multi-GPU path needs it, so the library carries no link-time dependency on it.
+namespace {
+typedef struct ncclComm *ncclComm_t;
+typedef struct { char internal[128]; } ncclUniqueId;
+typedef int ncclResult_t;
+enum { NCCL_UINT32 = 3 };
+struct Nccl {
+    void *handle = nullptr;
+    ncclResult_t (*GetUniqueId)(ncclUniqueId *) = nullptr;
+    ncclResult_t (*CommInitRank)(ncclComm_t *, int, ncclUniqueId, int) = nullptr;
+    ncclResult_t (*CommDestroy)(ncclComm_t) = nullptr;
+    ncclResult_t (*AllGather)(const void *, void *, size_t, int, ncclComm_t, cudaStream_t) = nullptr;
+    const char *(*GetErrorString)(ncclResult_t) = nullptr;
+    bool load() {
+        if (handle) return true;
+        const char *names[] = {"libnccl.so.2", "libnccl.so"};
+        for (const char *nm : names) {
+            handle = dlopen(nm, RTLD_NOW | RTLD_GLOBAL);
+            if (handle) break;
+        }
+        if (!handle) return false;
+        GetUniqueId = (decltype(GetUniqueId))dlsym(handle, "ncclGetUniqueId");
+        CommInitRank = (decltype(CommInitRank))dlsym(handle, "ncclCommInitRank");
+        CommDestroy = (decltype(CommDestroy))dlsym(handle, "ncclCommDestroy");
+        AllGather = (decltype(AllGather))dlsym(handle, "ncclAllGather");
+        GetErrorString = (decltype(GetErrorString))dlsym(handle, "ncclGetErrorString");
+        return GetUniqueId && CommInitRank && CommDestroy && AllGather && GetErrorString;
+    }
+} g_nccl;
+}  // namespace
+
+// ------------------------------------------------------------------ the context
+
+struct TableState {
+    u32 *t0 = nullptr;          // the caller's table on the device (canonical words)
+    u64 t0_cap = 0;             // bytes allocated
+    u64 entries = 0;
+    int stride = 0;
+    u32 *buf[2] = {nullptr, nullptr};   // ping-pong buffers of the folded table (Montgomery form, D words per entry)
+    u64 buf_cap[2] = {0, 0};
+    // the table as the next kernel reads it
+    const u32 *cur = nullptr;
+    int cur_buf = -1;           // -1: t0 (or the gathered buffer), else buf index
+    bool cur_base = false, cur_raw = false;
+    u64 cur_entries = 0;
+};
+
+struct RoundPlan {
+    int logL = 0;
+    bool use_low = false, use_high = false;
+    u64 low_word = 0, high_word = 0;
+};
+
+struct sc_ctx {
+    int device = 0;
+    int sms = 148;
+    cudaStream_t stream = nullptr;
+    std::string last_error;
+    u64 budget = 0, used = 0;
+    uint64_t launches = 0;
+
+    // statement
+    int D = 0, points = 0, ntables = 0, nt_used = 0;
+    bool have_statement = false;
+    int order[SC_MAX_TABLES];        // kernel position -> slot (the statement's tables first)
+    DevStatement st;                 // factors are kernel positions
+
+    TableState tab[SC_MAX_TABLES];
+
+    // proof state
+    bool begun = false, have_r = false, have_eq = false;
+    int n = 0, K = 1, j = 0;
+    int nloc = 0;                    // rounds before the tables are gathered (n - log2 world)
+    u32 r[8];
+    u32 post[8];
+    bool use_post = false;
+    std::vector<RoundPlan> plan;
+
+    // device buffers
+    u32 *d_eq = nullptr, *d_bw = nullptr, *d_chunks = nullptr, *d_weights = nullptr;
+    u64 eq_cap = 0, bw_cap = 0, chunks_cap = 0, weights_cap = 0;
+    WeightDesc *d_descs = nullptr;
+    u64 descs_cap = 0;
+    u32 *d_partials = nullptr;
+    unsigned int *d_counter = nullptr;
+    u32 *d_out = nullptr, *h_out = nullptr, *h_out_dev = nullptr;   // h_out: mapped pinned; h_out_dev its device alias
+    u32 *d_export = nullptr, *h_export = nullptr;
+    u64 export_cap = 0;
+    u32 *d_gather = nullptr;         // world * MAX_PARTIAL_WORDS
+    u32 *d_gtab[SC_MAX_TABLES];      // gathered tables (world entries each)
+    int grid_cap = 0;
+
+    // timing
+    bool timing = false;
+    std::vector<cudaEvent_t> ev;
+    std::vector<sc_round_stat> stats;
+
+    // communicator
+    ncclComm_t comm = nullptr;
+    int rank = 0, world = 1, logw = 0;
+};
+
+static int fail(sc_ctx *c, int code, const char *fmt, ...) {
+    char buf[512];
+    va_list ap;
+    va_start(ap, fmt);
+    vsnprintf(buf, sizeof buf, fmt, ap);
+    va_end(ap);
+    if (c) c->last_error = buf;
+    return code;
+}
+#define CU(call)                                                                                          \
+    do {                                                                                                  \
+        cudaError_t e_ = (call);                                                                          \
+        if (e_ != cudaSuccess) return fail(ctx, e_ == cudaErrorMemoryAllocation ? SC_ENOMEM : SC_ECUDA, "%s: %s", #call, cudaGetErrorString(e_)); \
+    } while (0)
+
+static int dev_alloc(sc_ctx *ctx, void **p, u64 bytes) {
+    if (ctx->budget && ctx->used + bytes > ctx->budget)
+        return fail(ctx, SC_ENOMEM, "memory budget: %llu bytes held, %llu more asked, cap %llu", (unsigned long long)ctx->used,
+                    (unsigned long long)bytes, (unsigned long long)ctx->budget);
+    cudaError_t e = cudaMalloc(p, bytes ? bytes : 16);
+    if (e != cudaSuccess) { cudaGetLastError(); return fail(ctx, SC_ENOMEM, "cudaMalloc of %llu bytes: %s", (unsigned long long)bytes, cudaGetErrorString(e)); }
+    ctx->used += bytes;
+    return SC_OK;
+}
+static void dev_free(sc_ctx *ctx, void *p, u64 bytes) {
+    if (!p) return;
+    cudaFree(p);
+    ctx->used -= bytes <= ctx->used ? bytes : ctx->used;
+}
+// grow a buffer to at least BYTES (contents are not kept)
+template <class T> static int ensure(sc_ctx *ctx, T **p, u64 *cap, u64 bytes) {
+    if (*p && *cap >= bytes) return SC_OK;
+    dev_free(ctx, *p, *cap);
+    *p = nullptr; *cap = 0;
+    int rc = dev_alloc(ctx, (void **)p, bytes);
+    if (rc) return rc;
+    *cap = bytes;
+    return SC_OK;
+}
+
+extern "C" const char *sc_strerror(int code) {
+    switch (code) {
+    case SC_OK: return "ok";
+    case SC_EINVAL: return "invalid parameter";
+    case SC_ECUDA: return "CUDA error";
+    case SC_ENOMEM: return "out of memory";
+    case SC_EUNSUPPORTED: return "unsupported shape";
+    case SC_ESTATE: return "call out of order";
+    case SC_ECOMM: return "communicator error";
+    case SC_ESTATEMENT: return "bad statement";
+    default: return "unknown error";
+    }
+}
+extern "C" const char *sc_last_error(const sc_ctx *ctx) { return ctx ? ctx->last_error.c_str() : ""; }
+
+extern "C" int sc_create(int device, sc_ctx **out) {
+    if (!out) return SC_EINVAL;
+    *out = nullptr;
+    int count = 0;
+    if (cudaGetDeviceCount(&count) != cudaSuccess || count == 0) { cudaGetLastError(); return SC_ECUDA; }
+    if (device < 0 || device >= count) return SC_EINVAL;
+    sc_ctx *ctx = new sc_ctx();
+    ctx->device = device;
+    for (int t = 0; t < SC_MAX_TABLES; t++) ctx->d_gtab[t] = nullptr;
+    cudaError_t e = cudaSetDevice(device);
+    if (e == cudaSuccess) e = cudaStreamCreateWithFlags(&ctx->stream, cudaStreamNonBlocking);
+    cudaDeviceProp prop;
+    if (e == cudaSuccess) e = cudaGetDeviceProperties(&prop, device);
+    if (e != cudaSuccess) { delete ctx; return SC_ECUDA; }
+    ctx->sms = prop.multiProcessorCount;
+    ctx->grid_cap = ctx->sms * 8;
+    bool ok = cudaMalloc(&ctx->d_partials, (size_t)ctx->grid_cap * MAX_PARTIAL_WORDS * 4) == cudaSuccess &&
+              cudaMalloc(&ctx->d_counter, 64) == cudaSuccess && cudaMemset(ctx->d_counter, 0, 64) == cudaSuccess &&
+              cudaMalloc(&ctx->d_out, MAX_PARTIAL_WORDS * 4) == cudaSuccess &&
+              cudaHostAlloc(&ctx->h_out, MAX_PARTIAL_WORDS * 4, cudaHostAllocMapped) == cudaSuccess &&
+              cudaHostGetDevicePointer(&ctx->h_out_dev, ctx->h_out, 0) == cudaSuccess;
+    if (!ok) { cudaGetLastError(); sc_destroy(ctx); return SC_ECUDA; }
+    *out = ctx;
+    return SC_OK;
+}
+
+extern "C" int sc_destroy(sc_ctx *ctx) {
+    if (!ctx) return SC_OK;
+    cudaSetDevice(ctx->device);
+    if (ctx->stream) cudaStreamSynchronize(ctx->stream);
+    if (ctx->comm && g_nccl.CommDestroy) g_nccl.CommDestroy(ctx->comm);
+    for (auto &t : ctx->tab) { cudaFree(t.t0); cudaFree(t.buf[0]); cudaFree(t.buf[1]); }
+    for (auto p : ctx->d_gtab) cudaFree(p);
+    cudaFree(ctx->d_eq); cudaFree(ctx->d_bw); cudaFree(ctx->d_chunks); cudaFree(ctx->d_weights); cudaFree(ctx->d_descs);
+    cudaFree(ctx->d_partials); cudaFree(ctx->d_counter); cudaFree(ctx->d_out); cudaFree(ctx->d_export); cudaFree(ctx->d_gather);
+    if (ctx->h_out) cudaFreeHost(ctx->h_out);
+    if (ctx->h_export) cudaFreeHost(ctx->h_export);
+    for (auto e : ctx->ev) cudaEventDestroy(e);
+    if (ctx->stream) cudaStreamDestroy(ctx->stream);
+    cudaGetLastError();
+    delete ctx;
+    return SC_OK;
+}
+
+extern "C" int sc_set_memory_budget(sc_ctx *ctx, uint64_t bytes) {
+    if (!ctx) return SC_EINVAL;
+    ctx->budget = bytes;
+    return SC_OK;
+}
+extern "C" uint64_t sc_launch_count(const sc_ctx *ctx) { return ctx ? ctx->launches : 0; }
+
+extern "C" int sc_enable_timing(sc_ctx *ctx, int on) {
+    if (!ctx) return SC_EINVAL;
+    ctx->timing = on != 0;
+    return SC_OK;
+}
+extern "C" int sc_round_stats(sc_ctx *ctx, sc_round_stat *stats, int cap, int *count) {
+    if (!ctx || !count) return SC_EINVAL;
+    *count = (int)ctx->stats.size();
+    for (int i = 0; i < *count && i < cap && stats; i++) stats[i] = ctx->stats[i];
+    return SC_OK;
+}
+
+// ------------------------------------------------------------------ statement
+
+extern "C" int sc_set_statement(sc_ctx *ctx, int D, int points, int ntables, int nterms, const uint32_t *coeffs,
+                                const int32_t *term_ptr, const int32_t *term_tables) {
+    if (!ctx) return SC_EINVAL;
+    if (D != 4 && D != 8) return fail(ctx, SC_EINVAL, "extension degree %d: expected 4 or 8", D);
+    if (points < 1) return fail(ctx, SC_EINVAL, "points %d: expected at least 1", points);
+    if (ntables < 1 || nterms < 0 || (nterms && (!coeffs || !term_ptr))) return fail(ctx, SC_EINVAL, "bad term table");
+    if (ntables > SC_MAX_TABLES) return fail(ctx, SC_EUNSUPPORTED, "%d tables: at most %d", ntables, SC_MAX_TABLES);
+    if (nterms > SC_MAX_TERMS) return fail(ctx, SC_EUNSUPPORTED, "%d terms: at most %d", nterms, SC_MAX_TERMS);
+    if (points > SC_MAX_POINTS) return fail(ctx, SC_EUNSUPPORTED, "degree %d: at most %d", points, SC_MAX_POINTS);
+    bool used[SC_MAX_TABLES] = {false};
+    for (int t = 0; t < nterms; t++) {
+        const int nf = term_ptr[t + 1] - term_ptr[t];
+        if (nf < 0 || nf > SC_MAX_FACTORS) return fail(ctx, SC_EUNSUPPORTED, "term %d has %d factors: at most %d", t, nf, SC_MAX_FACTORS);
+        for (int k = term_ptr[t]; k < term_ptr[t + 1]; k++) {
+            if (term_tables[k] < 0 || term_tables[k] >= ntables) return fail(ctx, SC_EINVAL, "term %d names table %d of %d", t, term_tables[k], ntables);
+            used[term_tables[k]] = true;
+        }
+    }
+    // the statement's tables first, in slot order; the others (only folded) after them
+    int pos_of[SC_MAX_TABLES], npos = 0;
+    for (int s = 0; s < ntables; s++) if (used[s]) { ctx->order[npos] = s; pos_of[s] = npos++; }
+    const int nt_used = npos;
+    for (int s = 0; s < ntables; s++) if (!used[s]) { ctx->order[npos] = s; pos_of[s] = npos++; }
+    if (nt_used > 4) return fail(ctx, SC_EUNSUPPORTED, "the statement multiplies %d different tables: at most 4", nt_used);
+    ctx->D = D; ctx->points = points; ctx->ntables = ntables; ctx->nt_used = nt_used > 0 ? nt_used : 1;
+    memset(&ctx->st, 0, sizeof ctx->st);
+    ctx->st.nterms = nterms;
+    for (int t = 0; t < nterms; t++) {
+        DevTerm &tm = ctx->st.terms[t];
+        bool upper = false;
+        for (int c = 0; c < D; c++) {
+            const u32 v = coeffs[(size_t)t * D + c] % P;
+            tm.coeff[c] = to_mont(v);
+            if (c && v) upper = true;
+        }
+        tm.ckind = upper ? CK_EXT : ((coeffs[(size_t)t * D] % P) == 1 ? CK_ONE : CK_BASE);
+        tm.nf = (uint8_t)(term_ptr[t + 1] - term_ptr[t]);
+        for (int k = 0; k < tm.nf; k++) tm.f[k] = (uint8_t)pos_of[term_tables[term_ptr[t] + k]];
+        if (tm.nf == 0) tm.ckind = CK_EXT;
+    }
+    ctx->have_statement = true;
+    ctx->begun = false;
+    return SC_OK;
+}
+
+// ------------------------------------------------------------------ tables
+
+static int table_slot(sc_ctx *ctx, int slot, uint64_t entries, int stride) {
+    if (!ctx) return SC_EINVAL;
+    if (slot < 0 || slot >= SC_MAX_TABLES) return fail(ctx, SC_EINVAL, "table slot %d: expected 0..%d", slot, SC_MAX_TABLES - 1);
+    if (stride != 1 && stride != 4 && stride != 8) return fail(ctx, SC_EINVAL, "stride %d: expected 1 or the extension degree", stride);
+    if (entries == 0) return fail(ctx, SC_EINVAL, "empty table");
+    cudaSetDevice(ctx->device);
+    TableState &t = ctx->tab[slot];
+    int rc = ensure(ctx, &t.t0, &t.t0_cap, entries * (u64)stride * 4);
+    if (rc) return rc;
+    t.entries = entries; t.stride = stride;
+    ctx->begun = false;
+    return SC_OK;
+}
+
+extern "C" int sc_upload_table(sc_ctx *ctx, int slot, const uint32_t *host, uint64_t entries, int stride) {
+    if (!host) return SC_EINVAL;
+    int rc = table_slot(ctx, slot, entries, stride);
+    if (rc) return rc;
+    TableState &t = ctx->tab[slot];
+    CU(cudaMemcpyAsync(t.t0, host, entries * (u64)stride * 4, cudaMemcpyHostToDevice, ctx->stream));
+    CU(launch_reduce_words(t.t0, entries * (u64)stride, ctx->stream));   // COERCE-EXT reduces its input
+    ctx->launches++;
+    CU(cudaStreamSynchronize(ctx->stream));
+    return SC_OK;
+}
+
+extern "C" int sc_generate_table(sc_ctx *ctx, int slot, uint64_t seed, int table_id, uint64_t first, uint64_t entries, int stride,
+                                 int nonzero) {
+    int rc = table_slot(ctx, slot, entries, stride);
+    if (rc) return rc;
+    CU(launch_generate(ctx->tab[slot].t0, seed, table_id, first, entries, stride, nonzero, ctx->stream));
+    ctx->launches++;
+    CU(cudaStreamSynchronize(ctx->stream));
+    return SC_OK;
+}
+
+static int export_tables(sc_ctx *ctx, const int *slots, int count, u64 entries, u32 *host) {
+    const int D = ctx->D;
+    const u64 words = (u64)count * entries * D;
+    if (!words) return SC_OK;
+    if (ctx->export_cap < words * 4) {
+        if (ctx->h_export) cudaFreeHost(ctx->h_export);
+        ctx->h_export = nullptr;
+        u64 cap = ctx->export_cap;
+        int rc = ensure(ctx, &ctx->d_export, &cap, words * 4);
+        ctx->export_cap = cap;
+        if (rc) return rc;
+        CU(cudaHostAlloc(&ctx->h_export, words * 4, cudaHostAllocDefault));
+    }
+    ExportArgs a;
+    memset(&a, 0, sizeof a);
+    a.ntables = count; a.count = entries; a.out = ctx->d_export;
+    bool raw = false;
+    for (int k = 0; k < count; k++) {
+        const TableState &t = ctx->tab[slots[k]];
+        a.src[k] = t.cur; a.src_base[k] = t.cur_base;
+        if (k && raw != t.cur_raw) return fail(ctx, SC_ESTATE, "tables in different states");
+        raw = t.cur_raw;
+    }
+    a.raw = raw;
+    CU(launch_export(D, a, ctx->stream));
+    ctx->launches++;
+    CU(cudaMemcpyAsync(ctx->h_export, ctx->d_export, words * 4, cudaMemcpyDeviceToHost, ctx->stream));
+    CU(cudaStreamSynchronize(ctx->stream));
+    memcpy(host, ctx->h_export, words * 4);
+    return SC_OK;
+}
+
+extern "C" int sc_download_table(sc_ctx *ctx, int slot, uint32_t *host, uint64_t cap, uint64_t *entries) {
+    if (!ctx || slot < 0 || slot >= SC_MAX_TABLES || !ctx->D) return SC_EINVAL;
+    TableState &t = ctx->tab[slot];
+    if (!t.t0) return fail(ctx, SC_ESTATE, "table %d was never uploaded", slot);
+    cudaSetDevice(ctx->device);
+    if (!ctx->begun) { t.cur = t.t0; t.cur_base = t.stride == 1; t.cur_raw = true; t.cur_entries = t.entries; t.cur_buf = -1; }
+    if (entries) *entries = t.cur_entries;
+    const u64 count = t.cur_entries < cap ? t.cur_entries : cap;
+    if (!host || !count) return SC_OK;
+    return export_tables(ctx, &slot, 1, count, host);
+}
+
+// ------------------------------------------------------------------ begin: the weights of every round
+
+static int low_bits_cap(int D) { return D == 4 ? 10 : 9; }   // 2^a multipliers of 2 D words in shared memory: 32 KiB
+
+// The split of the v = (variables after the round's own) eq variables of a round: the lower a of
+// them index the low multipliers held in shared memory, the others the high weights.  Any split
+// gives the same sums (SPLIT-WEIGHTS, src/sumcheck.lisp:43-49, splits in the middle).
+static int split_bits(int D, int v) {
+    if (v < 20) return 0;
+    int a = v - 12;
+    return a < low_bits_cap(D) ? a : low_bits_cap(D);
+}
+
+extern "C" int sc_begin(sc_ctx *ctx, int n, const uint32_t *eq, int K, const uint32_t *block_weights) {
+    if (!ctx) return SC_EINVAL;
+    if (!ctx->have_statement) return fail(ctx, SC_ESTATE, "sc_begin before sc_set_statement");
+    if (n < 0 || n > 40) return fail(ctx, SC_EINVAL, "n = %d", n);
+    if (block_weights && K < 1) return fail(ctx, SC_EINVAL, "K = %d block weights", K);
+    if (!block_weights) K = 1;
+    const int D = ctx->D, w = ctx->logw;
+    if (ctx->world > 1 && (block_weights || n < w)) return fail(ctx, SC_EUNSUPPORTED, "several GPUs: no block weights, and n >= log2(world)");
+    cudaSetDevice(ctx->device);
+    const int nloc = n - w;
+    const u64 want = (u64)K << nloc;
+    for (int s = 0; s < ctx->ntables; s++) {
+        TableState &t = ctx->tab[s];
+        if (!t.t0) return fail(ctx, SC_ESTATE, "table %d was never uploaded", s);
+        if (t.entries != want) return fail(ctx, SC_EINVAL, "table %d has %llu entries: expected %llu", s, (unsigned long long)t.entries, (unsigned long long)want);
+        if (t.stride != 1 && t.stride != D) return fail(ctx, SC_EINVAL, "table %d has stride %d: expected 1 or %d", s, t.stride, D);
+        t.cur = t.t0; t.cur_buf = -1; t.cur_base = t.stride == 1; t.cur_raw = true; t.cur_entries = t.entries;
+    }
+    ctx->n = n; ctx->K = K; ctx->j = 0; ctx->nloc = nloc; ctx->have_r = false; ctx->have_eq = eq != nullptr;
+    ctx->stats.clear();
+    ctx->plan.assign(n, RoundPlan());
+
+    // eq and block weights in Montgomery form
+    std::vector<u32> eqm((size_t)(n > 0 ? n : 1) * D, 0), bwm((size_t)K * D, 0);
+    if (eq) for (size_t i = 0; i < (size_t)n * D; i++) eqm[i] = to_mont(eq[i] % P);
+    if (block_weights) for (size_t i = 0; i < (size_t)K * D; i++) bwm[i] = to_mont(block_weights[i] % P);
+
+    // the factor of this rank: eq(r[nloc .. n), rank)
+    ctx->use_post = false;
+    if (ctx->world > 1 && eq) {
+        if (D == 4) {
+            Ext<4> acc = eone_mont<4>(), one = eone_mont<4>();
+            for (int k = 0; k < w; k++) {
+                Ext<4> rk; for (int c = 0; c < 4; c++) rk.v[c] = eqm[(size_t)(nloc + k) * 4 + c];
+                acc = emul<4>(acc, ((ctx->rank >> k) & 1) ? rk : esub<4>(one, rk));
+            }
+            for (int c = 0; c < 4; c++) ctx->post[c] = acc.v[c];
+        } else {
+            Ext<8> acc = eone_mont<8>(), one = eone_mont<8>();
+            for (int k = 0; k < w; k++) {
+                Ext<8> rk; for (int c = 0; c < 8; c++) rk.v[c] = eqm[(size_t)(nloc + k) * 8 + c];
+                acc = emul<8>(acc, ((ctx->rank >> k) & 1) ? rk : esub<8>(one, rk));
+            }
+            for (int c = 0; c < 8; c++) ctx->post[c] = acc.v[c];
+        }
+        ctx->use_post = true;
+    }
+
+    // one LOW and one HIGH table per round
+    std::vector<WeightDesc> descs;
+    u64 words = 0, total_entries = 0;
+    for (int j = 0; j < n; j++) {
+        RoundPlan &pl = ctx->plan[j];
+        const bool local = j < nloc;                 // before the gather
+        const int end = local ? nloc : n;            // eq variables of this stage end here
+        const int v = end - 1 - j;
+        const int blocks = local ? K : 1;
+        const int a = split_bits(D, v);
+        pl.logL = a;
+        pl.use_low = eq && a > 0;
+        const bool has_bw = block_weights && local;
+        pl.use_high = (eq && v - a > 0) || has_bw;   // a single high weight without block weights is 1
+        if (pl.use_low) {
+            WeightDesc d; d.out_word = words; d.entries = 1ull << a; d.start = j + 1; d.bits = a; d.kind = 1; d.blocks = 0;
+            pl.low_word = words; words += d.entries * 2 * D; total_entries += d.entries; descs.push_back(d);
+        }
+        if (pl.use_high) {
+            WeightDesc d; d.out_word = words; d.entries = 1ull << (v - a); d.start = j + 1 + a; d.bits = eq ? v - a : 0; d.kind = 0;
+            d.blocks = has_bw ? blocks : 0;
+            const u64 count = d.entries * (u64)(d.blocks ? d.blocks : 1);
+            pl.high_word = words; words += count * D; total_entries += count; descs.push_back(d);
+        }
+    }
+    int rc;
+    if ((rc = ensure(ctx, &ctx->d_eq, &ctx->eq_cap, eqm.size() * 4))) return rc;
+    if ((rc = ensure(ctx, &ctx->d_bw, &ctx->bw_cap, bwm.size() * 4))) return rc;
+    if ((rc = ensure(ctx, &ctx->d_chunks, &ctx->chunks_cap, (u64)(n > 0 ? n : 1) * 512 * D * 4))) return rc;
+    if ((rc = ensure(ctx, &ctx->d_weights, &ctx->weights_cap, (words ? words : 4) * 4))) return rc;
+    if ((rc = ensure(ctx, &ctx->d_descs, &ctx->descs_cap, (descs.size() ? descs.size() : 1) * sizeof(WeightDesc)))) return rc;
+    CU(cudaMemcpyAsync(ctx->d_eq, eqm.data(), eqm.size() * 4, cudaMemcpyHostToDevice, ctx->stream));
+    CU(cudaMemcpyAsync(ctx->d_bw, bwm.data(), bwm.size() * 4, cudaMemcpyHostToDevice, ctx->stream));
+    if (!descs.empty()) CU(cudaMemcpyAsync(ctx->d_descs, descs.data(), descs.size() * sizeof(WeightDesc), cudaMemcpyHostToDevice, ctx->stream));
+    if (eq && n > 0) { CU(launch_eq_chunks(D, ctx->d_eq, n, ctx->d_chunks, ctx->stream)); ctx->launches++; }
+    if (total_entries) {
+        CU(launch_weight_tables(D, ctx->d_chunks, ctx->d_descs, (int)descs.size(), ctx->d_bw, ctx->d_weights, total_entries, ctx->stream));
+        ctx->launches++;
+    }
+    // the host vectors above must outlive the copies
+    CU(cudaStreamSynchronize(ctx->stream));
+    ctx->begun = true;
+    return SC_OK;
+}
+
+// ------------------------------------------------------------------ rounds
+
+static void challenge_words(const sc_ctx *ctx, bool raw, u32 *out) {
+    // r R for a source in Montgomery form; r R^2 for canonical words, so that REDC(r' s) = r s R
+    for (int c = 0; c < ctx->D; c++) {
+        u32 m = to_mont(ctx->r[c]);
+        out[c] = raw ? to_mont(m) : m;
+    }
+}
+
+// Fold every table by the pending challenge with the stand-alone kernel (the last fold, and the
+// fold before the gather).
+static int fold_all(sc_ctx *ctx) {
+    const int D = ctx->D;
+    FoldArgs a;
+    memset(&a, 0, sizeof a);
+    a.ntables = ctx->ntables;
+    if (!a.ntables) return SC_OK;
+    const TableState &t0 = ctx->tab[0];
+    a.raw = t0.cur_raw;
+    a.nout = t0.cur_entries / 2;
+    challenge_words(ctx, a.raw, a.r);
+    for (int s = 0; s < ctx->ntables; s++) {
+        TableState &t = ctx->tab[s];
+        const int nb = t.cur_buf == 0 ? 1 : 0;
+        int rc = ensure(ctx, &t.buf[nb], &t.buf_cap[nb], a.nout * D * 4);
+        if (rc) return rc;
+        a.src[s] = t.cur; a.src_base[s] = t.cur_base; a.dst[s] = t.buf[nb];
+    }
+    CU(launch_fold(D, a, ctx->stream));
+    ctx->launches++;
+    for (int s = 0; s < ctx->ntables; s++) {
+        TableState &t = ctx->tab[s];
+        const int nb = t.cur_buf == 0 ? 1 : 0;
+        t.cur = t.buf[nb]; t.cur_buf = nb; t.cur_base = false; t.cur_raw = false; t.cur_entries = a.nout;
+    }
+    ctx->have_r = false;
+    return SC_OK;
+}
+
+// Gather every rank's one entry per table into tables of WORLD entries, alike on every rank.
+static int gather_tables(sc_ctx *ctx) {
+    const int D = ctx->D;
+    for (int s = 0; s < ctx->ntables; s++) {
+        TableState &t = ctx->tab[s];
+        if (t.cur_entries != 1) return fail(ctx, SC_ESTATE, "gather with %llu entries per rank", (unsigned long long)t.cur_entries);
+        const int words = t.cur_base ? 1 : D;
+        if (!ctx->d_gtab[s]) { int rc = dev_alloc(ctx, (void **)&ctx->d_gtab[s], (u64)ctx->world * 8 * 4); if (rc) return rc; }
+        ncclResult_t r = g_nccl.AllGather(t.cur, ctx->d_gtab[s], (size_t)words, NCCL_UINT32, ctx->comm, ctx->stream);
+        if (r) return fail(ctx, SC_ECOMM, "ncclAllGather: %s", g_nccl.GetErrorString(r));
+        t.cur = ctx->d_gtab[s]; t.cur_buf = -1; t.cur_entries = (u64)ctx->world;
+    }
+    return SC_OK;
+}
+
+extern "C" int sc_round(sc_ctx *ctx, uint32_t *sums) {
+    if (!ctx || !sums) return SC_EINVAL;
+    if (!ctx->begun) return fail(ctx, SC_ESTATE, "sc_round before sc_begin");
+    if (ctx->j >= ctx->n) return fail(ctx, SC_ESTATE, "all %d rounds are done", ctx->n);
+    if (ctx->j > 0 && !ctx->have_r) return fail(ctx, SC_ESTATE, "round %d needs the challenge of round %d", ctx->j, ctx->j - 1);
+    cudaSetDevice(ctx->device);
+    const int D = ctx->D, j = ctx->j, W = ctx->points * D;
+    if (!round_supported(D, ctx->points, ctx->nt_used)) return fail(ctx, SC_EUNSUPPORTED, "no kernel for D=%d points=%d tables=%d", D, ctx->points, ctx->nt_used);
+    int rc;
+    if (ctx->world > 1 && j == ctx->nloc) {   // the tables are down to one entry per rank: gather them
+        if (ctx->have_r && (rc = fold_all(ctx))) return rc;
+        if ((rc = gather_tables(ctx))) return rc;
+    }
+    const bool local = ctx->world > 1 && j < ctx->nloc;
+    const bool fold = ctx->have_r;
+    const RoundPlan &pl = ctx->plan[j];
+
+    RoundArgs a;
+    memset(&a, 0, sizeof a);
+    a.ntables = ctx->ntables;
+    u64 in_entries = 0, bytes = 0;
+    for (int k = 0; k < ctx->ntables; k++) {
+        TableState &t = ctx->tab[ctx->order[k]];
+        a.src[k] = t.cur; a.src_base[k] = t.cur_base;
+        if (k == 0) { a.raw = t.cur_raw; in_entries = t.cur_entries; }
+        else if ((int)t.cur_raw != a.raw || t.cur_entries != in_entries) return fail(ctx, SC_ESTATE, "tables in different states");
+        bytes += t.cur_entries * (u64)(t.cur_base ? 1 : D) * 4;
+        if (fold) {
+            const int nb = t.cur_buf == 0 ? 1 : 0;
+            if ((rc = ensure(ctx, &t.buf[nb], &t.buf_cap[nb], in_entries / 2 * D * 4))) return rc;
+            a.dst[k] = t.buf[nb];
+            bytes += in_entries / 2 * (u64)D * 4;
+        }
+    }
+    a.npairs = fold ? in_entries / 4 : in_entries / 2;
+    if (fold) challenge_words(ctx, a.raw != 0, a.r);
+    a.logL = pl.logL;
+    a.use_low = pl.use_low; a.use_high = pl.use_high;
+    a.low = ctx->d_weights + pl.low_word;
+    a.high = ctx->d_weights + pl.high_word;
+    a.st = ctx->st;
+    a.use_post = local && ctx->use_post;
+    memcpy(a.post, ctx->post, sizeof a.post);
+    a.partials = ctx->d_partials; a.counter = ctx->d_counter;
+    a.out_dev = ctx->d_out;
+    a.out_host = local ? nullptr : ctx->h_out_dev;
+
+    const u64 chunk = (1ull << a.logL) > (u64)ROUND_THREADS ? (1ull << a.logL) : (u64)ROUND_THREADS;
+    u64 chunks = (a.npairs + chunk - 1) / chunk;
+    int grid = (int)(chunks < (u64)(ctx->sms * 2) ? chunks : (u64)(ctx->sms * 2));
+    if (grid < 1) grid = 1;
+    const size_t smem = a.use_low ? ((size_t)1 << a.logL) * 2 * D * 4 : 0;
+
+    cudaEvent_t e0 = nullptr, e1 = nullptr;
+    if (ctx->timing) {
+        while (ctx->ev.size() < 2) { cudaEvent_t e; CU(cudaEventCreate(&e)); ctx->ev.push_back(e); }
+        e0 = ctx->ev[0]; e1 = ctx->ev[1];
+        CU(cudaEventRecord(e0, ctx->stream));
+    }
+    CU(launch_round(D, ctx->points, ctx->nt_used, fold, a, grid, smem, ctx->stream));
+    ctx->launches++;
+    if (ctx->timing) CU(cudaEventRecord(e1, ctx->stream));
+    if (local) {   // the whole job's sums: all-gather of the ranks' words, then their sum mod p
+        if (!ctx->d_gather) { if ((rc = dev_alloc(ctx, (void **)&ctx->d_gather, (u64)ctx->world * MAX_PARTIAL_WORDS * 4))) return rc; }
+        ncclResult_t r = g_nccl.AllGather(ctx->d_out, ctx->d_gather, (size_t)W, NCCL_UINT32, ctx->comm, ctx->stream);
+        if (r) return fail(ctx, SC_ECOMM, "ncclAllGather: %s", g_nccl.GetErrorString(r));
+        CU(launch_sum_ranks(ctx->d_gather, ctx->world, W, ctx->d_out, ctx->h_out_dev, ctx->stream));
+        ctx->launches++;
+    }
+    CU(cudaStreamSynchronize(ctx->stream));
+    memcpy(sums, ctx->h_out, (size_t)W * 4);
+    if (ctx->timing) {
+        sc_round_stat s;
+        CU(cudaEventElapsedTime(&s.kernel_ms, e0, e1));
+        s.bytes = bytes; s.pairs = a.npairs;
+        ctx->stats.push_back(s);
+    }
+    if (fold) {
+        for (int k = 0; k < ctx->ntables; k++) {
+            TableState &t = ctx->tab[ctx->order[k]];
+            const int nb = t.cur_buf == 0 ? 1 : 0;
+            t.cur = t.buf[nb]; t.cur_buf = nb; t.cur_base = false; t.cur_raw = false; t.cur_entries = in_entries / 2;
+        }
+    }
+    ctx->have_r = false;
+    ctx->j = j + 1;
+    return SC_OK;
+}
+
+extern "C" int sc_challenge(sc_ctx *ctx, const uint32_t *r) {
+    if (!ctx || !r) return SC_EINVAL;
+    if (!ctx->begun || ctx->j == 0) return fail(ctx, SC_ESTATE, "sc_challenge before the first round");
+    if (ctx->have_r) return fail(ctx, SC_ESTATE, "round %d already has its challenge", ctx->j - 1);
+    for (int c = 0; c < ctx->D; c++) ctx->r[c] = r[c] % P;
+    ctx->have_r = true;
+    return SC_OK;
+}
+
+extern "C" int sc_finish(sc_ctx *ctx, uint32_t *folded) {
+    if (!ctx) return SC_EINVAL;
+    if (!ctx->begun) return fail(ctx, SC_ESTATE, "sc_finish before sc_begin");
+    if (ctx->j != ctx->n) return fail(ctx, SC_ESTATE, "%d of %d rounds done", ctx->j, ctx->n);
+    if (ctx->n > 0 && !ctx->have_r) return fail(ctx, SC_ESTATE, "the last round has no challenge");
+    cudaSetDevice(ctx->device);
+    int rc;
+    if (ctx->n > 0 && (rc = fold_all(ctx))) return rc;
+    if (folded && ctx->ntables) {
+        int slots[SC_MAX_TABLES];
+        for (int s = 0; s < ctx->ntables; s++) slots[s] = s;
+        if ((rc = export_tables(ctx, slots, ctx->ntables, (u64)ctx->K, folded))) return rc;
+    }
+    ctx->begun = false;
+    return SC_OK;
+}
+
+// ------------------------------------------------------------------ several GPUs
+
+extern "C" int sc_comm_unique_id(void *nccl_id128) {
+    if (!nccl_id128) return SC_EINVAL;
+    if (!g_nccl.load()) return SC_ECOMM;
+    ncclUniqueId id;
+    if (g_nccl.GetUniqueId(&id)) return SC_ECOMM;
+    memcpy(nccl_id128, &id, sizeof id);
+    return SC_OK;
+}
+
+extern "C" int sc_comm_init(sc_ctx *ctx, const void *nccl_id128, int rank, int world) {
+    if (!ctx || !nccl_id128) return SC_EINVAL;
+    if (world < 1 || (world & (world - 1)) || rank < 0 || rank >= world) return fail(ctx, SC_EINVAL, "rank %d of %d: the world must be a power of two", rank, world);
+    if (ctx->comm) return fail(ctx, SC_ESTATE, "the context already has a communicator");
+    if (!g_nccl.load()) return fail(ctx, SC_ECOMM, "cannot load libnccl.so.2: %s", dlerror());
+    cudaSetDevice(ctx->device);
+    ncclUniqueId id;
+    memcpy(&id, nccl_id128, sizeof id);
+    ncclResult_t r = g_nccl.CommInitRank(&ctx->comm, world, id, rank);
+    if (r) { ctx->comm = nullptr; return fail(ctx, SC_ECOMM, "ncclCommInitRank: %s", g_nccl.GetErrorString(r)); }
+    ctx->rank = rank; ctx->world = world;
+    ctx->logw = 0;
+    while ((1 << ctx->logw) < world) ctx->logw++;
+    ctx->begun = false;
+    return SC_OK;
+}

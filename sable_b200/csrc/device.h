@@ -1,0 +1,113 @@
+// device.h -- the structures handed to the kernels and the launchers the context calls.
+#pragma once
+#include <cuda_runtime.h>
+#include <cstdint>
+
+#include "../../include/sumcheck_b200.h"
+#include "field.cuh"
+
+namespace sc {
+
+using scf::u32;
+using scf::u64;
+
+enum CoeffKind : uint8_t { CK_ONE = 0, CK_BASE = 1, CK_EXT = 2 };
+
+// One term of the statement: coefficient times a product of tables.  The coefficient is in
+// Montgomery form; a term without factors is the constant term of the statement.
+struct DevTerm {
+    u32 coeff[8];
+    uint8_t ckind;
+    uint8_t nf;
+    uint8_t f[SC_MAX_FACTORS];
+    uint8_t pad[2];
+};
+struct DevStatement {
+    int nterms;
+    DevTerm terms[SC_MAX_TERMS];
+};
+
+constexpr int ROUND_THREADS = 256;
+constexpr int MAX_PARTIAL_WORDS = SC_MAX_POINTS * 8;   // points * D words per partial sum
+
+// Everything one round kernel needs.  The kernel reads the current tables (entries 2i, 2i+1 of
+// each for pair i; with FOLD entries 4i..4i+3, folded by r on the way in and written to dst),
+// evaluates the statement at X = 0, 2, .., points on the line through each pair, weights the
+// values by low[l] high[h] for i = h 2^logL + l, and sums over all pairs.
+struct RoundArgs {
+    const u32 *src[SC_MAX_TABLES];
+    u32 *dst[SC_MAX_TABLES];
+    uint8_t src_base[SC_MAX_TABLES];   // 1: the source holds base-field entries (one word each)
+    int ntables;          // tables read (and folded); the statement may use fewer
+    int raw;              // 1: source words are canonical residues (the caller's tables), else Montgomery form
+    u32 r[8];             // the fold challenge: r R when the source is in Montgomery form, r R^2 when raw
+    u64 npairs;           // pairs to sum, over all blocks
+    int logL;             // pairs per high weight: 2^logL
+    int use_low;          // 0: every low weight is 1 (and logL is 0 or there is no eq)
+    int use_high;         // 0: every high weight is 1
+    const u32 *low;       // 2^logL multipliers (ExtM layout: D words, then their D triples), Montgomery form
+    const u32 *high;      // npairs >> logL elements, Montgomery form
+    DevStatement st;
+    u32 post[8];          // the sums are multiplied by this element at the end (Montgomery form) ...
+    int use_post;         // ... when this is 1
+    u32 *partials;        // gridDim.x rows of points * D words
+    unsigned int *counter;// blocks that have written their partial; the last one finishes and resets it
+    u32 *out_dev;         // points * D canonical words
+    u32 *out_host;        // the same, in mapped host memory (may be NULL)
+};
+
+// Launchers (defined next to their kernels).  Each returns the CUDA error of the launch.
+cudaError_t launch_round(int D, int points, int nt_used, bool fold, const RoundArgs &args, int grid, size_t smem,
+                         cudaStream_t stream);
+bool round_supported(int D, int points, int nt_used);
+
+// Stand-alone fold of NTABLES tables: dst entry i = src[2i] + r (src[2i+1] - src[2i]).
+struct FoldArgs {
+    const u32 *src[SC_MAX_TABLES];
+    u32 *dst[SC_MAX_TABLES];
+    uint8_t src_base[SC_MAX_TABLES];
+    int ntables;
+    int raw;
+    u32 r[8];
+    u64 nout;     // entries written per table
+};
+cudaError_t launch_fold(int D, const FoldArgs &args, cudaStream_t stream);
+
+// Montgomery form (or raw, lifted) entries to canonical extension elements: count entries per table.
+struct ExportArgs {
+    const u32 *src[SC_MAX_TABLES];
+    uint8_t src_base[SC_MAX_TABLES];
+    int ntables;
+    int raw;
+    u64 count;
+    u32 *out;     // ntables * count * D words
+};
+cudaError_t launch_export(int D, const ExportArgs &args, cudaStream_t stream);
+
+// Seeded table generator (canonical residues).
+cudaError_t launch_generate(u32 *out, u64 seed, int table_id, u64 first, u64 entries, int stride, int nonzero,
+                            cudaStream_t stream);
+// In-place reduction of words >= p (inputs are reduced as COERCE-EXT does).
+cudaError_t launch_reduce_words(u32 *words, u64 count, cudaStream_t stream);
+
+// The eq weight tables of every round.  CHUNKS holds, for every start s < n and width w = 1..8,
+// eq(r[s .. s+w)) as 2^w elements at element offset s * 512 + 2^w (Montgomery form); each
+// descriptor names a table entry x -> product over 8-bit chunks of x, times an optional block
+// weight, written as Ext (kind 0) or as a multiplier with triples (kind 1).
+struct WeightDesc {
+    u64 out_word;     // word offset of the table in the weights buffer
+    u64 entries;      // entries per block
+    int start;        // first eq variable
+    int bits;         // variables covered: entries = 2^bits
+    int kind;         // 0: Ext, 1: ExtM
+    int blocks;       // > 0: the table has blocks * entries elements, element (b, x) times bw[b]
+};
+cudaError_t launch_eq_chunks(int D, const u32 *r_mont, int n, u32 *chunks, cudaStream_t stream);
+cudaError_t launch_weight_tables(int D, const u32 *chunks, const WeightDesc *descs, int ndescs, const u32 *bw_mont,
+                                 u32 *weights, u64 total_entries, cudaStream_t stream);
+
+// out[k] = sum over ranks of gathered[rank * words + k] mod p, to device and mapped host memory.
+cudaError_t launch_sum_ranks(const u32 *gathered, int world, int words, u32 *out_dev, u32 *out_host,
+                             cudaStream_t stream);
+
+}  // namespace sc

@@ -1,0 +1,266 @@
+"""Parity of the CUDA prover with the oracle and with the reference's sumcheck vectors.
+
+Every case calls the device through the C ABI (sable_b200.prove -> sc_prove -> sc_round ...) and
+compares challenges, finals, folded tables and proof bytes bit for bit.  The cases follow the
+reference's own prover tests (tests/tests.lisp:264-395): the Python-written vectors, base tables
+against their lift, statements with constants, powers and constant terms, with and without eq.
+"""
+import numpy as np
+import pytest
+
+import sable_b200 as sb
+from oracle import pyoracle as orc
+
+pytestmark = pytest.mark.gpu
+P = sb.P
+
+
+@pytest.fixture(scope="module")
+def prover():
+    p = sb.Prover(0)
+    yield p
+    p.close()
+
+
+def rand_ext(rng, d, count=None):
+    if count is None:
+        return rng.integers(0, P, size=d, dtype=np.uint32)
+    return rng.integers(0, P, size=(count, d), dtype=np.uint32)
+
+
+def both(prover, d, n, statement, tables, eq=None, constants=(), label="sc", block_weights=None, degree=None, tr_label="par",
+         threads=1):
+    """Run the device prover and the oracle on the same inputs; return both results."""
+    ta, tb = sb.Transcript(tr_label, d), orc.Transcript(tr_label, d)
+    got = sb.prove(ta, n, statement, tables, eq=eq, constants=constants, label=label, block_weights=block_weights,
+                   degree=degree, prover=prover)
+    want = orc.prove(tb, n, statement, tables, eq=eq, constants=list(constants), label=label, block_weights=block_weights,
+                     degree=degree, threads=threads)
+    return got, want, ta, tb
+
+
+def assert_same(got, want, ta, tb):
+    assert got[0] == want[0], "challenges"
+    assert got[1] == want[1], "finals"
+    assert got[2] == want[2], "folded tables"
+    assert ta.proof() == tb.proof(), "proof bytes"
+    assert ta.digest(32) == tb.digest(32), "transcript state"
+    assert ta.sent_bytes == tb.sent_bytes()
+
+
+def test_reference_vectors_through_the_device(golden, prover):
+    # reference tests/tests.lisp:264-282: the same challenges, finals and bytes as the Python prover
+    for v in golden["sumcheck"]:
+        d, n = v["d"], v["n"]
+        tables = [("t%d" % i, np.array(t, dtype=np.uint32)) for i, t in enumerate(v["tables"])]
+        statement = "(* %s)" % " ".join(name for name, _ in tables)
+        tr = sb.Transcript("sc-vec", d)
+        rho, finals, _ = sb.prove(tr, n, statement, tables, eq=v["eq-r"], prover=prover)
+        assert rho == v["rho"]
+        assert [finals[name] for name, _ in tables] == v["finals"]
+        assert tr.proof(b"SABLEPF1").hex() == v["proof"]
+
+
+STATEMENTS = [
+    # statement, tables, constants
+    ("(* t0 t1)", 2, 0),
+    ("(* t0 t1 t2)", 3, 0),
+    ("(* t0 t1 t2 t3)", 4, 0),
+    ("t0", 1, 0),
+    ("(+ (* t0 t1 t2) (* 7 t1) -1)", 3, 0),
+    ("(- (expt t0 3) (* t0 t1))", 2, 0),
+    ("(+ (* alpha t0 t1) (* 3 t1))", 2, 1),
+    ("(+ (* alpha t0 t1) (* 3 t1) -2)", 2, 1),
+    ("(- (* alpha (expt t0 2) t1) t1)", 2, 1),
+    ("(+ (* t0 t3) (* t1 t2) (* alpha t2 t3))", 4, 1),
+    ("(* (+ t0 alpha) (- t1 beta))", 2, 2),
+]
+
+
+@pytest.mark.parametrize("d", [4, 8])
+@pytest.mark.parametrize("kinds", ["base", "ext", "mixed"])
+def test_statements_against_the_oracle(prover, d, kinds):
+    rng = np.random.default_rng(100 * d + len(kinds))
+    for statement, nt, nc in STATEMENTS:
+        for n in (1, 2, 5, 9):
+            for with_eq in (True, False):
+                tables = []
+                for t in range(nt):
+                    base = kinds == "base" or (kinds == "mixed" and t % 2 == 0)
+                    tables.append(("t%d" % t, rng.integers(0, P, size=1 << n, dtype=np.uint32) if base else rand_ext(rng, d, 1 << n)))
+                constants = [(name, rand_ext(rng, d).tolist()) for name in ("alpha", "beta")[:nc]]
+                eq = rand_ext(rng, d, n) if with_eq else None
+                got, want, ta, tb = both(prover, d, n, statement, tables, eq=eq, constants=constants)
+                try:
+                    assert_same(got, want, ta, tb)
+                except AssertionError as e:
+                    raise AssertionError("%s n=%d D=%d %s eq=%s: %s" % (statement, n, d, kinds, with_eq, e))
+
+
+@pytest.mark.parametrize("d", [4, 8])
+def test_base_tables_equal_their_lift(prover, d):
+    # reference tests/tests.lisp:329-346
+    rng = np.random.default_rng(d)
+    n, statement = 4, "(+ (* t0 t1 t2) (* 7 t1))"
+    base = [("t%d" % i, rng.integers(0, P, size=1 << n, dtype=np.uint32)) for i in range(3)]
+    lifted = [(name, np.concatenate([a[:, None], np.zeros((1 << n, d - 1), dtype=np.uint32)], axis=1)) for name, a in base]
+    eq = rand_ext(rng, d, n)
+    out = []
+    for tables in (base, lifted):
+        tr = sb.Transcript("base", d)
+        rho, finals, folded = sb.prove(tr, n, statement, tables, eq=eq, prover=prover)
+        out.append((rho, finals, folded, tr.proof()))
+    assert out[0] == out[1]
+
+
+def test_proof_is_accepted_by_the_verifier(prover):
+    # reference tests/tests.lisp:311-327: a constant beside the tables, no eq; verify + check-final accept
+    d, n = 4, 3
+    rng = np.random.default_rng(3)
+    statement = "(+ (* alpha t0 t1) (* 3 t1) -2)"
+    constants = [("alpha", rand_ext(rng, d).tolist())]
+    tables = [("t0", rand_ext(rng, d, 1 << n)), ("t1", rand_ext(rng, d, 1 << n))]
+    claim = orc.hypercube_sum(d, n, statement, tables, constants=constants)
+    tr = sb.Transcript("any", d)
+    rho, finals, _ = sb.prove(tr, n, statement, tables, constants=constants, prover=prover)
+    vrho, reduced = orc.verify("any", d, n, 2, claim, tr.messages)
+    assert vrho == rho
+    assert orc.check_final(d, statement, list(finals.items()), reduced, constants=constants)
+
+
+@pytest.mark.parametrize("d", [4, 8])
+def test_zero_rounds_and_degree_override(prover, d):
+    rng = np.random.default_rng(7)
+    # n = 0 with degree 0 in the header, as the GKR caller does (reference src/gkr.lisp:236-238)
+    tables = [("a", rand_ext(rng, d, 1)), ("b", rng.integers(0, P, size=1, dtype=np.uint32))]
+    got, want, ta, tb = both(prover, d, 0, "(* a b)", tables, degree=0, label="gkr-top")
+    assert_same(got, want, ta, tb)
+    assert got[0] == [] and got[1]["b"] == [int(tables[1][1][0])] + [0] * (d - 1)
+    # a header degree above the statement's: more points per round
+    tables = [("a", rand_ext(rng, d, 16)), ("b", rand_ext(rng, d, 16))]
+    got, want, ta, tb = both(prover, d, 4, "(* a b)", tables, eq=rand_ext(rng, d, 4), degree=3)
+    assert_same(got, want, ta, tb)
+    assert ta.messages[0].shape == (3, d)
+
+
+@pytest.mark.parametrize("d", [4, 8])
+def test_block_weights(prover, d):
+    # K blocks, block-major, K not a power of two (reference src/sumcheck.lisp:519-525, src/gkr.lisp:253-255)
+    rng = np.random.default_rng(11 + d)
+    for K, n in ((3, 3), (5, 1), (1, 4), (6, 6)):
+        for with_eq in (True, False):
+            bw = rand_ext(rng, d, K)
+            tables = [("a", rand_ext(rng, d, K << n)), ("b", rng.integers(0, P, size=K << n, dtype=np.uint32)),
+                      ("c", rand_ext(rng, d, K << n))]
+            eq = rand_ext(rng, d, n) if with_eq else None
+            got, want, ta, tb = both(prover, d, n, "(+ (* a b) (* lam b c))", tables, eq=eq,
+                                     constants=[("lam", rand_ext(rng, d).tolist())], block_weights=bw, label="gkr")
+            assert_same(got, want, ta, tb)
+            assert len(got[2]["a"]) == K
+
+
+def test_tables_outside_the_statement_are_folded_too(prover):
+    # reference src/sumcheck.lisp:528,562-571: every table passed is folded and returned
+    d, n = 4, 5
+    rng = np.random.default_rng(21)
+    tables = [("u", rand_ext(rng, d, 1 << n)), ("t0", rand_ext(rng, d, 1 << n)), ("v", rng.integers(0, P, size=1 << n, dtype=np.uint32)),
+              ("t1", rng.integers(0, P, size=1 << n, dtype=np.uint32))]
+    got, want, ta, tb = both(prover, d, n, "(* t0 t1)", tables, eq=rand_ext(rng, d, n))
+    assert_same(got, want, ta, tb)
+    for name, values in tables:
+        assert got[1][name] == orc.mle_eval(d, values, got[0])
+
+
+def test_inputs_not_below_p_are_reduced(prover):
+    # COERCE-EXT reduces its input (reference src/field.lisp:115-117)
+    d, n = 4, 4
+    rng = np.random.default_rng(31)
+    big = [("t0", rng.integers(0, 2 ** 32, size=1 << n, dtype=np.uint32)), ("t1", rng.integers(0, 2 ** 32, size=(1 << n, d), dtype=np.uint32))]
+    small = [(nm, a % P) for nm, a in big]
+    eq = rand_ext(rng, d, n)
+    out = []
+    for tables in (big, small):
+        tr = sb.Transcript("red", d)
+        out.append((sb.prove(tr, n, "(* t0 t1)", tables, eq=eq, prover=prover), tr.proof()))
+    assert out[0] == out[1]
+
+
+@pytest.mark.parametrize("d,n,statement,nt", [(4, 21, "(* t0 t1 t2)", 3), (8, 21, "(* t0 t1)", 2), (4, 23, "(* t0 t1)", 2)])
+def test_split_weights_at_size(prover, d, n, statement, nt):
+    # large enough for the low/high split of the eq weights (and for several blocks per SM)
+    rng = np.random.default_rng(n + d)
+    tables = [("t%d" % t, rng.integers(0, P, size=1 << n, dtype=np.uint32)) for t in range(nt)]
+    got, want, ta, tb = both(prover, d, n, statement, tables, eq=rand_ext(rng, d, n), threads=0)
+    assert_same(got, want, ta, tb)
+
+
+def test_mixed_tables_at_size(prover):
+    # the shape of a LogUp-GKR layer: base and extension tables, an extension constant
+    d, n = 4, 20
+    rng = np.random.default_rng(77)
+    tables = [("t0", rng.integers(0, P, size=1 << n, dtype=np.uint32)), ("t1", rng.integers(0, P, size=1 << n, dtype=np.uint32)),
+              ("t2", rand_ext(rng, d, 1 << n)), ("t3", rand_ext(rng, d, 1 << n))]
+    got, want, ta, tb = both(prover, d, n, "(+ (* t0 t3) (* t1 t2) (* lam t2 t3))", tables, eq=rand_ext(rng, d, n),
+                             constants=[("lam", rand_ext(rng, d).tolist())], threads=0)
+    assert_same(got, want, ta, tb)
+
+
+def test_every_folded_table_matches(prover):
+    # round by round through the device layer: each message and each folded table against the oracle
+    d, n = 4, 6
+    rng = np.random.default_rng(55)
+    tabs = [rng.integers(0, P, size=1 << n, dtype=np.uint32), rand_ext(rng, d, 1 << n)]
+    eq = rand_ext(rng, d, n)
+    degree, terms = sb.lower_statement("(* a b)", d, ["a", "b"])
+    prover.set_statement(d, max(degree, 1), 2, terms)
+    for s, t in enumerate(tabs):
+        prover.upload_table(s, t)
+    prover.begin(n, eq=eq)
+    cur = [np.concatenate([tabs[0][:, None], np.zeros((1 << n, d - 1), dtype=np.uint32)], axis=1), tabs[1]]
+    tr = orc.Transcript("x", d)
+    for j in range(n):
+        sums = prover.round()
+        # the oracle's round j is the first round of a proof over the current tables
+        t2 = orc.Transcript("y", d)
+        orc.prove(t2, n - j, "(* a b)", [("a", cur[0]), ("b", cur[1])], eq=eq[j:])
+        assert sums.tolist() == t2.messages()[0].tolist(), "round %d" % j
+        tr.send(sums)
+        r = tr.challenge()
+        prover.challenge(r)
+        cur = [np.array([orc.ext_add(d, t[2 * i], orc.ext_mul(d, r, orc.ext_sub(d, t[2 * i + 1], t[2 * i]))) for i in range(len(t) // 2)],
+                        dtype=np.uint32) for t in cur]
+    out = prover.finish(2)
+    assert out[:, 0, :].tolist() == [c[0].tolist() for c in cur]
+
+
+def test_calls_out_of_order_and_bad_sizes(prover):
+    d = 4
+    degree, terms = sb.lower_statement("(* a b)", d, ["a", "b"])
+    prover.set_statement(d, 2, 2, terms)
+    prover.upload_table(0, np.zeros(8, dtype=np.uint32))
+    prover.upload_table(1, np.zeros(4, dtype=np.uint32))
+    with pytest.raises(sb.InvalidParameter):     # sizes disagree with n
+        prover.begin(3)
+    prover.upload_table(1, np.zeros(8, dtype=np.uint32))
+    prover.begin(3)
+    with pytest.raises(sb.SumcheckError):        # challenge before the round
+        prover.challenge([1, 2, 3, 4])
+    prover.round()
+    with pytest.raises(sb.SumcheckError):        # second round without a challenge
+        prover.round()
+    with pytest.raises(sb.SumcheckError):        # finish before the last round
+        prover.finish(2)
+    with pytest.raises(sb.SumcheckError):        # more tables than any kernel takes in one statement
+        sb.lower_statement("(* a b c d e)", d, list("abcde"))
+        prover.set_statement(d, 5, 5, [([1, 0, 0, 0], [0, 1, 2, 3, 4])])
+
+
+def test_memory_budget_is_enforced_on_the_host(prover):
+    p = sb.Prover(0)
+    try:
+        p.set_memory_budget(1 << 20)
+        with pytest.raises(sb.SumcheckError) as e:
+            p.upload_table(0, np.zeros(1 << 20, dtype=np.uint32))
+        assert e.value.code == -3
+    finally:
+        p.close()

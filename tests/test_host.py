@@ -1,0 +1,153 @@
+"""The host side of the library, without a GPU: the C ABI loads and exports what the header
+declares, and the transcript, the statement compiler and the proof bytes agree with the
+reference's vectors (tests/golden/vectors.json) and with the oracle."""
+import ctypes
+import os
+import re
+
+import numpy as np
+import pytest
+
+import sable_b200 as sb
+from oracle import pyoracle as orc
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+P = sb.P
+
+
+def test_library_exports_every_declared_symbol():
+    header = open(os.path.join(ROOT, "include", "sumcheck_b200.h")).read()
+    declared = set(re.findall(r"\b(sc_[a-z0-9_]+)\s*\(", header))
+    assert declared == set(sb.SYMBOLS)
+    lib = sb.library()
+    for name in sorted(declared):
+        assert getattr(lib, name) is not None, name
+
+
+def test_error_texts():
+    lib = sb.library()
+    assert lib.sc_strerror(0) == b"ok"
+    for code in range(-7, 0):
+        assert lib.sc_strerror(code) not in (b"ok", b"unknown error")
+    assert lib.sc_strerror(-99) == b"unknown error"
+
+
+def test_bad_extension_degree_is_rejected():
+    # reference tests/tests.lisp:92: (make-transcript "x" 5) signals INVALID-PARAMETER
+    with pytest.raises(sb.InvalidParameter):
+        sb.Transcript("x", 5)
+
+
+def test_transcript_vector(golden):
+    for v in golden["transcript"]:
+        tr = sb.Transcript(bytes.fromhex(v["label"]), 8)
+        for op in v["ops"]:
+            kind = op[0]
+            if kind == "absorb":
+                tr.absorb(bytes.fromhex(op[1]))
+            elif kind == "absorb-ext":
+                tr.absorb(b"".join(int(x).to_bytes(4, "little") for x in op[1]))
+            elif kind == "challenge-base":
+                assert tr.challenge_base(op[1]) == op[2]
+            elif kind == "challenge":
+                assert tr.challenge(op[1]) == op[2]
+            elif kind == "challenge-bits":
+                assert tr.challenge_bits(op[1], op[2]) == op[3]
+            elif kind == "digest":
+                assert tr.digest(32).hex() == op[1]
+
+
+def test_transcript_matches_oracle_on_random_traffic():
+    rng = np.random.default_rng(5)
+    for d in (4, 8):
+        a, b = sb.Transcript("t", d), orc.Transcript("t", d)
+        for step in range(40):
+            if step % 3 == 0:
+                data = rng.integers(0, 256, size=int(rng.integers(0, 200)), dtype=np.uint8).tobytes()
+                a.absorb(data); b.absorb(data)
+            elif step % 3 == 1:
+                m = rng.integers(0, P, size=(int(rng.integers(1, 5)), d), dtype=np.uint32)
+                a.send(m); b.send(m)
+            else:
+                assert a.challenge() == b.challenge()
+        assert a.digest(64) == b.digest(64)
+        assert a.proof() == b.proof()
+        assert a.sent_bytes == b.sent_bytes()
+
+
+def test_proof_bytes_of_the_sumcheck_vectors(golden):
+    # replaying a vector's round messages through SEND reproduces its proof bytes and challenges
+    for v in golden["sumcheck"]:
+        d, n, k = v["d"], v["n"], len(v["tables"])
+        raw = bytes.fromhex(v["proof"])
+        words = np.frombuffer(raw[12:], dtype=np.uint8)
+        tr = sb.Transcript("sc-vec", d)
+        tr.absorb(b"sc|" + n.to_bytes(2, "little") + k.to_bytes(2, "little") + (1).to_bytes(4, "little"))
+        pos, rho = 0, []
+        for _ in range(n):
+            pos += 18
+            m = np.frombuffer(words[pos:pos + 4 * k * d].tobytes(), dtype="<u4").reshape(k, d)
+            pos += 4 * k * d
+            tr.send(m)
+            rho.append(tr.challenge())
+        assert rho == v["rho"]
+        assert tr.proof(b"SABLEPF1") == raw
+
+
+def test_send_rejects_values_not_below_p():
+    tr = sb.Transcript("x", 4)
+    with pytest.raises(sb.InvalidParameter):
+        tr.send(np.array([[P, 0, 0, 0]], dtype=np.uint32))
+
+
+def test_lowering_matches_the_poly_vector(golden):
+    v = golden["poly"][0]
+    form = "(- (+ (* (+ c0 3) (- c1 c0) c2) 7) (expt c0 2))"  # reference tests/tests.lisp:107
+    degree, terms = sb.lower_statement(form, 4, ["c0", "c1", "c2"])
+    assert degree == v["degree"]
+    assert sorted([idx, c[0]] for c, idx in terms) == sorted(v["terms"])
+    assert all(c[1:] == [0, 0, 0] for c, _ in terms)
+
+
+def test_lowering_folds_constants_into_coefficients():
+    rng = np.random.default_rng(1)
+    alpha = rng.integers(0, P, size=4, dtype=np.uint32).tolist()
+    degree, terms = sb.lower_statement("(+ (* alpha t0 t1) (* 3 t1) -2)", 4, ["t0", "t1"], [("alpha", alpha)])
+    assert degree == 2
+    assert sorted(terms, key=lambda t: t[1]) == [([P - 2, 0, 0, 0], []), ([alpha[0], alpha[1], alpha[2], alpha[3]], [0, 1]),
+                                                ([3, 0, 0, 0], [1])]
+    # powers repeat the table; a product of constants is one coefficient
+    beta = rng.integers(0, P, size=4, dtype=np.uint32).tolist()
+    degree, terms = sb.lower_statement("(- (* alpha beta (expt t0 2) t1) t1)", 4, ["t0", "t1"], [("alpha", alpha), ("beta", beta)])
+    assert degree == 3
+    ab = orc.ext_mul(4, alpha, beta)
+    assert sorted(terms, key=lambda t: len(t[1])) == [([P - 1, 0, 0, 0], [1]), (ab, [0, 0, 1])]
+    # terms that cancel disappear, but the degree is that of the form
+    degree, terms = sb.lower_statement("(- (* 2 t0) t0 t0)", 4, ["t0"])
+    assert (degree, terms) == (0, [])
+
+
+def test_lowering_agrees_with_the_oracle_degree():
+    cases = ["(* t0 t1 t2)", "(+ (* t0 t1 t2) (* 7 t1) -1)", "t0", "(- (expt t0 3) (* t0 t1))", "(* t0 t1 t2 t3)",
+             "(+ (* t0 t3) (* t1 t2) (* lam t2 t3))", "(* (+ t0 1) (- t1 lam))"]
+    for form in cases:
+        tables = [t for t in ("t0", "t1", "t2", "t3") if t in form]
+        consts = [("lam", [5, 6, 7, 8])] if "lam" in form else []
+        degree, _ = sb.lower_statement(form, 4, tables, consts)
+        assert degree == orc.statement_degree(form, tables, [c[0] for c in consts])
+
+
+def test_bad_statements_are_rejected():
+    for form in ["(/ a b)", "(* a", "(expt a -1)", "(* a b) c", ""]:
+        with pytest.raises(sb.InvalidParameter):
+            sb.lower_statement(form, 4, ["a", "b", "c"])
+    with pytest.raises(sb.InvalidParameter):   # a free variable (reference tests/tests.lisp:139)
+        sb.lower_statement("(* a b)", 4, ["a"])
+
+
+def test_no_device_means_an_error_not_a_fallback():
+    import torch
+    if torch.cuda.is_available():
+        pytest.skip("a CUDA device is present")
+    with pytest.raises(sb.SumcheckError):
+        sb.Prover(0)
