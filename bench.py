@@ -1,0 +1,302 @@
+#!/usr/bin/env python3
+"""Benchmark of the sumcheck prover: Mentries/s of a whole proof, with the HBM roofline of its round kernel.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--config C4] [--degree 4] [--impl reference]
+
+One step is one whole proof (every round, host transcript included) of a BASELINE workload on
+seeded synthetic tables: value = 2^n / (time per proof) / 10^6, the tables resident in HBM when
+the clock starts.  `e2e` is the same proof through the public call with the tables in pinned host
+memory, uploaded inside the timed region.  `roofline` is the fused round kernel's algorithmic
+bytes over its measured launch time against the measured HBM copy bandwidth.  `cpu_baseline` is
+the CPU oracle (a port of the reference prover) on the box's host cores, on a bounded sample.
+
+With N > 1 (one process per GPU under torch.distributed.run) the hypercube of the same n is cut
+on its top log2(N) variables: total work is fixed, so the scaling is strong.
+
+`--impl reference` times the CPU port alone, with all host threads, on a bounded sample.
+"""
+import argparse
+import json
+import os
+import statistics
+import subprocess
+import sys
+import threading
+import time
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, ROOT)
+
+P = 2130706433
+MASK = (1 << 64) - 1
+
+# BASELINE.json configs: statement, n, tables (name, stride: 1 base, 0 extension, nonzero), constants
+CONFIGS = {
+    "C1": dict(n=20, statement="(* t0 t1)", tables=[("t0", 1, False), ("t1", 1, False)], constants=[]),
+    "C2": dict(n=24, statement="(* t0 t1 t2)", tables=[("t0", 1, False), ("t1", 1, False), ("t2", 1, False)], constants=[]),
+    "C3": dict(n=26, statement="(+ (* alpha t0 t1) (* 3 t1))", tables=[("t0", 1, False), ("t1", 1, False)], constants=["alpha"]),
+    "C4": dict(n=28, statement="(+ (* t0 t3) (* t1 t2) (* lam t2 t3))",
+               tables=[("t0", 1, False), ("t1", 1, False), ("t2", 0, True), ("t3", 0, True)], constants=["lam"]),
+    "C5": dict(n=30, statement="(* t0 t1 t2)", tables=[("t0", 1, False), ("t1", 1, False), ("t2", 1, False)], constants=[]),
+}
+SEED = 1
+EQ_ID, CONST_ID = 255, 254
+
+
+def splitmix64(x):
+    x = (x + 0x9E3779B97F4A7C15) & MASK
+    x = ((x ^ (x >> 30)) * 0xBF58476D1CE4E5B9) & MASK
+    x = ((x ^ (x >> 27)) * 0x94D049BB133111EB) & MASK
+    return x ^ (x >> 31)
+
+
+def seeded_ext(table_id, index, D):
+    return [splitmix64(SEED ^ (table_id << 56) ^ (c << 48) ^ index) % P for c in range(D)]
+
+
+def algorithmic_bytes(cfg, n, D):
+    """Whole-proof bytes: the inputs read twice (round 0, then the first fold) and every folded table written and read once."""
+    total = 0
+    sizes = [4 * (1 if stride == 1 else D) << n for _, stride, _ in cfg["tables"]]
+    total += sum(sizes)                      # round 0 reads T_0
+    prev = sizes
+    for j in range(1, n + 1):                # the kernel of round j reads T_{j-1} and writes T_j (the last fold: j = n)
+        cur = [4 * D << (n - j) for _ in sizes]
+        total += sum(prev) + sum(cur)
+        prev = cur
+    return total
+
+
+class ClockSampler:
+    """nvidia-smi clocks and throttle reasons every 200 ms while the timed region runs."""
+    FIELDS = "index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown," \
+             "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap"
+
+    def __init__(self, index):
+        self.index, self.rows, self.proc = index, [], None
+
+    def start(self):
+        try:
+            self.proc = subprocess.Popen(["nvidia-smi", "--query-gpu=" + self.FIELDS, "--format=csv,noheader,nounits", "-lms", "200"],
+                                         stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+            threading.Thread(target=self._read, daemon=True).start()
+        except OSError:
+            self.proc = None
+
+    def _read(self):
+        for line in self.proc.stdout:
+            parts = [p.strip() for p in line.split(",")]
+            if len(parts) >= 8 and parts[0] == str(self.index):
+                self.rows.append(parts)
+
+    def stop(self):
+        if self.proc:
+            self.proc.terminate()
+            try:
+                self.proc.wait(timeout=2)
+            except subprocess.TimeoutExpired:
+                self.proc.kill()
+        sm = [float(r[1]) for r in self.rows if r[1].replace(".", "").isdigit()]
+        reasons = set()
+        for r in self.rows:
+            for name, v in zip(("hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"), r[4:8]):
+                if v.lower() == "active":
+                    reasons.add(name)
+        return {"sm_mhz": statistics.median(sm) if sm else None, "sm_max_mhz": float(self.rows[0][2]) if self.rows else None,
+                "samples": len(sm), "reasons": sorted(reasons)}
+
+
+def measured_peak():
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(path):
+        return float(json.load(open(path))["hbm_gbs"]), "measured"
+    return 6650.0, "fallback"
+
+
+def cpu_port(cfg, D, n_sample, steps, warmup, threads=0):
+    """The CPU oracle (a port of the reference prover) on a bounded sample of the workload: Mentries/s."""
+    from oracle import pyoracle as orc
+    tables = [(name, orc.generate(SEED, t, 0, 1 << n_sample, 1 if stride == 1 else D, nonzero=nz)) for t, (name, stride, nz) in enumerate(cfg["tables"])]
+    eq = [seeded_ext(EQ_ID, i, D) for i in range(n_sample)]
+    constants = [(c, seeded_ext(CONST_ID, i, D)) for i, c in enumerate(cfg["constants"])]
+    cores = orc.max_threads() if threads == 0 else threads
+    times = []
+    for step in range(warmup + steps):
+        tr = orc.Transcript("bench", D)
+        t0 = time.perf_counter()
+        orc.prove(tr, n_sample, cfg["statement"], tables, eq=eq, constants=constants, threads=cores)
+        dt = time.perf_counter() - t0
+        if step >= warmup:
+            times.append(dt)
+    mean = sum(times) / len(times)
+    return (1 << n_sample) / mean / 1e6, mean, cores, tr.proof()
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=5)
+    ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--config", default="C4", choices=sorted(CONFIGS))
+    ap.add_argument("--degree", type=int, default=4, choices=(4, 8))
+    ap.add_argument("--n", type=int, default=None, help="override the config's n (smaller runs)")
+    ap.add_argument("--impl", default="sable", choices=("sable", "reference"))
+    ap.add_argument("--cpu-n", type=int, default=24, help="n of the CPU sample")
+    ap.add_argument("--no-e2e", action="store_true")
+    ap.add_argument("--no-cpu", action="store_true")
+    args = ap.parse_args()
+
+    rank = int(os.environ.get("RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    cfg = CONFIGS[args.config]
+    D = args.degree
+    n = args.n if args.n is not None else cfg["n"]
+    workload = "%s: %s, n=%d, D=%d, eq mode, %s" % (args.config, cfg["statement"], n, D,
+                                                      ", ".join("%s %s" % (nm, "base" if s == 1 else "ext") for nm, s, _ in cfg["tables"]))
+    metric = "sumcheck prove Mentries/s"
+
+    if args.impl == "reference":
+        if rank != 0:
+            return
+        n_sample = min(n, args.cpu_n)
+        value, mean, cores, _ = cpu_port(cfg, D, n_sample, max(args.steps, 1), args.warmup)
+        sample = "the same statement at n=%d (one whole proof per step), all host threads" % n_sample
+        print(json.dumps({
+            "impl": "reference", "metric": metric, "value": value, "unit": "Mentries/s", "n_gpus": args.gpus, "steps": args.steps,
+            "warmup": args.warmup, "ms_per_step": mean * 1e3, "higher_is_better": True, "scaling": "strong", "vs_baseline": None,
+            "dtype": "u32", "data": "synthetic",
+            "config": {"workload": workload, "sample": sample},
+            "cpu_baseline": {"value": value, "unit": "Mentries/s", "cores": cores, "kind": "port", "sample": sample},
+            "e2e": {"value": value, "unit": "Mentries/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+            "note": "the reference is Common Lisp (SBCL) and no Lisp is installed; this is the C port of its prover, pinned by the reference's own vectors",
+        }))
+        return
+
+    import numpy as np
+    import torch
+    import torch.distributed as dist
+    import sable_b200 as sb
+
+    if world > 1:
+        torch.cuda.set_device(local_rank)
+        dist.init_process_group("cpu:gloo,cuda:nccl", rank=rank, world_size=world)
+    assert world & (world - 1) == 0 and (1 << n) >= world, "the world must be a power of two"
+    logw = world.bit_length() - 1
+    n_loc = n - logw
+    prover = sb.Prover(local_rank)
+    if world > 1:
+        ids = [sb.comm_unique_id() if rank == 0 else None]
+        dist.broadcast_object_list(ids, src=0)
+        prover.comm_init(ids[0], rank, world)
+
+    # the tables of this rank's slice, generated on the device
+    first = rank << n_loc
+    strides = []
+    for slot, (name, stride, nz) in enumerate(cfg["tables"]):
+        st = 1 if stride == 1 else D
+        strides.append(st)
+        prover.generate_table(slot, SEED, slot, 1 << n_loc, st, first=first, nonzero=nz)
+    eq = np.array([seeded_ext(EQ_ID, i, D) for i in range(n)], dtype=np.uint32)
+    constants = [(c, seeded_ext(CONST_ID, i, D)) for i, c in enumerate(cfg["constants"])]
+    resident = [(name, sb.DeviceTable(strides[slot])) for slot, (name, _, _) in enumerate(cfg["tables"])]
+
+    def one_proof(tables):
+        tr = sb.Transcript("bench", D)
+        out = sb.prove(tr, n, cfg["statement"], tables, eq=eq, constants=constants, prover=prover)
+        return tr, out
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    def timed(tables, steps):
+        barrier()
+        launches0 = prover.launches
+        prover.timer_start()
+        t0 = time.perf_counter()
+        for _ in range(steps):
+            tr, out = one_proof(tables)
+        ms = prover.timer_stop()
+        wall = (time.perf_counter() - t0) * 1e3
+        barrier()
+        ms = max(ms, 0.0)
+        if world > 1:
+            t = torch.tensor([ms, wall], dtype=torch.float64, device="cuda")
+            dist.all_reduce(t, op=dist.ReduceOp.MAX)
+            ms, wall = t.tolist()
+        return ms, wall, prover.launches - launches0, tr, out
+
+    for _ in range(args.warmup):
+        one_proof(resident)
+    sampler = ClockSampler(local_rank)
+    if rank == 0:
+        sampler.start()
+    ms, wall, launches, tr, out = timed(resident, args.steps)
+    clocks = sampler.stop() if rank == 0 else None
+    ms_per_step = ms / args.steps
+    value = (1 << n) / (ms_per_step * 1e-3) / 1e6
+    proof_bytes = tr.proof()
+
+    # the round kernels, one by one (a separate pass: the events cost a little)
+    prover.enable_timing(True)
+    one_proof(resident)
+    stats = prover.round_stats()
+    prover.enable_timing(False)
+    peak, peak_kind = measured_peak()
+    fused = stats[1:] if len(stats) > 1 else stats
+    fused_bytes = sum(s[1] for s in fused)
+    fused_ms = sum(s[0] for s in fused)
+    achieved = fused_bytes / (fused_ms * 1e-3) / 1e9 if fused_ms > 0 else 0.0
+    rounds = [{"round": j, "ms": round(s[0], 4), "GB/s": round(s[1] / (s[0] * 1e-3) / 1e9, 1)} for j, s in enumerate(stats) if s[1] >= (128 << 20) and s[0] > 0]
+    roofline = {"bound": "hbm", "kernel": "round_kernel<D=%d,points,tables,fold> (rounds 1..n-1: fold by the previous challenge + round sums)" % D,
+                "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak, "peak_kind": peak_kind, "traffic": None,
+                "launches": len(fused), "bytes_per_step": fused_bytes, "ms_per_step": fused_ms, "rounds": rounds,
+                "whole_proof_frac": algorithmic_bytes(cfg, n_loc, D) / (ms_per_step * 1e-3) / 1e9 / peak}
+
+    # end to end: the tables start in pinned host memory and are uploaded inside the timed region
+    e2e = None
+    if not args.no_e2e:
+        host = []
+        for slot, (name, _, _) in enumerate(cfg["tables"]):
+            words = strides[slot] << n_loc
+            t = torch.empty(words, dtype=torch.int32, pin_memory=True)
+            prover.fetch_pointer(slot, t.data_ptr(), words)
+            a = t.numpy().view(np.uint32)
+            host.append((name, a if strides[slot] == 1 else a.reshape(-1, D), t))
+        host_tables = [(nm, a) for nm, a, _ in host]
+        e2e_steps = max(1, min(args.steps, 3))
+        one_proof(host_tables)
+        ems, ewall, _, etr, eout = timed(host_tables, e2e_steps)
+        assert etr.proof() == proof_bytes and eout == out, "the end-to-end proof differs from the resident one"
+        h2d = sum(4 * (strides[s] << n_loc) for s in range(len(strides))) + eq.nbytes + 4 * D * len(constants)
+        d2h = 4 * D * (n * max(len(tr.messages[0]) if n else 1, 1) + len(strides))
+        e2e = {"value": (1 << n) / (ewall / e2e_steps * 1e-3) / 1e6, "unit": "Mentries/s", "h2d_bytes_per_step": h2d * world,
+               "d2h_bytes_per_step": d2h, "steps": e2e_steps, "ms_per_step": ewall / e2e_steps}
+
+    cpu = None
+    if rank == 0 and world == 1 and not args.no_cpu:
+        n_sample = min(n, args.cpu_n)
+        v, mean, cores, cpu_proof = cpu_port(cfg, D, n_sample, 1, 0)
+        cpu = {"value": v, "unit": "Mentries/s", "cores": cores, "kind": "port",
+               "sample": "one proof of the same statement at n=%d on all host threads (%.2f s)" % (n_sample, mean)}
+        if n_sample == n:
+            assert cpu_proof == proof_bytes, "the device proof differs from the CPU port's"
+
+    if rank == 0:
+        print(json.dumps({
+            "metric": metric, "value": value, "unit": "Mentries/s", "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
+            "ms_per_step": ms_per_step, "wall_ms_per_step": wall / args.steps, "higher_is_better": True, "scaling": "strong",
+            "vs_baseline": None, "dtype": "u32", "data": "synthetic",
+            "config": {"workload": workload, "sharding": "top %d variables over %d GPUs" % (logw, world), "transcript": "host (BLAKE3)",
+                       "l2": "inputs larger than L2 (%.1f GiB per rank per proof)" % (sum(4 * (strides[s] << n_loc) for s in range(len(strides))) / 2 ** 30)},
+            "e2e": e2e, "gpu_launches": launches, "clocks": clocks, "roofline": roofline, "cpu_baseline": cpu,
+            "proof_bytes": len(proof_bytes),
+        }))
+    if world > 1:
+        dist.destroy_process_group()
+
+
+if __name__ == "__main__":
+    main()

@@ -119,6 +119,13 @@ int sc_enable_timing(sc_ctx *ctx, int on);
 int sc_round_stats(sc_ctx *ctx, sc_round_stat *stats, int cap, int *count);
 /* Kernels launched by this context since it was created. */
 uint64_t sc_launch_count(const sc_ctx *ctx);
+/* A stopwatch of CUDA events on the context's stream: sc_timer_stop waits for the stream and
+   gives the milliseconds since sc_timer_start. */
+int sc_timer_start(sc_ctx *ctx);
+int sc_timer_stop(sc_ctx *ctx, float *ms);
+/* The caller's words of table SLOT as they lie on the device (WORDS of them), for benchmarks that
+   generate a table on the device and want the same data in host memory. */
+int sc_fetch_table(sc_ctx *ctx, int slot, uint32_t *host, uint64_t words);
 
 /* Several GPUs: the hypercube is cut on its top log2(WORLD) variables, rank RANK holding entries
    [RANK * 2^N / WORLD, (RANK + 1) * 2^N / WORLD) of every table.  Each round's sums are combined

@@ -27,7 +27,7 @@ _u32p = C.POINTER(C.c_uint32)
 SYMBOLS = [
     "sc_create", "sc_destroy", "sc_set_memory_budget", "sc_strerror", "sc_last_error", "sc_set_statement",
     "sc_upload_table", "sc_generate_table", "sc_download_table", "sc_begin", "sc_round", "sc_challenge", "sc_finish",
-    "sc_enable_timing", "sc_round_stats", "sc_launch_count", "sc_comm_unique_id", "sc_comm_init",
+    "sc_enable_timing", "sc_round_stats", "sc_launch_count", "sc_timer_start", "sc_timer_stop", "sc_fetch_table", "sc_comm_unique_id", "sc_comm_init",
     "sc_transcript_new", "sc_transcript_free", "sc_transcript_absorb", "sc_transcript_send",
     "sc_transcript_challenge_base", "sc_transcript_challenge_bits", "sc_transcript_digest",
     "sc_transcript_message_count", "sc_transcript_message", "sc_transcript_sent_bytes", "sc_transcript_encode",
@@ -276,6 +276,18 @@ class Prover:
         stats = (RoundStat * 64)()
         self._call("sc_round_stats", stats, 64, C.byref(count))
         return [(s.kernel_ms, s.bytes, s.pairs) for s in stats[:count.value]]
+
+    def timer_start(self):
+        self._call("sc_timer_start")
+
+    def timer_stop(self):
+        ms = C.c_float(0)
+        self._call("sc_timer_stop", C.byref(ms))
+        return ms.value
+
+    def fetch_pointer(self, slot, address, words):
+        """Copy the caller's words of table ``slot`` from the device to host memory at ``address``."""
+        self._call("sc_fetch_table", slot, C.cast(C.c_void_p(address), _u32p), C.c_uint64(words))
 
     @property
     def launches(self):

@@ -238,6 +238,22 @@ extern "C" int sc_round_stats(sc_ctx *ctx, sc_round_stat *stats, int cap, int *c
     return SC_OK;
 }
 
+extern "C" int sc_timer_start(sc_ctx *ctx) {
+    if (!ctx) return SC_EINVAL;
+    cudaSetDevice(ctx->device);
+    while (ctx->ev.size() < 4) { cudaEvent_t e; CU(cudaEventCreate(&e)); ctx->ev.push_back(e); }
+    CU(cudaEventRecord(ctx->ev[2], ctx->stream));
+    return SC_OK;
+}
+extern "C" int sc_timer_stop(sc_ctx *ctx, float *ms) {
+    if (!ctx || !ms || ctx->ev.size() < 4) return SC_EINVAL;
+    cudaSetDevice(ctx->device);
+    CU(cudaEventRecord(ctx->ev[3], ctx->stream));
+    CU(cudaEventSynchronize(ctx->ev[3]));
+    CU(cudaEventElapsedTime(ms, ctx->ev[2], ctx->ev[3]));
+    return SC_OK;
+}
+
 // ------------------------------------------------------------------ statement
 
 extern "C" int sc_set_statement(sc_ctx *ctx, int D, int points, int ntables, int nterms, const uint32_t *coeffs,
@@ -319,6 +335,16 @@ extern "C" int sc_generate_table(sc_ctx *ctx, int slot, uint64_t seed, int table
     if (rc) return rc;
     CU(launch_generate(ctx->tab[slot].t0, seed, table_id, first, entries, stride, nonzero, ctx->stream));
     ctx->launches++;
+    CU(cudaStreamSynchronize(ctx->stream));
+    return SC_OK;
+}
+
+extern "C" int sc_fetch_table(sc_ctx *ctx, int slot, uint32_t *host, uint64_t words) {
+    if (!ctx || !host || slot < 0 || slot >= SC_MAX_TABLES) return SC_EINVAL;
+    TableState &t = ctx->tab[slot];
+    if (!t.t0 || words > t.entries * (u64)t.stride) return fail(ctx, SC_EINVAL, "table %d holds %llu words", slot, (unsigned long long)(t.entries * (u64)t.stride));
+    cudaSetDevice(ctx->device);
+    CU(cudaMemcpyAsync(host, t.t0, words * 4, cudaMemcpyDeviceToHost, ctx->stream));
     CU(cudaStreamSynchronize(ctx->stream));
     return SC_OK;
 }
