@@ -20,7 +20,7 @@ P = 2130706433                      # the KoalaBear prime 2^31 - 2^24 + 1 (refer
 MAGIC = b"EXACTPF1"                 # reference src/proofio.lisp:18
 
 _HERE = os.path.dirname(os.path.abspath(__file__))
-LIBRARY = os.path.join(_HERE, "libsumcheck_b200.so")
+LIBRARY = os.environ.get("SABLE_B200_LIBRARY", os.path.join(_HERE, "libsumcheck_b200.so"))
 _lib = None
 _u32p = C.POINTER(C.c_uint32)
 

@@ -5,15 +5,15 @@
 
 namespace sc {
 
-cudaError_t launch_round_d4(int points, int nt, bool fold, const RoundArgs &args, int grid, size_t smem, cudaStream_t stream);
-cudaError_t launch_round_d8(int points, int nt, bool fold, const RoundArgs &args, int grid, size_t smem, cudaStream_t stream);
+cudaError_t launch_round_d4(int shape, int points, int nt, bool fold, const RoundArgs &args, int grid, size_t smem, cudaStream_t stream);
+cudaError_t launch_round_d8(int shape, int points, int nt, bool fold, const RoundArgs &args, int grid, size_t smem, cudaStream_t stream);
 
 bool round_supported(int D, int points, int nt_used) {
     return (D == 4 || D == 8) && points >= 1 && points <= SC_MAX_POINTS && nt_used >= 1 && nt_used <= 4;
 }
-cudaError_t launch_round(int D, int points, int nt_used, bool fold, const RoundArgs &args, int grid, size_t smem, cudaStream_t stream) {
-    if (D == 4) return launch_round_d4(points, nt_used, fold, args, grid, smem, stream);
-    if (D == 8) return launch_round_d8(points, nt_used, fold, args, grid, smem, stream);
+cudaError_t launch_round(int D, int shape, int points, int nt_used, bool fold, const RoundArgs &args, int grid, size_t smem, cudaStream_t stream) {
+    if (D == 4) return launch_round_d4(shape, points, nt_used, fold, args, grid, smem, stream);
+    if (D == 8) return launch_round_d8(shape, points, nt_used, fold, args, grid, smem, stream);
     return cudaErrorInvalidValue;
 }
 
@@ -113,12 +113,10 @@ template <int D> __global__ void fold_kernel(const __grid_constant__ FoldArgs a)
                 const u32 s = fsub(w.y, w.x);
 #pragma unroll
                 for (int c = 0; c < D; c++) o.v[c] = mmul(rm.v[c], s);
-                o.v[0] = fadd(o.v[0], a.raw ? to_mont(w.x) : w.x);
+                o.v[0] = fadd(o.v[0], w.x);
             } else {
                 Ext<D> e0 = load_ext<D>(a.src[t] + (2 * i) * D), e1 = load_ext<D>(a.src[t] + (2 * i + 1) * D);
-                Ext<D> p = emul<D>(esub<D>(e1, e0), rm);
-                if (a.raw) e0 = eto_mont<D>(e0);
-                o = eadd<D>(e0, p);
+                o = eadd<D>(e0, emul<D>(esub<D>(e1, e0), rm));
             }
             store_ext<D>(a.dst[t] + i * D, o);
         }
@@ -133,7 +131,7 @@ cudaError_t launch_fold(int D, const FoldArgs &args, cudaStream_t stream) {
     return cudaGetLastError();
 }
 
-// ------------------------------------------------------------------ export: canonical extension elements
+// ------------------------------------------------------------------ export: entries as extension elements
 
 template <int D> __global__ void export_kernel(const __grid_constant__ ExportArgs a) {
     for (u64 i = (u64)blockIdx.x * blockDim.x + threadIdx.x; i < a.count; i += (u64)gridDim.x * blockDim.x) {
@@ -141,7 +139,6 @@ template <int D> __global__ void export_kernel(const __grid_constant__ ExportArg
             Ext<D> e;
             if (a.src_base[t]) e = lift<D>(a.src[t][i]);
             else e = load_ext<D>(a.src[t] + i * D);
-            if (!a.raw) e = efrom_mont<D>(e);
             store_ext<D>(a.out + ((u64)t * a.count + i) * D, e);
         }
     }

@@ -5,6 +5,7 @@
 // the host and D words come back.
 #include <dlfcn.h>
 
+#include <algorithm>
 #include <cstdarg>
 #include <cstdio>
 #include <cstdlib>
@@ -56,12 +57,12 @@ struct TableState {
     u64 t0_cap = 0;             // bytes allocated
     u64 entries = 0;
     int stride = 0;
-    u32 *buf[2] = {nullptr, nullptr};   // ping-pong buffers of the folded table (Montgomery form, D words per entry)
+    u32 *buf[2] = {nullptr, nullptr};   // ping-pong buffers of the folded table (D canonical words per entry)
     u64 buf_cap[2] = {0, 0};
     // the table as the next kernel reads it
     const u32 *cur = nullptr;
     int cur_buf = -1;           // -1: t0 (or the gathered buffer), else buf index
-    bool cur_base = false, cur_raw = false;
+    bool cur_base = false;
     u64 cur_entries = 0;
 };
 
@@ -74,6 +75,7 @@ struct RoundPlan {
 struct sc_ctx {
     int device = 0;
     int sms = 148;
+    int blocks_per_sm = 2;           // round-kernel blocks launched per SM (SABLE_B200_BLOCKS_PER_SM overrides)
     cudaStream_t stream = nullptr;
     std::string last_error;
     u64 budget = 0, used = 0;
@@ -92,8 +94,12 @@ struct sc_ctx {
     int n = 0, K = 1, j = 0;
     int nloc = 0;                    // rounds before the tables are gathered (n - log2 world)
     u32 r[8];
-    u32 post[8];
+    u32 post[8];                     // the final factor of a round: R^e of the statement times this rank's eq weight
     bool use_post = false;
+    int st_e = 0;                    // e of the statement (see DevTerm)
+    int shape = SHAPE_GENERIC;       // the kernel family of the statement
+    u32 st_factor[8];                // a product statement's coefficient (canonical), applied with the final factor
+    bool use_factor = false;
     std::vector<RoundPlan> plan;
 
     // device buffers
@@ -190,6 +196,7 @@ extern "C" int sc_create(int device, sc_ctx **out) {
     if (e == cudaSuccess) e = cudaGetDeviceProperties(&prop, device);
     if (e != cudaSuccess) { delete ctx; return SC_ECUDA; }
     ctx->sms = prop.multiProcessorCount;
+    if (const char *env = getenv("SABLE_B200_BLOCKS_PER_SM")) { int v = atoi(env); if (v >= 1 && v <= 8) ctx->blocks_per_sm = v; }
     ctx->grid_cap = ctx->sms * 8;
     bool ok = cudaMalloc(&ctx->d_partials, (size_t)ctx->grid_cap * MAX_PARTIAL_WORDS * 4) == cudaSuccess &&
               cudaMalloc(&ctx->d_counter, 64) == cudaSuccess && cudaMemset(ctx->d_counter, 0, 64) == cudaSuccess &&
@@ -256,6 +263,23 @@ extern "C" int sc_timer_stop(sc_ctx *ctx, float *ms) {
 
 // ------------------------------------------------------------------ statement
 
+// a b for elements in Montgomery form, on the host
+static void ext_mul_host(int D, const u32 *a, const u32 *b, u32 *o) {
+    if (D == 4) {
+        Ext<4> x, y; for (int c = 0; c < 4; c++) { x.v[c] = a[c]; y.v[c] = b[c]; }
+        Ext<4> z = emul<4>(x, y); for (int c = 0; c < 4; c++) o[c] = z.v[c];
+    } else {
+        Ext<8> x, y; for (int c = 0; c < 8; c++) { x.v[c] = a[c]; y.v[c] = b[c]; }
+        Ext<8> z = emul<8>(x, y); for (int c = 0; c < 8; c++) o[c] = z.v[c];
+    }
+}
+
+// R^k mod p for any integer k (R = 2^32)
+static u32 pow_r(int k) {
+    auto pw = [](u32 b, u64 ex) { u64 r = 1, x = b; for (; ex; ex >>= 1) { if (ex & 1) r = r * x % P; x = x * x % P; } return (u32)r; };
+    return k >= 0 ? pw(R1, (u64)k) : pw(pw(R1, P - 2), (u64)(-k));
+}
+
 extern "C" int sc_set_statement(sc_ctx *ctx, int D, int points, int ntables, int nterms, const uint32_t *coeffs,
                                 const int32_t *term_ptr, const int32_t *term_tables) {
     if (!ctx) return SC_EINVAL;
@@ -276,25 +300,77 @@ extern "C" int sc_set_statement(sc_ctx *ctx, int D, int points, int ntables, int
     }
     // the statement's tables first, in slot order; the others (only folded) after them
     int pos_of[SC_MAX_TABLES], npos = 0;
-    for (int s = 0; s < ntables; s++) if (used[s]) { ctx->order[npos] = s; pos_of[s] = npos++; }
-    const int nt_used = npos;
-    for (int s = 0; s < ntables; s++) if (!used[s]) { ctx->order[npos] = s; pos_of[s] = npos++; }
+    int occurrences[SC_MAX_TABLES] = {0};
+    for (int t = 0; t < nterms; t++) for (int k = term_ptr[t]; k < term_ptr[t + 1]; k++) occurrences[term_tables[k]]++;
+    int nt_used = 0;
+    for (int s = 0; s < ntables; s++) nt_used += used[s];
     if (nt_used > 4) return fail(ctx, SC_EUNSUPPORTED, "the statement multiplies %d different tables: at most 4", nt_used);
+
+    // statements with a kernel of their own (see Shape)
+    int shape = SHAPE_GENERIC, lam_term = -1;
+    int first[SC_MAX_TABLES];
+    int nfirst = 0;
+    auto is_one = [&](int t) {
+        for (int c = 0; c < D; c++) if (coeffs[(size_t)t * D + c] % P != (c == 0 ? 1u : 0u)) return false;
+        return true;
+    };
+    if (nterms == 1 && term_ptr[1] - term_ptr[0] == nt_used && points == nt_used && nt_used >= 1) {
+        bool distinct = true;
+        for (int s = 0; s < ntables; s++) if (occurrences[s] > 1) distinct = false;
+        if (distinct) shape = SHAPE_PRODUCT;
+    } else if (nterms == 3 && nt_used == 4 && points == 2) {
+        // a d + b c + lam c d: two tables occur twice (c, d) and share the term with the free coefficient
+        int doubles[4], nd = 0;
+        bool ok = true;
+        for (int s = 0; s < ntables; s++) { if (occurrences[s] == 2) doubles[nd++ & 3] = s; else if (occurrences[s] > 2) ok = false; }
+        for (int t = 0; t < 3; t++) if (term_ptr[t + 1] - term_ptr[t] != 2) ok = false;
+        if (ok && nd == 2) {
+            const int c = doubles[0], d = doubles[1];
+            int a = -1, b = -1;
+            for (int t = 0; t < 3; t++) {
+                const int x = term_tables[term_ptr[t]], y = term_tables[term_ptr[t] + 1];
+                if ((x == c && y == d) || (x == d && y == c)) lam_term = t;
+                else if ((x == d || y == d) && is_one(t)) a = (x == d) ? y : x;
+                else if ((x == c || y == c) && is_one(t)) b = (x == c) ? y : x;
+            }
+            if (lam_term >= 0 && a >= 0 && b >= 0 && a != b && occurrences[a] == 1 && occurrences[b] == 1) {
+                shape = SHAPE_GKR;
+                first[0] = a; first[1] = b; first[2] = c; first[3] = d; nfirst = 4;
+            }
+        }
+    }
+    bool placed[SC_MAX_TABLES] = {false};
+    for (int k = 0; k < nfirst; k++) { ctx->order[npos] = first[k]; pos_of[first[k]] = npos++; placed[first[k]] = true; }
+    for (int s = 0; s < ntables; s++) if (used[s] && !placed[s]) { ctx->order[npos] = s; pos_of[s] = npos++; placed[s] = true; }
+    for (int s = 0; s < ntables; s++) if (!placed[s]) { ctx->order[npos] = s; pos_of[s] = npos++; }
+    ctx->shape = shape;
     ctx->D = D; ctx->points = points; ctx->ntables = ntables; ctx->nt_used = nt_used > 0 ? nt_used : 1;
     memset(&ctx->st, 0, sizeof ctx->st);
     ctx->st.nterms = nterms;
+    int e = 0;
+    for (int t = 0; t < nterms; t++) e = std::max(e, term_ptr[t + 1] - term_ptr[t] - 1);
+    ctx->st_e = e;
+    ctx->use_factor = false;
     for (int t = 0; t < nterms; t++) {
-        DevTerm &tm = ctx->st.terms[t];
-        bool upper = false;
-        for (int c = 0; c < D; c++) {
-            const u32 v = coeffs[(size_t)t * D + c] % P;
-            tm.coeff[c] = to_mont(v);
-            if (c && v) upper = true;
-        }
-        tm.ckind = upper ? CK_EXT : ((coeffs[(size_t)t * D] % P) == 1 ? CK_ONE : CK_BASE);
+        // the GKR kernel reads lam from term 0
+        const int at = shape == SHAPE_GKR ? (t == lam_term ? 0 : (t < lam_term ? t + 1 : t)) : t;
+        DevTerm &tm = ctx->st.terms[at];
         tm.nf = (uint8_t)(term_ptr[t + 1] - term_ptr[t]);
         for (int k = 0; k < tm.nf; k++) tm.f[k] = (uint8_t)pos_of[term_tables[term_ptr[t] + k]];
-        if (tm.nf == 0) tm.ckind = CK_EXT;
+        // c R^(m-1-e) for a term of m tables, c R^-e for the constant term
+        const u32 scale = pow_r((tm.nf ? tm.nf - 1 : 0) - e);
+        bool upper = false;
+        u32 c[8];
+        for (int k = 0; k < D; k++) {
+            c[k] = (u32)(((u64)(coeffs[(size_t)t * D + k] % P) * scale) % P);
+            if (k && c[k]) upper = true;
+        }
+        tm.ckind = upper ? CK_EXT : (c[0] == 1 ? CK_ONE : CK_BASE);
+        for (int k = 0; k < D; k++) tm.coeff[k] = tm.nf ? to_mont(c[k]) : c[k];
+        if (shape == SHAPE_PRODUCT) {   // the coefficient waits for the final factor
+            ctx->use_factor = tm.ckind != CK_ONE;
+            for (int k = 0; k < D; k++) ctx->st_factor[k] = c[k];
+        }
     }
     ctx->have_statement = true;
     ctx->begun = false;
@@ -365,14 +441,10 @@ static int export_tables(sc_ctx *ctx, const int *slots, int count, u64 entries, 
     ExportArgs a;
     memset(&a, 0, sizeof a);
     a.ntables = count; a.count = entries; a.out = ctx->d_export;
-    bool raw = false;
     for (int k = 0; k < count; k++) {
         const TableState &t = ctx->tab[slots[k]];
         a.src[k] = t.cur; a.src_base[k] = t.cur_base;
-        if (k && raw != t.cur_raw) return fail(ctx, SC_ESTATE, "tables in different states");
-        raw = t.cur_raw;
     }
-    a.raw = raw;
     CU(launch_export(D, a, ctx->stream));
     ctx->launches++;
     CU(cudaMemcpyAsync(ctx->h_export, ctx->d_export, words * 4, cudaMemcpyDeviceToHost, ctx->stream));
@@ -386,7 +458,7 @@ extern "C" int sc_download_table(sc_ctx *ctx, int slot, uint32_t *host, uint64_t
     TableState &t = ctx->tab[slot];
     if (!t.t0) return fail(ctx, SC_ESTATE, "table %d was never uploaded", slot);
     cudaSetDevice(ctx->device);
-    if (!ctx->begun) { t.cur = t.t0; t.cur_base = t.stride == 1; t.cur_raw = true; t.cur_entries = t.entries; t.cur_buf = -1; }
+    if (!ctx->begun) { t.cur = t.t0; t.cur_base = t.stride == 1; t.cur_entries = t.entries; t.cur_buf = -1; }
     if (entries) *entries = t.cur_entries;
     const u64 count = t.cur_entries < cap ? t.cur_entries : cap;
     if (!host || !count) return SC_OK;
@@ -422,7 +494,7 @@ extern "C" int sc_begin(sc_ctx *ctx, int n, const uint32_t *eq, int K, const uin
         if (!t.t0) return fail(ctx, SC_ESTATE, "table %d was never uploaded", s);
         if (t.entries != want) return fail(ctx, SC_EINVAL, "table %d has %llu entries: expected %llu", s, (unsigned long long)t.entries, (unsigned long long)want);
         if (t.stride != 1 && t.stride != D) return fail(ctx, SC_EINVAL, "table %d has stride %d: expected 1 or %d", s, t.stride, D);
-        t.cur = t.t0; t.cur_buf = -1; t.cur_base = t.stride == 1; t.cur_raw = true; t.cur_entries = t.entries;
+        t.cur = t.t0; t.cur_buf = -1; t.cur_base = t.stride == 1; t.cur_entries = t.entries;
     }
     ctx->n = n; ctx->K = K; ctx->j = 0; ctx->nloc = nloc; ctx->have_r = false; ctx->have_eq = eq != nullptr;
     ctx->stats.clear();
@@ -501,12 +573,8 @@ extern "C" int sc_begin(sc_ctx *ctx, int n, const uint32_t *eq, int K, const uin
 
 // ------------------------------------------------------------------ rounds
 
-static void challenge_words(const sc_ctx *ctx, bool raw, u32 *out) {
-    // r R for a source in Montgomery form; r R^2 for canonical words, so that REDC(r' s) = r s R
-    for (int c = 0; c < ctx->D; c++) {
-        u32 m = to_mont(ctx->r[c]);
-        out[c] = raw ? to_mont(m) : m;
-    }
+static void challenge_words(const sc_ctx *ctx, u32 *out) {
+    for (int c = 0; c < ctx->D; c++) out[c] = to_mont(ctx->r[c]);   // REDC(r R s) = r s
 }
 
 // Fold every table by the pending challenge with the stand-alone kernel (the last fold, and the
@@ -518,9 +586,8 @@ static int fold_all(sc_ctx *ctx) {
     a.ntables = ctx->ntables;
     if (!a.ntables) return SC_OK;
     const TableState &t0 = ctx->tab[0];
-    a.raw = t0.cur_raw;
     a.nout = t0.cur_entries / 2;
-    challenge_words(ctx, a.raw, a.r);
+    challenge_words(ctx, a.r);
     for (int s = 0; s < ctx->ntables; s++) {
         TableState &t = ctx->tab[s];
         const int nb = t.cur_buf == 0 ? 1 : 0;
@@ -533,7 +600,7 @@ static int fold_all(sc_ctx *ctx) {
     for (int s = 0; s < ctx->ntables; s++) {
         TableState &t = ctx->tab[s];
         const int nb = t.cur_buf == 0 ? 1 : 0;
-        t.cur = t.buf[nb]; t.cur_buf = nb; t.cur_base = false; t.cur_raw = false; t.cur_entries = a.nout;
+        t.cur = t.buf[nb]; t.cur_buf = nb; t.cur_base = false; t.cur_entries = a.nout;
     }
     ctx->have_r = false;
     return SC_OK;
@@ -578,8 +645,8 @@ extern "C" int sc_round(sc_ctx *ctx, uint32_t *sums) {
     for (int k = 0; k < ctx->ntables; k++) {
         TableState &t = ctx->tab[ctx->order[k]];
         a.src[k] = t.cur; a.src_base[k] = t.cur_base;
-        if (k == 0) { a.raw = t.cur_raw; in_entries = t.cur_entries; }
-        else if ((int)t.cur_raw != a.raw || t.cur_entries != in_entries) return fail(ctx, SC_ESTATE, "tables in different states");
+        if (k == 0) in_entries = t.cur_entries;
+        else if (t.cur_entries != in_entries) return fail(ctx, SC_ESTATE, "tables in different states");
         bytes += t.cur_entries * (u64)(t.cur_base ? 1 : D) * 4;
         if (fold) {
             const int nb = t.cur_buf == 0 ? 1 : 0;
@@ -589,21 +656,29 @@ extern "C" int sc_round(sc_ctx *ctx, uint32_t *sums) {
         }
     }
     a.npairs = fold ? in_entries / 4 : in_entries / 2;
-    if (fold) challenge_words(ctx, a.raw != 0, a.r);
+    if (fold) challenge_words(ctx, a.r);
     a.logL = pl.logL;
     a.use_low = pl.use_low; a.use_high = pl.use_high;
     a.low = ctx->d_weights + pl.low_word;
     a.high = ctx->d_weights + pl.high_word;
     a.st = ctx->st;
-    a.use_post = local && ctx->use_post;
-    memcpy(a.post, ctx->post, sizeof a.post);
+    // the final factor: R^e of the statement, a product statement's coefficient, and this rank's eq
+    // weight while the tables are sharded
+    {
+        const bool rankw = local && ctx->use_post;
+        a.use_post = ctx->st_e > 0 || rankw || ctx->use_factor;
+        const u32 re = to_mont(pow_r(ctx->st_e));
+        for (int c = 0; c < D; c++) a.post[c] = ctx->use_factor ? mmul(to_mont(ctx->st_factor[c]), re) : (c == 0 ? re : 0u);
+        if (rankw) ext_mul_host(D, a.post, ctx->post, a.post);
+    }
     a.partials = ctx->d_partials; a.counter = ctx->d_counter;
     a.out_dev = ctx->d_out;
     a.out_host = local ? nullptr : ctx->h_out_dev;
 
     const u64 chunk = (1ull << a.logL) > (u64)ROUND_THREADS ? (1ull << a.logL) : (u64)ROUND_THREADS;
     u64 chunks = (a.npairs + chunk - 1) / chunk;
-    int grid = (int)(chunks < (u64)(ctx->sms * 2) ? chunks : (u64)(ctx->sms * 2));
+    const u64 max_grid = (u64)ctx->sms * ctx->blocks_per_sm;
+    int grid = (int)(chunks < max_grid ? chunks : max_grid);
     if (grid < 1) grid = 1;
     const size_t smem = a.use_low ? ((size_t)1 << a.logL) * 2 * D * 4 : 0;
 
@@ -613,7 +688,7 @@ extern "C" int sc_round(sc_ctx *ctx, uint32_t *sums) {
         e0 = ctx->ev[0]; e1 = ctx->ev[1];
         CU(cudaEventRecord(e0, ctx->stream));
     }
-    CU(launch_round(D, ctx->points, ctx->nt_used, fold, a, grid, smem, ctx->stream));
+    CU(launch_round(D, ctx->shape, ctx->points, ctx->nt_used, fold, a, grid, smem, ctx->stream));
     ctx->launches++;
     if (ctx->timing) CU(cudaEventRecord(e1, ctx->stream));
     if (local) {   // the whole job's sums: all-gather of the ranks' words, then their sum mod p
@@ -635,7 +710,7 @@ extern "C" int sc_round(sc_ctx *ctx, uint32_t *sums) {
         for (int k = 0; k < ctx->ntables; k++) {
             TableState &t = ctx->tab[ctx->order[k]];
             const int nb = t.cur_buf == 0 ? 1 : 0;
-            t.cur = t.buf[nb]; t.cur_buf = nb; t.cur_base = false; t.cur_raw = false; t.cur_entries = in_entries / 2;
+            t.cur = t.buf[nb]; t.cur_buf = nb; t.cur_base = false; t.cur_entries = in_entries / 2;
         }
     }
     ctx->have_r = false;

@@ -13,8 +13,18 @@ using scf::u64;
 
 enum CoeffKind : uint8_t { CK_ONE = 0, CK_BASE = 1, CK_EXT = 2 };
 
-// One term of the statement: coefficient times a product of tables.  The coefficient is in
-// Montgomery form; a term without factors is the constant term of the statement.
+// Statements with a kernel of their own; every other statement runs the term-table kernel.
+//   SHAPE_PRODUCT  c t0 t1 .. t(k-1), each table once, k points; c rides in the round's final factor
+//   SHAPE_GKR      a d + b c + lam c d over the tables (a, b, c, d) = positions (0, 1, 2, 3);
+//                  lam is the coefficient of term 0
+enum Shape : int { SHAPE_GENERIC = 0, SHAPE_PRODUCT = 1, SHAPE_GKR = 2 };
+
+// One term of the statement: coefficient times a product of tables.  Tables hold canonical words
+// and constants (coefficients, weights, challenges) are in Montgomery form c R, so REDC of
+// constant times value is their canonical product.  A product of m table values computed with
+// m - 1 REDCs carries the factor R^-(m-1); with e = max(m - 1) over the terms, the coefficient of
+// a term is stored as c R^(m-1-e) and the round's final factor carries R^e.  A term without
+// factors is the constant term, stored as the canonical word c R^-e and added as it is.
 struct DevTerm {
     u32 coeff[8];
     uint8_t ckind;
@@ -39,8 +49,7 @@ struct RoundArgs {
     u32 *dst[SC_MAX_TABLES];
     uint8_t src_base[SC_MAX_TABLES];   // 1: the source holds base-field entries (one word each)
     int ntables;          // tables read (and folded); the statement may use fewer
-    int raw;              // 1: source words are canonical residues (the caller's tables), else Montgomery form
-    u32 r[8];             // the fold challenge: r R when the source is in Montgomery form, r R^2 when raw
+    u32 r[8];             // the fold challenge, Montgomery form
     u64 npairs;           // pairs to sum, over all blocks
     int logL;             // pairs per high weight: 2^logL
     int use_low;          // 0: every low weight is 1 (and logL is 0 or there is no eq)
@@ -57,7 +66,7 @@ struct RoundArgs {
 };
 
 // Launchers (defined next to their kernels).  Each returns the CUDA error of the launch.
-cudaError_t launch_round(int D, int points, int nt_used, bool fold, const RoundArgs &args, int grid, size_t smem,
+cudaError_t launch_round(int D, int shape, int points, int nt_used, bool fold, const RoundArgs &args, int grid, size_t smem,
                          cudaStream_t stream);
 bool round_supported(int D, int points, int nt_used);
 
@@ -67,18 +76,16 @@ struct FoldArgs {
     u32 *dst[SC_MAX_TABLES];
     uint8_t src_base[SC_MAX_TABLES];
     int ntables;
-    int raw;
-    u32 r[8];
+    u32 r[8];     // Montgomery form
     u64 nout;     // entries written per table
 };
 cudaError_t launch_fold(int D, const FoldArgs &args, cudaStream_t stream);
 
-// Montgomery form (or raw, lifted) entries to canonical extension elements: count entries per table.
+// Entries as extension elements (base entries lifted): count entries per table.
 struct ExportArgs {
     const u32 *src[SC_MAX_TABLES];
     uint8_t src_base[SC_MAX_TABLES];
     int ntables;
-    int raw;
     u64 count;
     u32 *out;     // ntables * count * D words
 };

@@ -3,9 +3,11 @@
 //
 // The reference computes a product as (mod (* a b) p) on 64-bit words (src/field.lisp:70-72) and an
 // extension product as a schoolbook sum with one reduction per four products (mul*, :220-234).
-// Here every value on the device is kept in Montgomery form x R mod p, R = 2^32: a product of two
-// such values followed by REDC is again in that form.  Values cross the library boundary as
-// canonical residues in [0, p).
+// Here a product is a 64-bit product followed by Montgomery's REDC (R = 2^32), which leaves the
+// factor 1/R: constants (challenges, weights, coefficients) are kept as c R so that constant
+// times value needs no correction, and the factors left by products of two table values are
+// collected into one constant per round (see DevTerm in device.h).  Tables hold canonical
+// residues in [0, p) on the device as they do at the library boundary.
 //
 // An extension element is D words in the reference's tower order: word i holds the coefficient of
 // w^bitrev(i) (power-order, src/field.lisp:195-204).

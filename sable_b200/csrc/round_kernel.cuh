@@ -18,6 +18,13 @@
 #pragma once
 #include "device.h"
 
+#ifndef SC_MINBLOCKS
+#define SC_MINBLOCKS 2
+#endif
+#ifndef SC_PREFETCH
+#define SC_PREFETCH 0
+#endif
+
 namespace sc {
 
 using namespace scf;
@@ -45,77 +52,111 @@ template <int D, int NT> __device__ __forceinline__ Ext<D> pick(const Ext<D> (&v
     return o;
 }
 
-// The statement at one point: sum of coefficient * product of the tables' values (in Montgomery form).
-template <int D, int NT> __device__ __forceinline__ Ext<D> eval_statement(const DevStatement &st, const Ext<D> (&val)[NT]) {
+// The statement at one point: sum of coefficient * product of the tables' values.  Values are
+// canonical words; a product of two of them leaves REDC's factor 1/R behind, which the
+// coefficients and the final factor of the round make up for (see DevStatement).  With BASEAWARE
+// (a round on the caller's tables) a value that is a base element multiplies by D base products,
+// or one when both factors are base elements (the reference's base variant, src/sumcheck.lisp:237-246).
+// *ALL_BASE comes back true when the value is a base element.
+template <int D, int NT, bool BASEAWARE>
+__device__ __forceinline__ Ext<D> eval_statement(const DevStatement &st, const Ext<D> (&val)[NT], unsigned base_mask, bool *all_base) {
     Ext<D> acc = ezero<D>();
+    bool abase = true;
     for (int t = 0; t < st.nterms; t++) {
         const DevTerm &tm = st.terms[t];
         Ext<D> prod;
+        bool pbase = false;
         if (tm.nf == 0) {
 #pragma unroll
             for (int c = 0; c < D; c++) prod.v[c] = tm.coeff[c];
             acc = eadd<D>(acc, prod);
+            abase = abase && tm.ckind != CK_EXT;
             continue;
         }
         prod = pick<D, NT>(val, tm.f[0]);
-        for (int k = 1; k < tm.nf; k++) prod = emul<D>(prod, pick<D, NT>(val, tm.f[k]));
-        if (tm.ckind == CK_BASE) prod = escale<D>(prod, tm.coeff[0]);
-        else if (tm.ckind == CK_EXT) {
+        if (BASEAWARE) pbase = (base_mask >> tm.f[0]) & 1;
+        for (int k = 1; k < tm.nf; k++) {
+            const Ext<D> v = pick<D, NT>(val, tm.f[k]);
+            if (BASEAWARE) {
+                const bool vbase = (base_mask >> tm.f[k]) & 1;
+                if (pbase && vbase) prod.v[0] = mmul(prod.v[0], v.v[0]);
+                else if (vbase) prod = escale<D>(prod, v.v[0]);
+                else if (pbase) { prod = escale<D>(v, prod.v[0]); pbase = false; }
+                else prod = emul<D>(prod, v);
+            } else {
+                prod = emul<D>(prod, v);
+            }
+        }
+        if (tm.ckind == CK_BASE) {
+            if (BASEAWARE && pbase) prod.v[0] = mmul(prod.v[0], tm.coeff[0]);
+            else prod = escale<D>(prod, tm.coeff[0]);
+        } else if (tm.ckind == CK_EXT) {
             Ext<D> c;
 #pragma unroll
             for (int q = 0; q < D; q++) c.v[q] = tm.coeff[q];
-            prod = emul<D>(prod, c);
+            if (BASEAWARE && pbase) { prod = escale<D>(c, prod.v[0]); pbase = false; }
+            else prod = emul<D>(prod, c);
         }
+        abase = abase && pbase;
         acc = eadd<D>(acc, prod);
     }
+    if (BASEAWARE) *all_base = abase;
     return acc;
 }
 
-// The pair (lo, hi) of table t for pair index i, in Montgomery form.
-template <int D, bool FOLD>
-__device__ __forceinline__ void load_pair(const RoundArgs &a, int t, u64 i, const ExtM<D> &rm, Ext<D> &lo, Ext<D> &hi) {
-    const u32 *src = a.src[t];
-    if (!FOLD) {
-        if (a.src_base[t]) {
-            uint2 w = __ldcs(reinterpret_cast<const uint2 *>(src) + i);
-            lo = lift<D>(a.raw ? to_mont(w.x) : w.x);
-            hi = lift<D>(a.raw ? to_mont(w.y) : w.y);
-        } else {
-            lo = load_ext<D>(src + 2 * i * D);
-            hi = load_ext<D>(src + (2 * i + 1) * D);
-            if (a.raw) { lo = eto_mont<D>(lo); hi = eto_mont<D>(hi); }
-        }
-        return;
-    }
-    // fold entries 4i .. 4i+3 by r: e0 + r (e1 - e0), e2 + r (e3 - e2)  (FOLD-FLAT-TABLE, src/sumcheck.lisp:84-104)
-    if (a.src_base[t]) {
-        uint4 w = __ldcs(reinterpret_cast<const uint4 *>(src) + i);
-        const u32 s0 = fsub(w.y, w.x), s1 = fsub(w.w, w.z);
-        // the slope is a base element: D base products (:96-98); r carries the factor that puts the product in Montgomery form
+// A pure product of the NT tables (the coefficient rides in the round's final factor).
+template <int D, int NT, bool BASEAWARE>
+__device__ __forceinline__ Ext<D> eval_product(const Ext<D> (&val)[NT], unsigned base_mask, bool *all_base) {
+    Ext<D> prod = val[0];
+    bool pbase = BASEAWARE && (base_mask & 1);
 #pragma unroll
-        for (int c = 0; c < D; c++) { lo.v[c] = mmul(rm.v[c], s0); hi.v[c] = mmul(rm.v[c], s1); }
-        lo.v[0] = fadd(lo.v[0], a.raw ? to_mont(w.x) : w.x);
-        hi.v[0] = fadd(hi.v[0], a.raw ? to_mont(w.z) : w.z);
-    } else {
-        Ext<D> e0 = load_ext<D>(src + (4 * i) * D), e1 = load_ext<D>(src + (4 * i + 1) * D);
-        Ext<D> e2 = load_ext<D>(src + (4 * i + 2) * D), e3 = load_ext<D>(src + (4 * i + 3) * D);
-        Ext<D> p0 = emul<D>(esub<D>(e1, e0), rm), p1 = emul<D>(esub<D>(e3, e2), rm);
-        if (a.raw) { e0 = eto_mont<D>(e0); e2 = eto_mont<D>(e2); }
-        lo = eadd<D>(e0, p0);
-        hi = eadd<D>(e2, p1);
+    for (int t = 1; t < NT; t++) {
+        if (BASEAWARE) {
+            const bool vbase = (base_mask >> t) & 1;
+            if (pbase && vbase) prod.v[0] = mmul(prod.v[0], val[t].v[0]);
+            else if (vbase) prod = escale<D>(prod, val[t].v[0]);
+            else if (pbase) { prod = escale<D>(val[t], prod.v[0]); pbase = false; }
+            else prod = emul<D>(prod, val[t]);
+        } else {
+            prod = emul<D>(prod, val[t]);
+        }
     }
-    u32 *dst = a.dst[t];
-    store_ext<D>(dst + (2 * i) * D, lo);
-    store_ext<D>(dst + (2 * i + 1) * D, hi);
+    if (BASEAWARE) *all_base = pbase;
+    return prod;
 }
 
-template <int D, int PTS, int NT, bool FOLD>
-__global__ void __launch_bounds__(ROUND_THREADS) round_kernel(const __grid_constant__ RoundArgs a) {
+// The layer statement of LogUp-GKR, a d + b c + lam c d for the tables (a, b, c, d) at positions
+// (0, 1, 2, 3) (reference LAYER-STATEMENT, src/gkr.lisp:30-41), as (a + lam c) d + b c: three
+// products, one of them by the constant.
+template <int D, bool BASEAWARE>
+__device__ __forceinline__ Ext<D> eval_gkr(const Ext<D> (&val)[4], const ExtM<D> &lam, unsigned base_mask) {
+    const bool ab = BASEAWARE && (base_mask & 1), bb = BASEAWARE && (base_mask & 2), cb = BASEAWARE && (base_mask & 4),
+               db = BASEAWARE && (base_mask & 8);
+    Ext<D> u;
+    if (cb) {
+#pragma unroll
+        for (int k = 0; k < D; k++) u.v[k] = mmul(lam.v[k], val[2].v[0]);
+    } else {
+        u = emul<D>(val[2], lam);
+    }
+    if (ab) u.v[0] = fadd(u.v[0], val[0].v[0]); else u = eadd<D>(u, val[0]);
+    Ext<D> f = db ? escale<D>(u, val[3].v[0]) : emul<D>(u, val[3]);
+    Ext<D> g;
+    if (bb && cb) g = lift<D>(mmul(val[1].v[0], val[2].v[0]));
+    else if (bb) g = escale<D>(val[2], val[1].v[0]);
+    else if (cb) g = escale<D>(val[1], val[2].v[0]);
+    else g = emul<D>(val[1], val[2]);
+    return eadd<D>(f, g);
+}
+
+template <int D, int PTS, int NT, bool FOLD, int SHAPE>
+__global__ void __launch_bounds__(ROUND_THREADS, SC_MINBLOCKS) round_kernel(const __grid_constant__ RoundArgs a) {
     extern __shared__ __align__(16) u32 smem[];
     __shared__ u32 red[ROUND_THREADS / 32][PTS * D];
     __shared__ bool is_last;
     const int tid = threadIdx.x;
     const u32 L = 1u << a.logL;
+    constexpr int NE = FOLD ? 4 : 2;   // entries read per table and pair
 
     if (a.use_low) {   // the low multipliers of this round: (v, 3v) per entry
         const uint4 *g = reinterpret_cast<const uint4 *>(a.low);
@@ -129,6 +170,16 @@ __global__ void __launch_bounds__(ROUND_THREADS) round_kernel(const __grid_const
 #pragma unroll
         for (int c = 0; c < D; c++) r.v[c] = a.r[c];
         rm = eprep<D>(r);
+    }
+    unsigned base_mask = 0;
+#pragma unroll
+    for (int t = 0; t < NT; t++) base_mask |= (a.src_base[t] ? 1u : 0u) << t;
+    ExtM<D> lam;
+    if (SHAPE == SHAPE_GKR) {
+        Ext<D> c;
+#pragma unroll
+        for (int k = 0; k < D; k++) c.v[k] = a.st.terms[0].coeff[k];
+        lam = eprep<D>(c);
     }
 
     Ext<D> total[PTS], inner[PTS];
@@ -160,16 +211,91 @@ __global__ void __launch_bounds__(ROUND_THREADS) round_kernel(const __grid_const
                 if (cur_h != ~0ull) flush();
                 cur_h = h;
             }
+#if SC_PREFETCH
+            {   // pull the next pair of this thread towards L2 while this one is computed
+                const u64 nx = (q + ROUND_THREADS < chunk) ? i + ROUND_THREADS : i + (u64)gridDim.x * chunk - q + tid;
+                if (nx < a.npairs && (tid & 1) == 0) {
+#pragma unroll
+                    for (int t = 0; t < NT; t++) {
+                        const char *pp = ((base_mask >> t) & 1) ? reinterpret_cast<const char *>(a.src[t]) + nx * (NE * 4)
+                                                                : reinterpret_cast<const char *>(a.src[t]) + nx * (NE * D * 4);
+                        const int bytes = ((base_mask >> t) & 1) ? NE * 4 * 2 : NE * D * 4 * 2;
+                        for (int o = 0; o < bytes; o += 128) asm volatile("prefetch.global.L2 [%0];" ::"l"(pp + o));
+                    }
+                }
+            }
+#endif
+            // every load of the pair first, so that they are all in flight together
+            Ext<D> e[NT][NE];
+#pragma unroll
+            for (int t = 0; t < NT; t++) {
+                if ((base_mask >> t) & 1) {
+                    if (FOLD) {
+                        const uint4 w = __ldcs(reinterpret_cast<const uint4 *>(a.src[t]) + i);
+                        e[t][0].v[0] = w.x; e[t][1].v[0] = w.y; e[t][2].v[0] = w.z; e[t][3].v[0] = w.w;
+                    } else {
+                        const uint2 w = __ldcs(reinterpret_cast<const uint2 *>(a.src[t]) + i);
+                        e[t][0].v[0] = w.x; e[t][1].v[0] = w.y;
+                    }
+                } else {
+#pragma unroll
+                    for (int k = 0; k < NE; k++) e[t][k] = load_ext<D>(a.src[t] + (NE * i + k) * D);
+                }
+            }
             Ext<D> val[NT], slope[NT];
 #pragma unroll
             for (int t = 0; t < NT; t++) {
-                Ext<D> hi;
-                load_pair<D, FOLD>(a, t, i, rm, val[t], hi);
-                slope[t] = esub<D>(hi, val[t]);
+                const bool tb = (base_mask >> t) & 1;
+                if (!FOLD) {
+                    if (tb) {
+                        val[t] = lift<D>(e[t][0].v[0]);
+                        const u32 sl = fsub(e[t][1].v[0], e[t][0].v[0]);
+                        slope[t] = lift<D>(PTS == 2 ? fadd(sl, e[t][1].v[0]) : sl);
+                    } else {
+                        val[t] = e[t][0];
+                        slope[t] = esub<D>(e[t][1], e[t][0]);
+                        if (PTS == 2) slope[t] = eadd<D>(slope[t], e[t][1]);
+                    }
+                } else {
+                    // fold entries 4i .. 4i+3 by r: e0 + r (e1 - e0), e2 + r (e3 - e2)  (FOLD-FLAT-TABLE, src/sumcheck.lisp:84-104)
+                    Ext<D> lo, hi;
+                    if (tb) {   // the slope is a base element: D base products (:96-98)
+                        const u32 s0 = fsub(e[t][1].v[0], e[t][0].v[0]), s1 = fsub(e[t][3].v[0], e[t][2].v[0]);
+#pragma unroll
+                        for (int c = 0; c < D; c++) { lo.v[c] = mmul(rm.v[c], s0); hi.v[c] = mmul(rm.v[c], s1); }
+                        lo.v[0] = fadd(lo.v[0], e[t][0].v[0]);
+                        hi.v[0] = fadd(hi.v[0], e[t][2].v[0]);
+                    } else {
+                        lo = eadd<D>(e[t][0], emul<D>(esub<D>(e[t][1], e[t][0]), rm));
+                        hi = eadd<D>(e[t][2], emul<D>(esub<D>(e[t][3], e[t][2]), rm));
+                    }
+                    store_ext<D>(a.dst[t] + (2 * i) * D, lo);
+                    store_ext<D>(a.dst[t] + (2 * i + 1) * D, hi);
+                    val[t] = lo;
+                    slope[t] = esub<D>(hi, lo);
+                    if (PTS == 2) slope[t] = eadd<D>(slope[t], hi);
+                }
             }
             // tables beyond the statement's are only folded
             if (FOLD) {
-                for (int t = NT; t < a.ntables; t++) { Ext<D> lo, hi; load_pair<D, true>(a, t, i, rm, lo, hi); }
+                for (int t = NT; t < a.ntables; t++) {
+                    Ext<D> lo, hi;
+                    if (a.src_base[t]) {
+                        const uint4 w = __ldcs(reinterpret_cast<const uint4 *>(a.src[t]) + i);
+                        const u32 s0 = fsub(w.y, w.x), s1 = fsub(w.w, w.z);
+#pragma unroll
+                        for (int c = 0; c < D; c++) { lo.v[c] = mmul(rm.v[c], s0); hi.v[c] = mmul(rm.v[c], s1); }
+                        lo.v[0] = fadd(lo.v[0], w.x);
+                        hi.v[0] = fadd(hi.v[0], w.z);
+                    } else {
+                        const u32 *src = a.src[t] + 4 * i * D;
+                        Ext<D> e0 = load_ext<D>(src), e1 = load_ext<D>(src + D), e2 = load_ext<D>(src + 2 * D), e3 = load_ext<D>(src + 3 * D);
+                        lo = eadd<D>(e0, emul<D>(esub<D>(e1, e0), rm));
+                        hi = eadd<D>(e2, emul<D>(esub<D>(e3, e2), rm));
+                    }
+                    store_ext<D>(a.dst[t] + (2 * i) * D, lo);
+                    store_ext<D>(a.dst[t] + (2 * i + 1) * D, hi);
+                }
             }
             ExtM<D> lw;
             if (a.use_low) {
@@ -183,15 +309,27 @@ __global__ void __launch_bounds__(ROUND_THREADS) round_kernel(const __grid_const
             }
 #pragma unroll
             for (int x = 0; x < PTS; x++) {
-                if (x == 1) {   // X = 2: lo + 2 s
+                if (x == 1) {   // X = 2: lo + 2 s; with two points the array holds 2 hi - lo already
 #pragma unroll
-                    for (int t = 0; t < NT; t++) val[t] = eadd<D>(eadd<D>(val[t], slope[t]), slope[t]);
+                    for (int t = 0; t < NT; t++) val[t] = PTS == 2 ? slope[t] : eadd<D>(eadd<D>(val[t], slope[t]), slope[t]);
                 } else if (x > 1) {
 #pragma unroll
                     for (int t = 0; t < NT; t++) val[t] = eadd<D>(val[t], slope[t]);
                 }
-                Ext<D> f = eval_statement<D, NT>(a.st, val);
-                if (a.use_low) f = emul<D>(f, lw);
+                bool fbase = false;
+                Ext<D> f;
+                if (SHAPE == SHAPE_PRODUCT) f = eval_product<D, NT, !FOLD>(val, base_mask, &fbase);
+                else if (SHAPE == SHAPE_GKR) f = eval_gkr<D, !FOLD>(reinterpret_cast<const Ext<D>(&)[4]>(val), lam, base_mask);
+                else f = eval_statement<D, NT, !FOLD>(a.st, val, FOLD ? 0u : base_mask, &fbase);
+                if (a.use_low) {
+                    if (!FOLD && fbase) {   // a base value times the weight: D base products (EXT-SCALE, src/sumcheck.lisp:246)
+                        const u32 fb = f.v[0];
+#pragma unroll
+                        for (int c = 0; c < D; c++) f.v[c] = mmul(lw.v[c], fb);
+                    } else {
+                        f = emul<D>(f, lw);
+                    }
+                }
                 inner[x] = eadd<D>(inner[x], f);
             }
         }
@@ -223,7 +361,7 @@ __global__ void __launch_bounds__(ROUND_THREADS) round_kernel(const __grid_const
     if (!is_last) return;
     __threadfence();
 
-    // the last block: add the partials, apply the final factor, leave Montgomery form
+    // the last block: add the partials and apply the final factor
     {
         constexpr int W = PTS * D;                 // <= 32 words
         constexpr int ROWS = ROUND_THREADS / 32;
@@ -249,7 +387,6 @@ __global__ void __launch_bounds__(ROUND_THREADS) round_kernel(const __grid_const
                 for (int c = 0; c < D; c++) pf.v[c] = a.post[c];
                 s = emul<D>(s, pf);
             }
-            s = efrom_mont<D>(s);
 #pragma unroll
             for (int c = 0; c < D; c++) {
                 a.out_dev[tid * D + c] = s.v[c];
@@ -261,14 +398,14 @@ __global__ void __launch_bounds__(ROUND_THREADS) round_kernel(const __grid_const
     }
 }
 
-template <int D, int PTS, int NT>
-static cudaError_t launch_round_dpn(bool fold, const RoundArgs &args, int grid, size_t smem, cudaStream_t stream) {
+template <int D, int PTS, int NT, int SHAPE>
+static cudaError_t launch_round_dpns(bool fold, const RoundArgs &args, int grid, size_t smem, cudaStream_t stream) {
     if (fold) {
-        if (smem > 48 * 1024) cudaFuncSetAttribute(round_kernel<D, PTS, NT, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-        round_kernel<D, PTS, NT, true><<<grid, ROUND_THREADS, smem, stream>>>(args);
+        if (smem > 48 * 1024) cudaFuncSetAttribute(round_kernel<D, PTS, NT, true, SHAPE>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        round_kernel<D, PTS, NT, true, SHAPE><<<grid, ROUND_THREADS, smem, stream>>>(args);
     } else {
-        if (smem > 48 * 1024) cudaFuncSetAttribute(round_kernel<D, PTS, NT, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-        round_kernel<D, PTS, NT, false><<<grid, ROUND_THREADS, smem, stream>>>(args);
+        if (smem > 48 * 1024) cudaFuncSetAttribute(round_kernel<D, PTS, NT, false, SHAPE>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        round_kernel<D, PTS, NT, false, SHAPE><<<grid, ROUND_THREADS, smem, stream>>>(args);
     }
     return cudaGetLastError();
 }
@@ -276,16 +413,32 @@ static cudaError_t launch_round_dpn(bool fold, const RoundArgs &args, int grid, 
 template <int D, int PTS>
 static cudaError_t launch_round_dp(int nt, bool fold, const RoundArgs &args, int grid, size_t smem, cudaStream_t stream) {
     switch (nt) {
-    case 1: return launch_round_dpn<D, PTS, 1>(fold, args, grid, smem, stream);
-    case 2: return launch_round_dpn<D, PTS, 2>(fold, args, grid, smem, stream);
-    case 3: return launch_round_dpn<D, PTS, 3>(fold, args, grid, smem, stream);
-    case 4: return launch_round_dpn<D, PTS, 4>(fold, args, grid, smem, stream);
+    case 1: return launch_round_dpns<D, PTS, 1, SHAPE_GENERIC>(fold, args, grid, smem, stream);
+    case 2: return launch_round_dpns<D, PTS, 2, SHAPE_GENERIC>(fold, args, grid, smem, stream);
+    case 3: return launch_round_dpns<D, PTS, 3, SHAPE_GENERIC>(fold, args, grid, smem, stream);
+    case 4: return launch_round_dpns<D, PTS, 4, SHAPE_GENERIC>(fold, args, grid, smem, stream);
     default: return cudaErrorInvalidValue;
     }
 }
 
+// The kernels with the statement built in: a product of nt tables at nt points, the GKR layer.
 template <int D>
-static cudaError_t launch_round_d(int points, int nt, bool fold, const RoundArgs &args, int grid, size_t smem, cudaStream_t stream) {
+static cudaError_t launch_round_shape(int shape, int points, int nt, bool fold, const RoundArgs &args, int grid, size_t smem, cudaStream_t stream) {
+    if (shape == SHAPE_GKR && points == 2 && nt == 4) return launch_round_dpns<D, 2, 4, SHAPE_GKR>(fold, args, grid, smem, stream);
+    if (shape == SHAPE_PRODUCT && points == nt) {
+        switch (nt) {
+        case 1: return launch_round_dpns<D, 1, 1, SHAPE_PRODUCT>(fold, args, grid, smem, stream);
+        case 2: return launch_round_dpns<D, 2, 2, SHAPE_PRODUCT>(fold, args, grid, smem, stream);
+        case 3: return launch_round_dpns<D, 3, 3, SHAPE_PRODUCT>(fold, args, grid, smem, stream);
+        case 4: return launch_round_dpns<D, 4, 4, SHAPE_PRODUCT>(fold, args, grid, smem, stream);
+        }
+    }
+    return cudaErrorInvalidValue;
+}
+
+template <int D>
+static cudaError_t launch_round_d(int shape, int points, int nt, bool fold, const RoundArgs &args, int grid, size_t smem, cudaStream_t stream) {
+    if (shape != SHAPE_GENERIC) return launch_round_shape<D>(shape, points, nt, fold, args, grid, smem, stream);
     switch (points) {
     case 1: return launch_round_dp<D, 1>(nt, fold, args, grid, smem, stream);
     case 2: return launch_round_dp<D, 2>(nt, fold, args, grid, smem, stream);
