@@ -1,0 +1,45 @@
+"""Several GPUs: the hypercube cut on its top variables, one process per GPU, sums combined by an
+NCCL all-gather and a sum mod p, tables gathered for the last rounds.  The proof must be the
+single-GPU (and the oracle's) proof, bit for bit.  Skipped with fewer than two GPUs."""
+import json
+import os
+import subprocess
+import sys
+import tempfile
+
+import pytest
+
+pytestmark = pytest.mark.gpu
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+
+
+def gpu_count():
+    import torch
+    return torch.cuda.device_count()
+
+
+@pytest.mark.parametrize("world", [2, 4, 8])
+def test_sharded_proof_equals_the_oracle(world):
+    if gpu_count() < world:
+        pytest.skip("needs %d GPUs" % world)
+    with tempfile.TemporaryDirectory() as tmp:
+        env = dict(os.environ, NCCL_NVLS_ENABLE="0")
+        procs = [subprocess.Popen([sys.executable, os.path.join(ROOT, "tests", "multi_gpu_worker.py"), str(r), str(world),
+                                   os.path.join(tmp, "id"), os.path.join(tmp, "out%d.json" % r)], env=env,
+                                  stdout=subprocess.PIPE, stderr=subprocess.STDOUT, text=True) for r in range(world)]
+        outs = []
+        for p in procs:
+            try:
+                out, _ = p.communicate(timeout=300)
+            except subprocess.TimeoutExpired:
+                for q in procs:
+                    q.kill()
+                raise
+            outs.append(out)
+        for r, p in enumerate(procs):
+            assert p.returncode == 0, "rank %d failed:\n%s" % (r, outs[r][-3000:])
+        res = [json.load(open(os.path.join(tmp, "out%d.json" % r))) for r in range(world)]
+        assert all(c["ok"] for c in res[0]), res[0]
+        # every rank ends with the same transcript and the same finals
+        for r in range(2, world):
+            assert res[r] == res[1]
