@@ -136,6 +136,30 @@ int sc_fetch_table(sc_ctx *ctx, int slot, uint32_t *host, uint64_t words);
 int sc_comm_unique_id(void *nccl_id128);
 int sc_comm_init(sc_ctx *ctx, const void *nccl_id128, int rank, int world);
 
+/* One round's sums with no allocation at all, for callers that cannot allocate device memory where
+   they run: code recording work into a stream capture, a service whose device memory was handed
+   out completely at start-up, a plug-in that receives device pointers but no allocator.  It has
+   no counterpart in the reference (which allocates freely); it computes what sc_round returns
+   for round 0 of a proof without eq weights: the sums of the statement (given as for
+   sc_set_statement) at X = 0, 2, .., POINTS over the pairs of the caller's device-resident
+   tables (TABLES_DEV[t]: ENTRIES entries of STRIDES[t] words, canonical, below p), written as
+   POINTS * D canonical words to the device buffer SUMS_DEV.  The launch is asynchronous on STREAM
+   (a cudaStream_t, or NULL).
+   Scratch: the per-block partial sums and a block counter live in one fixed array in the
+   library's device image (256.25 KiB, held by every GPU that loads the library until exit),
+   one row per 65 536 pairs and at most 2 048 rows, so ENTRIES may be at most 2^28; more is
+   refused with SC_EINVAL and a message naming the limit.  The first call on a device looks up
+   the array's device address (cudaGetSymbolAddress), so make that first call before any stream
+   capture begins.  All calls share the array: the counter is cleared at the start of each call,
+   the rows are overwritten, and two calls that run on the GPU at the same time race -- order
+   them on one stream or with events.  Nothing is allocated or freed, on the device or by any
+   library, and no context is needed.  On failure the text of the error is copied to MESSAGE
+   (MESSAGE_CAP bytes, may be NULL). */
+int sc_round_sums_static(int D, int points, int ntables, const uint32_t *const *tables_dev, const int *strides,
+                         uint64_t entries, int nterms, const uint32_t *coeffs, const int32_t *term_ptr,
+                         const int32_t *term_tables, uint32_t *sums_dev, void *stream, char *message,
+                         size_t message_cap);
+
 /* ------------------------------------------------------------------ part 2: the host layer */
 
 typedef struct sc_transcript sc_transcript;

@@ -27,7 +27,7 @@ _u32p = C.POINTER(C.c_uint32)
 SYMBOLS = [
     "sc_create", "sc_destroy", "sc_set_memory_budget", "sc_strerror", "sc_last_error", "sc_set_statement",
     "sc_upload_table", "sc_generate_table", "sc_download_table", "sc_begin", "sc_round", "sc_challenge", "sc_finish",
-    "sc_enable_timing", "sc_round_stats", "sc_launch_count", "sc_timer_start", "sc_timer_stop", "sc_fetch_table", "sc_comm_unique_id", "sc_comm_init",
+    "sc_enable_timing", "sc_round_stats", "sc_launch_count", "sc_timer_start", "sc_timer_stop", "sc_fetch_table", "sc_comm_unique_id", "sc_comm_init", "sc_round_sums_static",
     "sc_transcript_new", "sc_transcript_free", "sc_transcript_absorb", "sc_transcript_send",
     "sc_transcript_challenge_base", "sc_transcript_challenge_bits", "sc_transcript_digest",
     "sc_transcript_message_count", "sc_transcript_message", "sc_transcript_sent_bytes", "sc_transcript_encode",
@@ -295,6 +295,32 @@ class Prover:
 
     def comm_init(self, unique_id, rank, world):
         self._call("sc_comm_init", unique_id, rank, world)
+
+
+def round_sums_static(D, points, tables_dev, strides, entries, terms, sums_dev, stream=0):
+    """Round-0 sums without eq weights over device-resident tables, with no allocation (sc_round_sums_static).
+
+    For callers that cannot allocate device memory where they run.  ``tables_dev`` and ``sums_dev``
+    are device addresses (integers) the caller owns; ``terms`` is the term table as for
+    ``Prover.set_statement``.  The launch is asynchronous on ``stream``; calls share one fixed
+    scratch array in the library, so calls that overlap on the GPU race.  At most 2^28 entries.
+    """
+    coeffs = _u32([t[0] for t in terms]).reshape(-1, D) if terms else np.zeros((1, D), dtype=np.uint32)
+    ptr = np.zeros(len(terms) + 1, dtype=np.int32)
+    idx = []
+    for i, (_, tabs) in enumerate(terms):
+        idx.extend(tabs)
+        ptr[i + 1] = len(idx)
+    idx = np.asarray(idx + [0], dtype=np.int32)
+    tabs = (_u32p * max(len(tables_dev), 1))(*[C.cast(C.c_void_p(a), _u32p) for a in tables_dev])
+    message = C.create_string_buffer(512)
+    code = library().sc_round_sums_static(D, points, len(tables_dev), tabs, (C.c_int * max(len(strides), 1))(*strides),
+                                          C.c_uint64(entries), len(terms), _ptr(coeffs), ptr.ctypes.data_as(C.POINTER(C.c_int32)),
+                                          idx.ctypes.data_as(C.POINTER(C.c_int32)), C.cast(C.c_void_p(sums_dev), _u32p),
+                                          C.c_void_p(stream), message, C.c_size_t(512))
+    if code:
+        text = "%s: %s" % (library().sc_strerror(code).decode(), message.value.decode())
+        raise (InvalidParameter if code in (-1, -7) else SumcheckError)(code, text)
 
 
 def comm_unique_id():

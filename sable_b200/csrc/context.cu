@@ -771,3 +771,90 @@ extern "C" int sc_comm_init(sc_ctx *ctx, const void *nccl_id128, int rank, int w
     ctx->begun = false;
     return SC_OK;
 }
+
+// ------------------------------------------------------------------ a round without any allocation
+//
+// sc_round_sums_static is for callers that must not allocate device memory while they run: code
+// between the capture calls of a stream, a service whose memory pool was sized up front and
+// handed out completely, a plug-in that is given device pointers but no allocator.  A context
+// (sc_create) allocates its partial-sum buffers and grows table buffers on demand; this entry
+// point takes everything from the caller and keeps its only scratch -- one row of partial sums
+// per block and the counter of finished blocks -- in the fixed array below, which every GPU that
+// loads the library holds until the process ends.
+
+namespace {
+constexpr int STATIC_ROWS = 2048;                 // blocks a call may launch: one partial row each
+constexpr u64 STATIC_PAIRS_PER_ROW = 65536;       // pairs a block sums
+constexpr int STATIC_HEAD_WORDS = 64;             // the counter, in 256 bytes of its own
+constexpr int STATIC_WORDS = STATIC_HEAD_WORDS + STATIC_ROWS * MAX_PARTIAL_WORDS;   // 64 + 2048 * 32 words = 256.25 KiB
+static __device__ __align__(256) u32 g_static_scratch[STATIC_WORDS];
+constexpr int STATIC_MAX_DEVICES = 64;
+u32 *g_static_ptr[STATIC_MAX_DEVICES];            // the array's device address, per device ordinal (0 = not asked yet)
+}  // namespace
+
+static int round_sums_static(sc_ctx *ctx, int D, int points, int ntables, const uint32_t *const *tables_dev, const int *strides,
+                             uint64_t entries, int nterms, const uint32_t *coeffs, const int32_t *term_ptr,
+                             const int32_t *term_tables, uint32_t *sums_dev, void *stream);
+
+extern "C" int sc_round_sums_static(int D, int points, int ntables, const uint32_t *const *tables_dev, const int *strides,
+                                    uint64_t entries, int nterms, const uint32_t *coeffs, const int32_t *term_ptr,
+                                    const int32_t *term_tables, uint32_t *sums_dev, void *stream, char *message,
+                                    size_t message_cap) {
+    static sc_ctx lowering;   // holds only the lowered statement; it never owns device memory
+    sc_ctx *ctx = &lowering;
+    if (message && message_cap) message[0] = 0;
+    const int rc = round_sums_static(ctx, D, points, ntables, tables_dev, strides, entries, nterms, coeffs, term_ptr, term_tables,
+                                     sums_dev, stream);
+    if (rc && message && message_cap) snprintf(message, message_cap, "%s", ctx->last_error.c_str());
+    return rc;
+}
+
+static int round_sums_static(sc_ctx *ctx, int D, int points, int ntables, const uint32_t *const *tables_dev, const int *strides,
+                             uint64_t entries, int nterms, const uint32_t *coeffs, const int32_t *term_ptr,
+                             const int32_t *term_tables, uint32_t *sums_dev, void *stream) {
+    if (!tables_dev || !strides || !sums_dev) return fail(ctx, SC_EINVAL, "null argument");
+    if (entries < 2 || (entries & 1)) return fail(ctx, SC_EINVAL, "%llu entries: expected an even number", (unsigned long long)entries);
+    const u64 npairs = entries / 2;
+    const u64 rows = (npairs + STATIC_PAIRS_PER_ROW - 1) / STATIC_PAIRS_PER_ROW;
+    if (rows > (u64)STATIC_ROWS)
+        return fail(ctx, SC_EINVAL, "%llu entries need %llu rows of scratch: the static array holds %d (at most %llu entries per table)",
+                    (unsigned long long)entries, (unsigned long long)rows, STATIC_ROWS,
+                    (unsigned long long)(2 * STATIC_PAIRS_PER_ROW * STATIC_ROWS));
+    int rc = sc_set_statement(ctx, D, points, ntables, nterms, coeffs, term_ptr, term_tables);
+    if (rc) return rc;
+    if (!round_supported(D, ctx->points, ctx->nt_used)) return fail(ctx, SC_EUNSUPPORTED, "no kernel for D=%d points=%d tables=%d", D, points, ctx->nt_used);
+    for (int t = 0; t < ntables; t++)
+        if (!tables_dev[t] || (strides[t] != 1 && strides[t] != D)) return fail(ctx, SC_EINVAL, "table %d: null, or stride %d not 1 or %d", t, strides[t], D);
+
+    // set-up, once per device: the array's name is a host-side stand-in, the kernel needs its device address
+    int device = -1;
+    CU(cudaGetDevice(&device));
+    if (device < 0 || device >= STATIC_MAX_DEVICES) return fail(ctx, SC_EUNSUPPORTED, "device ordinal %d", device);
+    if (!g_static_ptr[device]) {
+        u32 *p = nullptr;
+        CU(cudaGetSymbolAddress((void **)&p, g_static_scratch));
+        g_static_ptr[device] = p;
+    }
+    u32 *scratch = g_static_ptr[device];
+    cudaStream_t s = (cudaStream_t)stream;
+    // the array keeps what the last call left: the counter must start at zero
+    CU(cudaMemsetAsync(scratch, 0, STATIC_HEAD_WORDS * 4, s));
+
+    RoundArgs a;
+    memset(&a, 0, sizeof a);
+    a.ntables = ctx->nt_used;
+    for (int k = 0; k < ctx->nt_used; k++) {
+        a.src[k] = tables_dev[ctx->order[k]];
+        a.src_base[k] = strides[ctx->order[k]] == 1;
+    }
+    a.npairs = npairs;
+    a.st = ctx->st;
+    a.use_post = ctx->st_e > 0 || ctx->use_factor;
+    const u32 re = to_mont(pow_r(ctx->st_e));
+    for (int c = 0; c < D; c++) a.post[c] = ctx->use_factor ? mmul(to_mont(ctx->st_factor[c]), re) : (c == 0 ? re : 0u);
+    a.counter = scratch;
+    a.partials = scratch + STATIC_HEAD_WORDS;
+    a.out_dev = sums_dev;
+    CU(launch_round(D, ctx->shape, ctx->points, ctx->nt_used, false, a, (int)rows, 0, s));
+    return SC_OK;
+}
