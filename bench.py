@@ -16,6 +16,7 @@ on its top log2(N) variables: total work is fixed, so the scaling is strong.
 `--impl reference` times the CPU port alone, with all host threads, on a bounded sample.
 """
 import argparse
+import hashlib
 import json
 import os
 import statistics
@@ -292,7 +293,7 @@ def main():
             "config": {"workload": workload, "sharding": "top %d variables over %d GPUs" % (logw, world), "transcript": "host (BLAKE3)",
                        "l2": "inputs larger than L2 (%.1f GiB per rank per proof)" % (sum(4 * (strides[s] << n_loc) for s in range(len(strides))) / 2 ** 30)},
             "e2e": e2e, "gpu_launches": launches, "clocks": clocks, "roofline": roofline, "cpu_baseline": cpu,
-            "proof_bytes": len(proof_bytes),
+            "proof_bytes": len(proof_bytes), "proof_sha256": hashlib.sha256(proof_bytes).hexdigest(),
         }))
     if world > 1:
         dist.destroy_process_group()

@@ -135,6 +135,8 @@ int sc_fetch_table(sc_ctx *ctx, int slot, uint32_t *host, uint64_t words);
    others by the caller.  sc_begin's N stays the whole job's.  No reference counterpart. */
 int sc_comm_unique_id(void *nccl_id128);
 int sc_comm_init(sc_ctx *ctx, const void *nccl_id128, int rank, int world);
+/* The context's place in its communicator (rank 0 of 1 without one). */
+int sc_comm_info(const sc_ctx *ctx, int *rank, int *world);
 
 /* One round's sums with no allocation at all, for callers that cannot allocate device memory where
    they run: code recording work into a stream capture, a service whose device memory was handed
@@ -189,8 +191,8 @@ int sc_lower_statement(const char *statement, int D, int ntables, const char *co
                        uint32_t *coeffs, int32_t *term_ptr, int32_t *term_tables);
 
 /* PROVE (src/sumcheck.lisp:512-571) with the reference's argument meaning.  TABLES[t] is host
-   memory of K * 2^N entries of STRIDES[t] words, or NULL for a table already on the device in
-   slot t (sc_upload_table, sc_generate_table).  DEGREE < 0 takes the statement's degree.
+   memory of K * 2^N entries of STRIDES[t] words (with a communicator: this rank's slice, 2^N / world
+   entries), or NULL for a table already on the device in slot t (sc_upload_table, sc_generate_table).  DEGREE < 0 takes the statement's degree.
    Outputs (any may be NULL): CHALLENGES n * D, FINALS ntables * D, FOLDED ntables * max(K,1) * D.
    TR ends in the state, and with the recorded messages, the reference leaves it in. */
 int sc_prove(sc_ctx *ctx, sc_transcript *tr, int n, const char *statement, int ntables,

@@ -27,7 +27,7 @@ _u32p = C.POINTER(C.c_uint32)
 SYMBOLS = [
     "sc_create", "sc_destroy", "sc_set_memory_budget", "sc_strerror", "sc_last_error", "sc_set_statement",
     "sc_upload_table", "sc_generate_table", "sc_download_table", "sc_begin", "sc_round", "sc_challenge", "sc_finish",
-    "sc_enable_timing", "sc_round_stats", "sc_launch_count", "sc_timer_start", "sc_timer_stop", "sc_fetch_table", "sc_comm_unique_id", "sc_comm_init", "sc_round_sums_static",
+    "sc_enable_timing", "sc_round_stats", "sc_launch_count", "sc_timer_start", "sc_timer_stop", "sc_fetch_table", "sc_comm_unique_id", "sc_comm_init", "sc_comm_info", "sc_round_sums_static",
     "sc_transcript_new", "sc_transcript_free", "sc_transcript_absorb", "sc_transcript_send",
     "sc_transcript_challenge_base", "sc_transcript_challenge_bits", "sc_transcript_digest",
     "sc_transcript_message_count", "sc_transcript_message", "sc_transcript_sent_bytes", "sc_transcript_encode",
@@ -296,6 +296,13 @@ class Prover:
     def comm_init(self, unique_id, rank, world):
         self._call("sc_comm_init", unique_id, rank, world)
 
+    @property
+    def world(self):
+        """Ranks of the communicator (1 without one); with several, each rank's tables are its slice."""
+        w = C.c_int(1)
+        self._call("sc_comm_info", None, C.byref(w))
+        return w.value
+
 
 def round_sums_static(D, points, tables_dev, strides, entries, terms, sums_dev, stream=0):
     """Round-0 sums without eq weights over device-resident tables, with no allocation (sc_round_sums_static).
@@ -376,9 +383,9 @@ def prove(tr, n, statement, tables, eq=None, constants=(), label="sc", block_wei
             continue
         a = _u32(values)
         stride = 1 if a.ndim == 1 else a.shape[1]
-        if a.ndim > 2 or stride not in (1, D) or a.shape[0] != K << n:
+        if a.ndim > 2 or stride not in (1, D) or a.shape[0] != (K << n) // prover.world:
             raise InvalidParameter(-1, "table %s of shape %s: expected %d base elements or extension elements of degree %d"
-                                   % (name, a.shape, K << n, D))
+                                   % (name, a.shape, (K << n) // prover.world, D))
         arrays.append(a)
         strides.append(stride)
     ptrs = (_u32p * max(len(names), 1))(*[_ptr(a) if a is not None else None for a in arrays])

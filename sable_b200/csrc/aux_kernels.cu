@@ -195,17 +195,23 @@ cudaError_t launch_reduce_words(u32 *words, u64 count, cudaStream_t stream) {
 
 // ------------------------------------------------------------------ sum of the ranks' partial sums (canonical words)
 
-__global__ void sum_ranks_kernel(const u32 *gathered, int world, int words, u32 *out_dev, u32 *out_host) {
+__global__ void sum_ranks_kernel(const u32 *gathered, int world, int words, u32 *out_dev, u32 *out_host, u32 seq) {
     const int k = threadIdx.x;
-    if (k >= words) return;
-    u32 acc = 0;
-    for (int r = 0; r < world; r++) acc = fadd(acc, gathered[r * words + k]);
-    out_dev[k] = acc;
-    if (out_host) out_host[k] = acc;
-    __threadfence_system();
+    if (k < words) {
+        u32 acc = 0;
+        for (int r = 0; r < world; r++) acc = fadd(acc, gathered[r * words + k]);
+        out_dev[k] = acc;
+        if (out_host) out_host[k] = acc;
+        __threadfence_system();
+    }
+    __syncthreads();
+    if (k == 0 && out_host) {
+        __threadfence_system();
+        *reinterpret_cast<volatile u32 *>(out_host + MAX_PARTIAL_WORDS) = seq;
+    }
 }
-cudaError_t launch_sum_ranks(const u32 *gathered, int world, int words, u32 *out_dev, u32 *out_host, cudaStream_t stream) {
-    sum_ranks_kernel<<<1, 64, 0, stream>>>(gathered, world, words, out_dev, out_host);
+cudaError_t launch_sum_ranks(const u32 *gathered, int world, int words, u32 *out_dev, u32 *out_host, u32 seq, cudaStream_t stream) {
+    sum_ranks_kernel<<<1, 64, 0, stream>>>(gathered, world, words, out_dev, out_host, seq);
     return cudaGetLastError();
 }
 

@@ -6,6 +6,8 @@
 #include <dlfcn.h>
 
 #include <algorithm>
+#include <atomic>
+#include <chrono>
 #include <cstdarg>
 #include <cstdio>
 #include <cstdlib>
@@ -97,6 +99,10 @@ struct sc_ctx {
     u32 post[8];                     // the final factor of a round: R^e of the statement times this rank's eq weight
     bool use_post = false;
     int st_e = 0;                    // e of the statement (see DevTerm)
+    u32 st_re = 0;                   // R^e in Montgomery form
+    u32 seq = 0;                     // number of the last round launch; the kernel posts it after the sums
+    int base_groups = 0;             // > 0: the statement can run the base-table kernel with this many groups
+    u32 gcoef[2][8];                 // the groups' coefficients (Montgomery form)
     int shape = SHAPE_GENERIC;       // the kernel family of the statement
     u32 st_factor[8];                // a product statement's coefficient (canonical), applied with the final factor
     bool use_factor = false;
@@ -198,10 +204,10 @@ extern "C" int sc_create(int device, sc_ctx **out) {
     ctx->sms = prop.multiProcessorCount;
     if (const char *env = getenv("SABLE_B200_BLOCKS_PER_SM")) { int v = atoi(env); if (v >= 1 && v <= 8) ctx->blocks_per_sm = v; }
     ctx->grid_cap = ctx->sms * 8;
-    bool ok = cudaMalloc(&ctx->d_partials, (size_t)ctx->grid_cap * MAX_PARTIAL_WORDS * 4) == cudaSuccess &&
+    bool ok = cudaMalloc(&ctx->d_partials, (size_t)ctx->grid_cap * PARTIAL_ROW_WORDS * 4) == cudaSuccess &&
               cudaMalloc(&ctx->d_counter, 64) == cudaSuccess && cudaMemset(ctx->d_counter, 0, 64) == cudaSuccess &&
               cudaMalloc(&ctx->d_out, MAX_PARTIAL_WORDS * 4) == cudaSuccess &&
-              cudaHostAlloc(&ctx->h_out, MAX_PARTIAL_WORDS * 4, cudaHostAllocMapped) == cudaSuccess &&
+              cudaHostAlloc(&ctx->h_out, (MAX_PARTIAL_WORDS + 32) * 4, cudaHostAllocMapped) == cudaSuccess &&
               cudaHostGetDevicePointer(&ctx->h_out_dev, ctx->h_out, 0) == cudaSuccess;
     if (!ok) { cudaGetLastError(); sc_destroy(ctx); return SC_ECUDA; }
     *out = ctx;
@@ -343,6 +349,7 @@ extern "C" int sc_set_statement(sc_ctx *ctx, int D, int points, int ntables, int
     for (int k = 0; k < nfirst; k++) { ctx->order[npos] = first[k]; pos_of[first[k]] = npos++; placed[first[k]] = true; }
     for (int s = 0; s < ntables; s++) if (used[s] && !placed[s]) { ctx->order[npos] = s; pos_of[s] = npos++; placed[s] = true; }
     for (int s = 0; s < ntables; s++) if (!placed[s]) { ctx->order[npos] = s; pos_of[s] = npos++; }
+    if (getenv("SABLE_B200_GENERIC")) shape = SHAPE_GENERIC;   // run every statement through the term-table kernel (for cross-checks)
     ctx->shape = shape;
     ctx->D = D; ctx->points = points; ctx->ntables = ntables; ctx->nt_used = nt_used > 0 ? nt_used : 1;
     memset(&ctx->st, 0, sizeof ctx->st);
@@ -350,6 +357,7 @@ extern "C" int sc_set_statement(sc_ctx *ctx, int D, int points, int ntables, int
     int e = 0;
     for (int t = 0; t < nterms; t++) e = std::max(e, term_ptr[t + 1] - term_ptr[t] - 1);
     ctx->st_e = e;
+    ctx->st_re = to_mont(pow_r(e));
     ctx->use_factor = false;
     for (int t = 0; t < nterms; t++) {
         // the GKR kernel reads lam from term 0
@@ -370,6 +378,31 @@ extern "C" int sc_set_statement(sc_ctx *ctx, int D, int points, int ntables, int
         if (shape == SHAPE_PRODUCT) {   // the coefficient waits for the final factor
             ctx->use_factor = tm.ckind != CK_ONE;
             for (int k = 0; k < D; k++) ctx->st_factor[k] = c[k];
+        }
+    }
+    // the kernel for rounds whose tables are all in the base field: terms with base coefficients share
+    // one sum, a term with an extension coefficient has its own (at most one of those)
+    {
+        int ext_terms = 0, base_terms = 0;
+        bool ok = true;
+        for (int t = 0; t < nterms; t++) {
+            DevTerm &tm = ctx->st.terms[t];
+            if (tm.ckind == CK_EXT && tm.nf > 0) ext_terms++;
+            else if (tm.ckind == CK_EXT) ok = false;          // an extension constant term
+            else base_terms++;
+        }
+        if (ext_terms > 1 || nterms == 0) ok = false;
+        ctx->base_groups = ok ? (base_terms > 0) + ext_terms : 0;
+        memset(ctx->gcoef, 0, sizeof ctx->gcoef);
+        ctx->gcoef[0][0] = R1;
+        if (shape == SHAPE_PRODUCT) { ctx->base_groups = 1; ok = false; }   // the product's coefficient rides in the final factor
+        for (int t = 0; t < nterms && ok; t++) {
+            DevTerm &tm = ctx->st.terms[t];
+            tm.group = 0;
+            if (tm.ckind == CK_EXT && tm.nf > 0) {
+                tm.group = base_terms > 0 ? 1 : 0;
+                for (int c = 0; c < D; c++) ctx->gcoef[tm.group][c] = tm.coeff[c];
+            }
         }
     }
     ctx->have_statement = true;
@@ -467,7 +500,7 @@ extern "C" int sc_download_table(sc_ctx *ctx, int slot, uint32_t *host, uint64_t
 
 // ------------------------------------------------------------------ begin: the weights of every round
 
-static int low_bits_cap(int D) { return D == 4 ? 10 : 9; }   // 2^a multipliers of 2 D words in shared memory: 32 KiB
+static int low_bits_cap(int D) { return D == 4 ? 11 : 10; }   // 2^a multipliers of 2 D words in shared memory: 64 KiB
 
 // The split of the v = (variables after the round's own) eq variables of a round: the lower a of
 // them index the low multipliers held in shared memory, the others the high weights.  Any split
@@ -626,6 +659,8 @@ extern "C" int sc_round(sc_ctx *ctx, uint32_t *sums) {
     if (!ctx->begun) return fail(ctx, SC_ESTATE, "sc_round before sc_begin");
     if (ctx->j >= ctx->n) return fail(ctx, SC_ESTATE, "all %d rounds are done", ctx->n);
     if (ctx->j > 0 && !ctx->have_r) return fail(ctx, SC_ESTATE, "round %d needs the challenge of round %d", ctx->j, ctx->j - 1);
+    static const bool trace = getenv("SABLE_B200_TRACE") != nullptr;
+    const auto tr0 = std::chrono::steady_clock::now();
     cudaSetDevice(ctx->device);
     const int D = ctx->D, j = ctx->j, W = ctx->points * D;
     if (!round_supported(D, ctx->points, ctx->nt_used)) return fail(ctx, SC_EUNSUPPORTED, "no kernel for D=%d points=%d tables=%d", D, ctx->points, ctx->nt_used);
@@ -667,10 +702,11 @@ extern "C" int sc_round(sc_ctx *ctx, uint32_t *sums) {
     {
         const bool rankw = local && ctx->use_post;
         a.use_post = ctx->st_e > 0 || rankw || ctx->use_factor;
-        const u32 re = to_mont(pow_r(ctx->st_e));
+        const u32 re = ctx->st_re;
         for (int c = 0; c < D; c++) a.post[c] = ctx->use_factor ? mmul(to_mont(ctx->st_factor[c]), re) : (c == 0 ? re : 0u);
         if (rankw) ext_mul_host(D, a.post, ctx->post, a.post);
     }
+    a.seq = ++ctx->seq;
     a.partials = ctx->d_partials; a.counter = ctx->d_counter;
     a.out_dev = ctx->d_out;
     a.out_host = local ? nullptr : ctx->h_out_dev;
@@ -688,18 +724,51 @@ extern "C" int sc_round(sc_ctx *ctx, uint32_t *sums) {
         e0 = ctx->ev[0]; e1 = ctx->ev[1];
         CU(cudaEventRecord(e0, ctx->stream));
     }
-    CU(launch_round(D, ctx->shape, ctx->points, ctx->nt_used, fold, a, grid, smem, ctx->stream));
+    const auto tr1 = std::chrono::steady_clock::now();
+    bool all_base = !fold && ctx->base_groups > 0 && !getenv("SABLE_B200_GENERIC");
+    for (int k = 0; k < ctx->nt_used && all_base; k++) all_base = a.src_base[k];
+    if (all_base) {
+        a.ngroups = ctx->base_groups;
+        a.product = ctx->shape == SHAPE_PRODUCT;
+        memcpy(a.gcoef, ctx->gcoef, sizeof a.gcoef);
+        CU(launch_round_base(D, ctx->points, ctx->nt_used, a.ngroups, a, grid, smem, ctx->stream));
+    } else {
+        CU(launch_round(D, ctx->shape, ctx->points, ctx->nt_used, fold, a, grid, smem, ctx->stream));
+    }
     ctx->launches++;
     if (ctx->timing) CU(cudaEventRecord(e1, ctx->stream));
     if (local) {   // the whole job's sums: all-gather of the ranks' words, then their sum mod p
         if (!ctx->d_gather) { if ((rc = dev_alloc(ctx, (void **)&ctx->d_gather, (u64)ctx->world * MAX_PARTIAL_WORDS * 4))) return rc; }
         ncclResult_t r = g_nccl.AllGather(ctx->d_out, ctx->d_gather, (size_t)W, NCCL_UINT32, ctx->comm, ctx->stream);
         if (r) return fail(ctx, SC_ECOMM, "ncclAllGather: %s", g_nccl.GetErrorString(r));
-        CU(launch_sum_ranks(ctx->d_gather, ctx->world, W, ctx->d_out, ctx->h_out_dev, ctx->stream));
+        CU(launch_sum_ranks(ctx->d_gather, ctx->world, W, ctx->d_out, ctx->h_out_dev, a.seq, ctx->stream));
         ctx->launches++;
     }
-    CU(cudaStreamSynchronize(ctx->stream));
+    const auto tr2 = std::chrono::steady_clock::now();
+    // wait for the sums: poll the word the kernel posts after them (a stream synchronize costs several
+    // microseconds more per round); the wait is bounded and falls back to the synchronize, which also
+    // reports any fault
+    {
+        volatile u32 *flag = ctx->h_out + MAX_PARTIAL_WORDS;
+        const auto t0 = std::chrono::steady_clock::now();
+        bool seen = false;
+        for (u64 spin = 0; !seen; spin++) {
+            if (*flag == a.seq) { seen = true; break; }
+            if ((spin & 0xfff) == 0xfff) {
+                cudaError_t q = cudaStreamQuery(ctx->stream);
+                if (q != cudaErrorNotReady) break;   // finished (the flag is about to show) or failed
+                if (std::chrono::steady_clock::now() - t0 > std::chrono::seconds(20)) break;
+            }
+        }
+        if (!seen || ctx->timing) CU(cudaStreamSynchronize(ctx->stream));
+        std::atomic_thread_fence(std::memory_order_acquire);
+    }
     memcpy(sums, ctx->h_out, (size_t)W * 4);
+    if (trace) {
+        const auto tr3 = std::chrono::steady_clock::now();
+        auto us = [](std::chrono::steady_clock::time_point x, std::chrono::steady_clock::time_point y) { return std::chrono::duration<double, std::micro>(y - x).count(); };
+        fprintf(stderr, "  sc_round %d: prepare %.1f us, launch %.1f us, wait %.1f us\n", j, us(tr0, tr1), us(tr1, tr2), us(tr2, tr3));
+    }
     if (ctx->timing) {
         sc_round_stat s;
         CU(cudaEventElapsedTime(&s.kernel_ms, e0, e1));
@@ -752,6 +821,13 @@ extern "C" int sc_comm_unique_id(void *nccl_id128) {
     ncclUniqueId id;
     if (g_nccl.GetUniqueId(&id)) return SC_ECOMM;
     memcpy(nccl_id128, &id, sizeof id);
+    return SC_OK;
+}
+
+extern "C" int sc_comm_info(const sc_ctx *ctx, int *rank, int *world) {
+    if (!ctx) return SC_EINVAL;
+    if (rank) *rank = ctx->rank;
+    if (world) *world = ctx->world;
     return SC_OK;
 }
 

@@ -30,7 +30,8 @@ struct DevTerm {
     uint8_t ckind;
     uint8_t nf;
     uint8_t f[SC_MAX_FACTORS];
-    uint8_t pad[2];
+    uint8_t group;        // the base-table kernel: which sum the term's base value goes to (see RoundArgs::gcoef)
+    uint8_t pad;
 };
 struct DevStatement {
     int nterms;
@@ -62,13 +63,26 @@ struct RoundArgs {
     u32 *partials;        // gridDim.x rows of points * D words
     unsigned int *counter;// blocks that have written their partial; the last one finishes and resets it
     u32 *out_dev;         // points * D canonical words
-    u32 *out_host;        // the same, in mapped host memory (may be NULL)
+    u32 *out_host;        // the same, in mapped host memory (may be NULL) ...
+    u32 seq;              // ... followed, at word MAX_PARTIAL_WORDS, by this launch's number once the sums are visible
+    // The kernel for a round whose tables are all in the base field sums base values: one sum per
+    // group of terms, weighted by the eq weights, and multiplies each group's sum by its
+    // coefficient at the end.  Group 0 holds the terms with base-field coefficients (their sum is a
+    // base value, gcoef = 1); a term with an extension coefficient is a group of its own.
+    int ngroups;
+    int product;          // 1: the statement is the product of the tables (no term table needed)
+    u32 gcoef[2][8];      // Montgomery form
 };
+constexpr int MAX_GROUPS = 2;
+constexpr int PARTIAL_ROW_WORDS = MAX_GROUPS * MAX_PARTIAL_WORDS;   // words per block in the partials buffer
 
 // Launchers (defined next to their kernels).  Each returns the CUDA error of the launch.
 cudaError_t launch_round(int D, int shape, int points, int nt_used, bool fold, const RoundArgs &args, int grid, size_t smem,
                          cudaStream_t stream);
 bool round_supported(int D, int points, int nt_used);
+// The round on tables that are all in the base field (no fold): see RoundArgs::ngroups.
+cudaError_t launch_round_base(int D, int points, int nt_used, int ngroups, const RoundArgs &args, int grid, size_t smem,
+                              cudaStream_t stream);
 
 // Stand-alone fold of NTABLES tables: dst entry i = src[2i] + r (src[2i+1] - src[2i]).
 struct FoldArgs {
@@ -114,7 +128,7 @@ cudaError_t launch_weight_tables(int D, const u32 *chunks, const WeightDesc *des
                                  u32 *weights, u64 total_entries, cudaStream_t stream);
 
 // out[k] = sum over ranks of gathered[rank * words + k] mod p, to device and mapped host memory.
-cudaError_t launch_sum_ranks(const u32 *gathered, int world, int words, u32 *out_dev, u32 *out_host,
+cudaError_t launch_sum_ranks(const u32 *gathered, int world, int words, u32 *out_dev, u32 *out_host, u32 seq,
                              cudaStream_t stream);
 
 }  // namespace sc

@@ -5,6 +5,7 @@
 // (src/sumcheck.lisp:512-571), whose rounds run on the device through part 1 of the ABI.
 #include <algorithm>
 #include <cctype>
+#include <chrono>
 #include <cstdio>
 #include <cstdlib>
 #include <cstring>
@@ -404,8 +405,12 @@ extern "C" int sc_prove(sc_ctx *ctx, sc_transcript *tr, int n, const char *state
     if (degree < 0) degree = deg;                       // :513
     const int points = std::max(degree, 1);             // :527
     if ((rc = sc_set_statement(ctx, D, points, ntables, nterms, coeffs.data(), ptr.data(), idx.data()))) return rc;
+    // with a communicator each rank passes its slice: entries [rank 2^n / world, (rank + 1) 2^n / world)
+    int world = 1;
+    sc_comm_info(ctx, nullptr, &world);
+    if (world > 1 && (((u64)1 << n) < (u64)world)) return SC_EINVAL;
     for (int t = 0; t < ntables; t++)
-        if (tables && tables[t] && (rc = sc_upload_table(ctx, t, tables[t], (u64)blocks << n, strides[t]))) return rc;
+        if (tables && tables[t] && (rc = sc_upload_table(ctx, t, tables[t], ((u64)blocks << n) / (u64)world, strides[t]))) return rc;
     if ((rc = sc_begin(ctx, n, eq, blocks, block_weights))) return rc;
 
     // header: label | "|" | n u16 | degree u16 | blocks u32 (:24-27, :534)
@@ -417,12 +422,21 @@ extern "C" int sc_prove(sc_ctx *ctx, sc_transcript *tr, int n, const char *state
     tr->absorb(header.data(), header.size());
 
     u32 sums[SC_MAX_POINTS * 8], r[8];
+    const bool trace = getenv("SABLE_B200_TRACE") != nullptr;   // per-round host times on stderr
+    auto now = [] { return std::chrono::steady_clock::now(); };
+    auto us = [](std::chrono::steady_clock::time_point a, std::chrono::steady_clock::time_point b) {
+        return std::chrono::duration<double, std::micro>(b - a).count();
+    };
     for (int j = 0; j < n; j++) {                        // :547-563
+        const auto t0 = now();
         if ((rc = sc_round(ctx, sums))) return rc;
+        const auto t1 = now();
         tr->send(sums, points, D);
         tr->challenge_base(D, r);
+        const auto t2 = now();
         if (challenges) memcpy(challenges + (size_t)j * D, r, 4 * (size_t)D);
         if ((rc = sc_challenge(ctx, r))) return rc;
+        if (trace) fprintf(stderr, "round %d: device %.1f us, transcript %.1f us\n", j, us(t0, t1), us(t1, t2));
     }
     std::vector<u32> out((size_t)ntables * blocks * D);
     if ((rc = sc_finish(ctx, out.data()))) return rc;   // :564-571

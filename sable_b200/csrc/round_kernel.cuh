@@ -348,23 +348,22 @@ __global__ void __launch_bounds__(ROUND_THREADS, SC_MINBLOCKS) round_kernel(cons
             if (lane == 0) red[warp][x * D + c] = v;
         }
     __syncthreads();
-    if (tid < PTS * D) {
-        u32 v = red[0][tid];
+    constexpr int W = PTS * D;                 // <= 32 words
+    constexpr int ROWS = ROUND_THREADS / 32;
+    if (gridDim.x > 1) {
+        if (tid < W) {
+            u32 v = red[0][tid];
 #pragma unroll
-        for (int w = 1; w < ROUND_THREADS / 32; w++) v = fadd(v, red[w][tid]);
-        a.partials[(size_t)blockIdx.x * (PTS * D) + tid] = v;
-    }
-    __threadfence();
-    __syncthreads();
-    if (tid == 0) is_last = atomicAdd(a.counter, 1u) == gridDim.x - 1;
-    __syncthreads();
-    if (!is_last) return;
-    __threadfence();
-
-    // the last block: add the partials and apply the final factor
-    {
-        constexpr int W = PTS * D;                 // <= 32 words
-        constexpr int ROWS = ROUND_THREADS / 32;
+            for (int w = 1; w < ROWS; w++) v = fadd(v, red[w][tid]);
+            a.partials[(size_t)blockIdx.x * W + tid] = v;
+        }
+        __threadfence();
+        __syncthreads();
+        if (tid == 0) is_last = atomicAdd(a.counter, 1u) == gridDim.x - 1;
+        __syncthreads();
+        if (!is_last) return;
+        __threadfence();
+        // the last block: add the partials (a single block has its rows in shared memory already)
         const int k = tid & 31, row = tid >> 5;
         u32 v = 0;
         if (k < W)
@@ -372,6 +371,10 @@ __global__ void __launch_bounds__(ROUND_THREADS, SC_MINBLOCKS) round_kernel(cons
         __syncthreads();
         if (k < W) red[row][k] = v;
         __syncthreads();
+        if (tid == 0) *a.counter = 0;
+    }
+    // apply the final factor and publish
+    {
         if (tid < PTS) {
             Ext<D> s;
 #pragma unroll
@@ -392,9 +395,13 @@ __global__ void __launch_bounds__(ROUND_THREADS, SC_MINBLOCKS) round_kernel(cons
                 a.out_dev[tid * D + c] = s.v[c];
                 if (a.out_host) a.out_host[tid * D + c] = s.v[c];
             }
+            __threadfence_system();
         }
-        if (tid == 0) *a.counter = 0;
-        __threadfence_system();
+        __syncthreads();
+        if (tid == 0 && a.out_host) {   // the host polls this word: the sums above are visible before it
+            __threadfence_system();
+            *reinterpret_cast<volatile u32 *>(a.out_host + MAX_PARTIAL_WORDS) = a.seq;
+        }
     }
 }
 
