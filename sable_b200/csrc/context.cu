@@ -94,7 +94,9 @@ struct sc_ctx {
     // proof state
     bool begun = false, have_r = false, have_eq = false;
     int n = 0, K = 1, j = 0;
-    int nloc = 0;                    // rounds before the tables are gathered (n - log2 world)
+    int nloc = 0;                    // variables of a rank's slice (n - log2 world)
+    int gather_round = 0;            // the round before which the slices are gathered: every rank then holds the
+                                     // whole (small) tables and the rounds need no exchange any more
     u32 r[8];
     u32 post[8];                     // the final factor of a round: R^e of the statement times this rank's eq weight
     bool use_post = false;
@@ -119,7 +121,8 @@ struct sc_ctx {
     u32 *d_export = nullptr, *h_export = nullptr;
     u64 export_cap = 0;
     u32 *d_gather = nullptr;         // world * MAX_PARTIAL_WORDS
-    u32 *d_gtab[SC_MAX_TABLES];      // gathered tables (world entries each)
+    u32 *d_gtab[SC_MAX_TABLES];      // gathered tables
+    u64 gtab_cap[SC_MAX_TABLES] = {0};
     int grid_cap = 0;
 
     // timing
@@ -530,6 +533,12 @@ extern "C" int sc_begin(sc_ctx *ctx, int n, const uint32_t *eq, int K, const uin
         t.cur = t.t0; t.cur_buf = -1; t.cur_base = t.stride == 1; t.cur_entries = t.entries;
     }
     ctx->n = n; ctx->K = K; ctx->j = 0; ctx->nloc = nloc; ctx->have_r = false; ctx->have_eq = eq != nullptr;
+    // gather once a slice is down to 2^GATHER_BITS entries: from there on a round is latency, and an
+    // exchange per round would double it
+    int GATHER_BITS = 13;
+    if (const char *env = getenv("SABLE_B200_GATHER_BITS")) GATHER_BITS = std::max(0, std::min(30, atoi(env)));
+    ctx->gather_round = ctx->world > 1 ? std::max(0, nloc - GATHER_BITS) : n;
+    const int gather_round = ctx->gather_round;
     ctx->stats.clear();
     ctx->plan.assign(n, RoundPlan());
 
@@ -564,7 +573,7 @@ extern "C" int sc_begin(sc_ctx *ctx, int n, const uint32_t *eq, int K, const uin
     u64 words = 0, total_entries = 0;
     for (int j = 0; j < n; j++) {
         RoundPlan &pl = ctx->plan[j];
-        const bool local = j < nloc;                 // before the gather
+        const bool local = j < gather_round;         // before the gather
         const int end = local ? nloc : n;            // eq variables of this stage end here
         const int v = end - 1 - j;
         const int blocks = local ? K : 1;
@@ -639,17 +648,18 @@ static int fold_all(sc_ctx *ctx) {
     return SC_OK;
 }
 
-// Gather every rank's one entry per table into tables of WORLD entries, alike on every rank.
+// Gather every rank's slice of each table into whole tables, alike on every rank (rank k holds
+// entries [k N/W, (k+1) N/W), so the slices in rank order are the table).
 static int gather_tables(sc_ctx *ctx) {
     const int D = ctx->D;
     for (int s = 0; s < ctx->ntables; s++) {
         TableState &t = ctx->tab[s];
-        if (t.cur_entries != 1) return fail(ctx, SC_ESTATE, "gather with %llu entries per rank", (unsigned long long)t.cur_entries);
-        const int words = t.cur_base ? 1 : D;
-        if (!ctx->d_gtab[s]) { int rc = dev_alloc(ctx, (void **)&ctx->d_gtab[s], (u64)ctx->world * 8 * 4); if (rc) return rc; }
+        const u64 words = t.cur_entries * (u64)(t.cur_base ? 1 : D);
+        int rc = ensure(ctx, &ctx->d_gtab[s], &ctx->gtab_cap[s], (u64)ctx->world * words * 4);
+        if (rc) return rc;
         ncclResult_t r = g_nccl.AllGather(t.cur, ctx->d_gtab[s], (size_t)words, NCCL_UINT32, ctx->comm, ctx->stream);
         if (r) return fail(ctx, SC_ECOMM, "ncclAllGather: %s", g_nccl.GetErrorString(r));
-        t.cur = ctx->d_gtab[s]; t.cur_buf = -1; t.cur_entries = (u64)ctx->world;
+        t.cur = ctx->d_gtab[s]; t.cur_buf = -1; t.cur_entries *= (u64)ctx->world;
     }
     return SC_OK;
 }
@@ -665,11 +675,11 @@ extern "C" int sc_round(sc_ctx *ctx, uint32_t *sums) {
     const int D = ctx->D, j = ctx->j, W = ctx->points * D;
     if (!round_supported(D, ctx->points, ctx->nt_used)) return fail(ctx, SC_EUNSUPPORTED, "no kernel for D=%d points=%d tables=%d", D, ctx->points, ctx->nt_used);
     int rc;
-    if (ctx->world > 1 && j == ctx->nloc) {   // the tables are down to one entry per rank: gather them
+    if (ctx->world > 1 && j == ctx->gather_round) {   // the slices are small: gather them, every rank goes on alike
         if (ctx->have_r && (rc = fold_all(ctx))) return rc;
         if ((rc = gather_tables(ctx))) return rc;
     }
-    const bool local = ctx->world > 1 && j < ctx->nloc;
+    const bool local = ctx->world > 1 && j < ctx->gather_round;
     const bool fold = ctx->have_r;
     const RoundPlan &pl = ctx->plan[j];
 

@@ -22,6 +22,7 @@ CASES = [
     (4, 9, "(* t0 t1 t2)", [1, 1, 1], [], True),
     (8, 7, "(+ (* alpha t0 t1) (* 3 t1) -2)", [0, 1], ["alpha"], False),
     (4, 3, "(* t0 t1)", [0, 0], [], True),
+    (4, 17, "(+ (* t0 t3) (* t1 t2) (* lam t2 t3))", [1, 1, 0, 0], ["lam"], True),   # sharded rounds before the gather
 ]
 
 

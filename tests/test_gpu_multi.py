@@ -18,12 +18,15 @@ def gpu_count():
     return torch.cuda.device_count()
 
 
-@pytest.mark.parametrize("world", [2, 4, 8])
-def test_sharded_proof_equals_the_oracle(world):
+@pytest.mark.parametrize("world,gather_bits", [(2, None), (2, 0), (4, None), (8, 2)])
+def test_sharded_proof_equals_the_oracle(world, gather_bits):
+    # gather_bits: the slice size (log2) at which the ranks gather their tables; 0 keeps every round but the last sharded
     if gpu_count() < world:
         pytest.skip("needs %d GPUs" % world)
     with tempfile.TemporaryDirectory() as tmp:
         env = dict(os.environ, NCCL_NVLS_ENABLE="0")
+        if gather_bits is not None:
+            env["SABLE_B200_GATHER_BITS"] = str(gather_bits)
         procs = [subprocess.Popen([sys.executable, os.path.join(ROOT, "tests", "multi_gpu_worker.py"), str(r), str(world),
                                    os.path.join(tmp, "id"), os.path.join(tmp, "out%d.json" % r)], env=env,
                                   stdout=subprocess.PIPE, stderr=subprocess.STDOUT, text=True) for r in range(world)]
