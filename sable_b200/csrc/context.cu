@@ -125,6 +125,12 @@ struct sc_ctx {
     u64 gtab_cap[SC_MAX_TABLES] = {0};
     int grid_cap = 0;
 
+    // the resident kernel of the last rounds (see TailArgs)
+    u32 *h_tail = nullptr, *h_tail_dev = nullptr;   // mapped host memory and its device alias
+    bool tail_active = false;
+    int tail_first = 0, tail_rounds = 0, tail_bits = 12;
+    u32 tail_seq = 0;
+
     // timing
     bool timing = false;
     std::vector<cudaEvent_t> ev;
@@ -175,6 +181,33 @@ template <class T> static int ensure(sc_ctx *ctx, T **p, u64 *cap, u64 bytes) {
     return SC_OK;
 }
 
+// Make the resident kernel of the last rounds return (it polls this word), and wait for it.
+static void tail_stop(sc_ctx *ctx) {
+    if (!ctx->tail_active) return;
+    *(volatile u32 *)(ctx->h_tail + TAIL_STOP) = ctx->tail_seq;
+    std::atomic_thread_fence(std::memory_order_seq_cst);
+    cudaStreamSynchronize(ctx->stream);
+    ctx->tail_active = false;
+}
+
+// Wait until a word of mapped memory holds WANT.  Bounded: the stream finishing without the word
+// showing, or 30 seconds passing, ends the wait.
+static bool wait_word(sc_ctx *ctx, const u32 *word, u32 want) {
+    volatile const u32 *w = word;
+    const auto t0 = std::chrono::steady_clock::now();
+    for (u64 spin = 0;; spin++) {
+        if (*w == want) { std::atomic_thread_fence(std::memory_order_acquire); return true; }
+        if ((spin & 0xfff) == 0xfff) {
+            if (cudaStreamQuery(ctx->stream) != cudaErrorNotReady) {
+                cudaStreamSynchronize(ctx->stream);
+                std::atomic_thread_fence(std::memory_order_acquire);
+                return *w == want;
+            }
+            if (std::chrono::steady_clock::now() - t0 > std::chrono::seconds(30)) return false;
+        }
+    }
+}
+
 extern "C" const char *sc_strerror(int code) {
     switch (code) {
     case SC_OK: return "ok";
@@ -212,7 +245,11 @@ extern "C" int sc_create(int device, sc_ctx **out) {
               cudaMalloc(&ctx->d_out, MAX_PARTIAL_WORDS * 4) == cudaSuccess &&
               cudaHostAlloc(&ctx->h_out, (MAX_PARTIAL_WORDS + 32) * 4, cudaHostAllocMapped) == cudaSuccess &&
               cudaHostGetDevicePointer(&ctx->h_out_dev, ctx->h_out, 0) == cudaSuccess;
+    ok = ok && cudaHostAlloc(&ctx->h_tail, TAIL_WORDS * 4, cudaHostAllocMapped) == cudaSuccess &&
+         cudaHostGetDevicePointer(&ctx->h_tail_dev, ctx->h_tail, 0) == cudaSuccess;
     if (!ok) { cudaGetLastError(); sc_destroy(ctx); return SC_ECUDA; }
+    memset(ctx->h_tail, 0, TAIL_WORDS * 4);
+    if (const char *env = getenv("SABLE_B200_TAIL_BITS")) ctx->tail_bits = std::max(0, std::min(14, atoi(env)));
     *out = ctx;
     return SC_OK;
 }
@@ -220,7 +257,9 @@ extern "C" int sc_create(int device, sc_ctx **out) {
 extern "C" int sc_destroy(sc_ctx *ctx) {
     if (!ctx) return SC_OK;
     cudaSetDevice(ctx->device);
+    tail_stop(ctx);
     if (ctx->stream) cudaStreamSynchronize(ctx->stream);
+    if (ctx->h_tail) cudaFreeHost(ctx->h_tail);
     if (ctx->comm && g_nccl.CommDestroy) g_nccl.CommDestroy(ctx->comm);
     for (auto &t : ctx->tab) { cudaFree(t.t0); cudaFree(t.buf[0]); cudaFree(t.buf[1]); }
     for (auto p : ctx->d_gtab) cudaFree(p);
@@ -292,6 +331,7 @@ static u32 pow_r(int k) {
 extern "C" int sc_set_statement(sc_ctx *ctx, int D, int points, int ntables, int nterms, const uint32_t *coeffs,
                                 const int32_t *term_ptr, const int32_t *term_tables) {
     if (!ctx) return SC_EINVAL;
+    tail_stop(ctx);
     if (D != 4 && D != 8) return fail(ctx, SC_EINVAL, "extension degree %d: expected 4 or 8", D);
     if (points < 1) return fail(ctx, SC_EINVAL, "points %d: expected at least 1", points);
     if (ntables < 1 || nterms < 0 || (nterms && (!coeffs || !term_ptr))) return fail(ctx, SC_EINVAL, "bad term table");
@@ -421,6 +461,7 @@ static int table_slot(sc_ctx *ctx, int slot, uint64_t entries, int stride) {
     if (stride != 1 && stride != 4 && stride != 8) return fail(ctx, SC_EINVAL, "stride %d: expected 1 or the extension degree", stride);
     if (entries == 0) return fail(ctx, SC_EINVAL, "empty table");
     cudaSetDevice(ctx->device);
+    tail_stop(ctx);
     TableState &t = ctx->tab[slot];
     int rc = ensure(ctx, &t.t0, &t.t0_cap, entries * (u64)stride * 4);
     if (rc) return rc;
@@ -493,6 +534,7 @@ extern "C" int sc_download_table(sc_ctx *ctx, int slot, uint32_t *host, uint64_t
     if (!ctx || slot < 0 || slot >= SC_MAX_TABLES || !ctx->D) return SC_EINVAL;
     TableState &t = ctx->tab[slot];
     if (!t.t0) return fail(ctx, SC_ESTATE, "table %d was never uploaded", slot);
+    if (ctx->tail_active) return fail(ctx, SC_ESTATE, "the last rounds are running on the device: the folded tables are not available");
     cudaSetDevice(ctx->device);
     if (!ctx->begun) { t.cur = t.t0; t.cur_base = t.stride == 1; t.cur_entries = t.entries; t.cur_buf = -1; }
     if (entries) *entries = t.cur_entries;
@@ -517,6 +559,7 @@ static int split_bits(int D, int v) {
 extern "C" int sc_begin(sc_ctx *ctx, int n, const uint32_t *eq, int K, const uint32_t *block_weights) {
     if (!ctx) return SC_EINVAL;
     if (!ctx->have_statement) return fail(ctx, SC_ESTATE, "sc_begin before sc_set_statement");
+    tail_stop(ctx);
     if (n < 0 || n > 40) return fail(ctx, SC_EINVAL, "n = %d", n);
     if (block_weights && K < 1) return fail(ctx, SC_EINVAL, "K = %d block weights", K);
     if (!block_weights) K = 1;
@@ -664,6 +707,74 @@ static int gather_tables(sc_ctx *ctx) {
     return SC_OK;
 }
 
+// The last rounds run in one resident launch when the tables are small, there is one block of
+// weights, and nobody asked for per-round timing.
+static bool tail_wanted(const sc_ctx *ctx) {
+    if (ctx->tail_bits <= 0 || ctx->K != 1 || ctx->timing || ctx->ntables < 1) return false;
+    if (ctx->n - ctx->j > TAIL_MAX_ROUNDS) return false;
+    return ctx->tab[ctx->order[0]].cur_entries <= (1ull << ctx->tail_bits);
+}
+
+static int tail_start(sc_ctx *ctx) {
+    const int D = ctx->D, j = ctx->j;
+    TailArgs a;
+    memset(&a, 0, sizeof a);
+    a.ntables = ctx->ntables;
+    a.nrounds = ctx->n - j;
+    u64 entries = 0;
+    for (int k = 0; k < ctx->ntables; k++) {
+        TableState &t = ctx->tab[ctx->order[k]];
+        entries = t.cur_entries;
+        a.src[k] = t.cur; a.src_base[k] = t.cur_base;
+        // the folded tables alternate between the two buffers, starting with the one the source is not in
+        const int first = t.cur_buf == 0 ? 1 : 0;
+        for (int b = 0; b < 2; b++) { int rc = ensure(ctx, &t.buf[b], &t.buf_cap[b], std::max<u64>(entries / 2, 1) * D * 4); if (rc) return rc; }
+        if (t.cur_buf >= 0 && t.buf_cap[t.cur_buf] == 0) return fail(ctx, SC_ESTATE, "table buffer lost");
+        a.src[k] = t.cur_buf >= 0 ? t.buf[t.cur_buf] : t.cur;
+        a.buf[0][k] = t.buf[first]; a.buf[1][k] = t.buf[first ^ 1];
+    }
+    for (int k = 0; k < a.nrounds; k++) {
+        const RoundPlan &pl = ctx->plan[j + k];
+        if (pl.logL != 0 || pl.use_low) return fail(ctx, SC_ESTATE, "a split round in the tail");
+        a.rd[k].npairs = entries >> (k + 2);
+        a.rd[k].high_word = pl.high_word;
+        a.rd[k].use_high = pl.use_high;
+    }
+    challenge_words(ctx, a.r);
+    a.weights = ctx->d_weights;
+    a.st = ctx->st;
+    a.use_post = ctx->st_e > 0 || ctx->use_factor;
+    for (int c = 0; c < D; c++) a.post[c] = ctx->use_factor ? mmul(to_mont(ctx->st_factor[c]), ctx->st_re) : (c == 0 ? ctx->st_re : 0u);
+    ctx->tail_seq = ctx->seq + 1;
+    ctx->seq += TAIL_MAX_ROUNDS + 2;
+    a.seq = ctx->tail_seq;
+    a.host = ctx->h_tail_dev;
+    ((volatile u32 *)ctx->h_tail)[TAIL_STATUS] = 0;
+    std::atomic_thread_fence(std::memory_order_seq_cst);
+    CU(launch_tail(D, ctx->shape, ctx->points, ctx->nt_used, a, ctx->stream));
+    ctx->launches++;
+    ctx->tail_active = true;
+    ctx->tail_first = j;
+    ctx->tail_rounds = a.nrounds;
+    ctx->have_r = false;
+    return SC_OK;
+}
+
+// A round of the resident kernel: wait for its sums to be posted.
+static int tail_round(sc_ctx *ctx, uint32_t *sums) {
+    const int k = ctx->j - ctx->tail_first;
+    const u32 *slot = ctx->h_tail + (size_t)k * TAIL_SLOT_WORDS;
+    if (!wait_word(ctx, slot + 32, ctx->tail_seq + (u32)k)) {
+        ctx->tail_active = false;
+        ctx->begun = false;
+        return fail(ctx, SC_ESTATE, "the device stopped waiting for a challenge (status %u)", ctx->h_tail[TAIL_STATUS]);
+    }
+    memcpy(sums, slot, (size_t)ctx->points * ctx->D * 4);
+    ctx->have_r = false;
+    ctx->j++;
+    return SC_OK;
+}
+
 extern "C" int sc_round(sc_ctx *ctx, uint32_t *sums) {
     if (!ctx || !sums) return SC_EINVAL;
     if (!ctx->begun) return fail(ctx, SC_ESTATE, "sc_round before sc_begin");
@@ -673,6 +784,7 @@ extern "C" int sc_round(sc_ctx *ctx, uint32_t *sums) {
     const auto tr0 = std::chrono::steady_clock::now();
     cudaSetDevice(ctx->device);
     const int D = ctx->D, j = ctx->j, W = ctx->points * D;
+    if (ctx->tail_active) return tail_round(ctx, sums);
     if (!round_supported(D, ctx->points, ctx->nt_used)) return fail(ctx, SC_EUNSUPPORTED, "no kernel for D=%d points=%d tables=%d", D, ctx->points, ctx->nt_used);
     int rc;
     if (ctx->world > 1 && j == ctx->gather_round) {   // the slices are small: gather them, every rank goes on alike
@@ -682,6 +794,10 @@ extern "C" int sc_round(sc_ctx *ctx, uint32_t *sums) {
     const bool local = ctx->world > 1 && j < ctx->gather_round;
     const bool fold = ctx->have_r;
     const RoundPlan &pl = ctx->plan[j];
+    if (fold && !local && tail_wanted(ctx)) {
+        if ((rc = tail_start(ctx))) return rc;
+        return tail_round(ctx, sums);
+    }
 
     RoundArgs a;
     memset(&a, 0, sizeof a);
@@ -803,6 +919,13 @@ extern "C" int sc_challenge(sc_ctx *ctx, const uint32_t *r) {
     if (ctx->have_r) return fail(ctx, SC_ESTATE, "round %d already has its challenge", ctx->j - 1);
     for (int c = 0; c < ctx->D; c++) ctx->r[c] = r[c] % P;
     ctx->have_r = true;
+    if (ctx->tail_active) {   // hand the challenge to the resident kernel: the words first, then the word it polls
+        u32 *slot = ctx->h_tail + (size_t)(ctx->j - 1 - ctx->tail_first) * TAIL_SLOT_WORDS;
+        for (int c = 0; c < ctx->D; c++) ((volatile u32 *)slot)[40 + c] = ctx->r[c];
+        std::atomic_thread_fence(std::memory_order_seq_cst);
+        ((volatile u32 *)slot)[48] = ctx->tail_seq + (u32)(ctx->j - 1 - ctx->tail_first);
+        std::atomic_thread_fence(std::memory_order_seq_cst);
+    }
     return SC_OK;
 }
 
@@ -813,6 +936,17 @@ extern "C" int sc_finish(sc_ctx *ctx, uint32_t *folded) {
     if (ctx->n > 0 && !ctx->have_r) return fail(ctx, SC_ESTATE, "the last round has no challenge");
     cudaSetDevice(ctx->device);
     int rc;
+    if (ctx->tail_active) {   // the resident kernel folds by the last challenge and posts the final entries
+        const bool ok = wait_word(ctx, ctx->h_tail + TAIL_FINALS - 1, ctx->tail_seq);
+        CU(cudaStreamSynchronize(ctx->stream));
+        ctx->tail_active = false;
+        ctx->begun = false;
+        if (!ok) return fail(ctx, SC_ESTATE, "the device stopped waiting for a challenge (status %u)", ctx->h_tail[TAIL_STATUS]);
+        if (folded)
+            for (int k = 0; k < ctx->ntables; k++)
+                memcpy(folded + (size_t)ctx->order[k] * ctx->D, ctx->h_tail + TAIL_FINALS + (size_t)k * ctx->D, 4 * (size_t)ctx->D);
+        return SC_OK;
+    }
     if (ctx->n > 0 && (rc = fold_all(ctx))) return rc;
     if (folded && ctx->ntables) {
         int slots[SC_MAX_TABLES];

@@ -84,6 +84,45 @@ bool round_supported(int D, int points, int nt_used);
 cudaError_t launch_round_base(int D, int points, int nt_used, int ngroups, const RoundArgs &args, int grid, size_t smem,
                               cudaStream_t stream);
 
+// The last rounds in one launch.  Once the tables are small a round is all latency (launch,
+// completion, the trip to the host and back), so a single block runs every remaining round and
+// talks to the host through mapped memory: it posts a round's sums, waits -- a bounded number of
+// polls -- for the challenge the host's transcript derives from them, folds, and goes on; after
+// the last challenge it folds once more and posts the final entries.  The transcript stays on
+// the host.  Slot k of the mapped buffer (TAIL_SLOT_WORDS words) belongs to round k of the launch:
+//   [0, 32) sums   [32] posted = seq + k   [40, 48) challenge (canonical)   [48] sent = seq + k
+// word TAIL_STATUS of the buffer: 0 running, 1 finished, 2 gave up waiting, 3 told to stop;
+// word TAIL_STOP: the host sets it to seq to make the kernel return at its next poll;
+// the final entries (ntables * D words) start at word TAIL_FINALS, posted at TAIL_FINALS - 1.
+constexpr int TAIL_MAX_ROUNDS = 16;
+constexpr int TAIL_SLOT_WORDS = 64;
+constexpr int TAIL_STATUS = TAIL_MAX_ROUNDS * TAIL_SLOT_WORDS;
+constexpr int TAIL_STOP = TAIL_STATUS + 1;
+constexpr int TAIL_FINALS = TAIL_STATUS + 16;
+constexpr int TAIL_WORDS = TAIL_FINALS + SC_MAX_TABLES * 8;
+constexpr unsigned TAIL_POLL_LIMIT = 4000000u;   // polls of mapped host memory (about a microsecond each) before giving up
+struct TailRound {
+    u64 npairs;
+    u64 high_word;     // offset of the round's weights in the weights buffer
+    int use_high;
+};
+struct TailArgs {
+    const u32 *src[SC_MAX_TABLES];     // the tables the first round of the launch reads (4 entries per pair)
+    u32 *buf[2][SC_MAX_TABLES];        // the folded tables go to buf[0], buf[1], buf[0], ..
+    uint8_t src_base[SC_MAX_TABLES];
+    int ntables;
+    int nrounds;
+    TailRound rd[TAIL_MAX_ROUNDS];
+    u32 r[8];                          // the challenge of the round before the launch, Montgomery form
+    const u32 *weights;
+    DevStatement st;
+    u32 post[8];
+    int use_post;
+    u32 seq;
+    u32 *host;                         // the mapped buffer (device address)
+};
+cudaError_t launch_tail(int D, int shape, int points, int nt_used, const TailArgs &args, cudaStream_t stream);
+
 // Stand-alone fold of NTABLES tables: dst entry i = src[2i] + r (src[2i+1] - src[2i]).
 struct FoldArgs {
     const u32 *src[SC_MAX_TABLES];

@@ -21,6 +21,9 @@
 #ifndef SC_MINBLOCKS
 #define SC_MINBLOCKS 2
 #endif
+#ifndef SC_MINBLOCKS_R0
+#define SC_MINBLOCKS_R0 2
+#endif
 #ifndef SC_PREFETCH
 #define SC_PREFETCH 0
 #endif
@@ -150,7 +153,7 @@ __device__ __forceinline__ Ext<D> eval_gkr(const Ext<D> (&val)[4], const ExtM<D>
 }
 
 template <int D, int PTS, int NT, bool FOLD, int SHAPE>
-__global__ void __launch_bounds__(ROUND_THREADS, SC_MINBLOCKS) round_kernel(const __grid_constant__ RoundArgs a) {
+__global__ void __launch_bounds__(ROUND_THREADS, FOLD ? SC_MINBLOCKS : SC_MINBLOCKS_R0) round_kernel(const __grid_constant__ RoundArgs a) {
     extern __shared__ __align__(16) u32 smem[];
     __shared__ u32 red[ROUND_THREADS / 32][PTS * D];
     __shared__ bool is_last;

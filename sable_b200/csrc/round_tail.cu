@@ -1,0 +1,210 @@
+// round_tail.cu -- the last rounds of a proof in one launch (see TailArgs in device.h).
+//
+// The arithmetic of a round is that of round_kernel with FOLD: entries 4i .. 4i+3 of every table
+// are folded by the last challenge into the pair (2i, 2i+1), written, and the statement is summed
+// over the pairs with the round's eq weights (one weight per pair: the tables are small, the
+// weights are not split).  What differs is that the block stays resident between rounds and gets
+// each challenge from the host through mapped memory, so a round costs a few microseconds
+// instead of a launch and a completion.  Every wait is bounded: a block that hears nothing for
+// TAIL_POLL_LIMIT polls, or is told to stop, records why and returns.
+#include "round_kernel.cuh"
+
+namespace sc {
+
+__device__ __forceinline__ u32 ld_sys(const u32 *p) {
+    u32 v;
+    asm volatile("ld.volatile.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+    return v;
+}
+__device__ __forceinline__ void st_sys(u32 *p, u32 v) { asm volatile("st.volatile.global.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory"); }
+
+template <int D, int PTS, int NT, int SHAPE>
+__global__ void __launch_bounds__(ROUND_THREADS) tail_kernel(const __grid_constant__ TailArgs a) {
+    __shared__ u32 red[ROUND_THREADS / 32][PTS * D];
+    __shared__ u32 chal[8];
+    __shared__ int go;
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    constexpr int W = PTS * D, ROWS = ROUND_THREADS / 32;
+
+    ExtM<D> lam;
+    if (SHAPE == SHAPE_GKR) {
+        Ext<D> c;
+#pragma unroll
+        for (int k = 0; k < D; k++) c.v[k] = a.st.terms[0].coeff[k];
+        lam = eprep<D>(c);
+    }
+    Ext<D> r;
+#pragma unroll
+    for (int c = 0; c < D; c++) r.v[c] = a.r[c];
+    ExtM<D> rm = eprep<D>(r);
+
+    for (int k = 0; k < a.nrounds; k++) {
+        const TailRound rd = a.rd[k];
+        const int out = k & 1;
+        Ext<D> total[PTS];
+#pragma unroll
+        for (int x = 0; x < PTS; x++) total[x] = ezero<D>();
+        for (u64 i = tid; i < rd.npairs; i += ROUND_THREADS) {
+            Ext<D> val[NT], slope[NT];
+            for (int t = 0; t < a.ntables; t++) {
+                const u32 *src = k == 0 ? a.src[t] : a.buf[out ^ 1][t];
+                Ext<D> lo, hi;
+                if (k == 0 && a.src_base[t]) {   // base entries: D base products (FOLD-FLAT-TABLE, src/sumcheck.lisp:95-98)
+                    const uint4 w = *reinterpret_cast<const uint4 *>(src + 4 * i);
+                    const u32 s0 = fsub(w.y, w.x), s1 = fsub(w.w, w.z);
+#pragma unroll
+                    for (int c = 0; c < D; c++) { lo.v[c] = mmul(rm.v[c], s0); hi.v[c] = mmul(rm.v[c], s1); }
+                    lo.v[0] = fadd(lo.v[0], w.x);
+                    hi.v[0] = fadd(hi.v[0], w.z);
+                } else {
+                    const u32 *e = src + 4 * i * D;
+                    const Ext<D> e0 = load_ext<D>(e), e1 = load_ext<D>(e + D), e2 = load_ext<D>(e + 2 * D), e3 = load_ext<D>(e + 3 * D);
+                    lo = eadd<D>(e0, emul<D>(esub<D>(e1, e0), rm));
+                    hi = eadd<D>(e2, emul<D>(esub<D>(e3, e2), rm));
+                }
+                u32 *dst = a.buf[out][t];
+                store_ext<D>(dst + (2 * i) * D, lo);
+                store_ext<D>(dst + (2 * i + 1) * D, hi);
+#pragma unroll
+                for (int u = 0; u < NT; u++)
+                    if (u == t) { val[u] = lo; slope[u] = esub<D>(hi, lo); }
+            }
+            Ext<D> sum[PTS];
+#pragma unroll
+            for (int x = 0; x < PTS; x++) {
+                if (x == 1) {
+#pragma unroll
+                    for (int t = 0; t < NT; t++) val[t] = eadd<D>(eadd<D>(val[t], slope[t]), slope[t]);
+                } else if (x > 1) {
+#pragma unroll
+                    for (int t = 0; t < NT; t++) val[t] = eadd<D>(val[t], slope[t]);
+                }
+                bool unused = false;
+                if (SHAPE == SHAPE_PRODUCT) sum[x] = eval_product<D, NT, false>(val, 0u, &unused);
+                else if (SHAPE == SHAPE_GKR) sum[x] = eval_gkr<D, false>(reinterpret_cast<const Ext<D>(&)[4]>(val), lam, 0u);
+                else sum[x] = eval_statement<D, NT, false>(a.st, val, 0u, &unused);
+            }
+            if (rd.use_high) {
+                const Ext<D> hw = *reinterpret_cast<const Ext<D> *>(a.weights + rd.high_word + i * D);
+                const ExtM<D> hm = eprep<D>(hw);
+#pragma unroll
+                for (int x = 0; x < PTS; x++) total[x] = eadd<D>(total[x], emul<D>(sum[x], hm));
+            } else {
+#pragma unroll
+                for (int x = 0; x < PTS; x++) total[x] = eadd<D>(total[x], sum[x]);
+            }
+        }
+        // the block's sums
+#pragma unroll
+        for (int x = 0; x < PTS; x++)
+#pragma unroll
+            for (int c = 0; c < D; c++) {
+                u32 v = total[x].v[c];
+#pragma unroll
+                for (int off = 16; off > 0; off >>= 1) v = fadd(v, __shfl_down_sync(0xffffffffu, v, off));
+                if (lane == 0) red[warp][x * D + c] = v;
+            }
+        __syncthreads();
+        u32 *slot = a.host + (size_t)k * TAIL_SLOT_WORDS;
+        if (tid < PTS) {
+            Ext<D> s;
+#pragma unroll
+            for (int c = 0; c < D; c++) {
+                u32 acc = red[0][tid * D + c];
+#pragma unroll
+                for (int w = 1; w < ROWS; w++) acc = fadd(acc, red[w][tid * D + c]);
+                s.v[c] = acc;
+            }
+            if (a.use_post) {
+                Ext<D> pf;
+#pragma unroll
+                for (int c = 0; c < D; c++) pf.v[c] = a.post[c];
+                s = emul<D>(s, pf);
+            }
+#pragma unroll
+            for (int c = 0; c < D; c++) slot[tid * D + c] = s.v[c];
+        }
+        __syncthreads();   // also: every store of the folded tables is done before the next round reads them
+        if (tid == 0) {
+            __threadfence_system();   // cumulative: the sums written before the barrier are visible before the word below
+            st_sys(slot + 32, a.seq + (u32)k);
+            // wait for the challenge, a bounded number of polls
+            int ok = 0;
+            for (unsigned poll = 0; poll < TAIL_POLL_LIMIT; poll++) {
+                if (ld_sys(slot + 48) == a.seq + (u32)k) { ok = 1; break; }
+                if ((poll & 63) == 63 && ld_sys(a.host + TAIL_STOP) == a.seq) { ok = -1; break; }
+            }
+            if (ok == 1) {
+#pragma unroll
+                for (int c = 0; c < D; c++) chal[c] = ld_sys(slot + 40 + c);
+            } else {
+                st_sys(a.host + TAIL_STATUS, ok == 0 ? 2u : 3u);
+            }
+            go = ok == 1;
+        }
+        __syncthreads();
+        if (!go) return;
+#pragma unroll
+        for (int c = 0; c < D; c++) r.v[c] = to_mont(chal[c]);
+        rm = eprep<D>(r);
+        __syncthreads();
+    }
+    // the last fold: one entry per table, posted to the host and left in the buffer the next round would read
+    {
+        const int last = (a.nrounds - 1) & 1;
+        if (tid < a.ntables) {
+            const u32 *e = a.buf[last][tid];
+            const Ext<D> e0 = load_ext<D>(e), e1 = load_ext<D>(e + D);
+            const Ext<D> f = eadd<D>(e0, emul<D>(esub<D>(e1, e0), rm));
+            store_ext<D>(a.buf[last ^ 1][tid], f);
+#pragma unroll
+            for (int c = 0; c < D; c++) a.host[TAIL_FINALS + tid * D + c] = f.v[c];
+            __threadfence_system();
+        }
+        __syncthreads();
+        if (tid == 0) {
+            __threadfence_system();
+            st_sys(a.host + TAIL_FINALS - 1, a.seq);
+            st_sys(a.host + TAIL_STATUS, 1u);
+        }
+    }
+}
+
+template <int D, int PTS, int NT, int SHAPE> static cudaError_t launch_tail_one(const TailArgs &args, cudaStream_t stream) {
+    tail_kernel<D, PTS, NT, SHAPE><<<1, ROUND_THREADS, 0, stream>>>(args);
+    return cudaGetLastError();
+}
+template <int D, int PTS> static cudaError_t launch_tail_dp(int nt, const TailArgs &args, cudaStream_t stream) {
+    switch (nt) {
+    case 1: return launch_tail_one<D, PTS, 1, SHAPE_GENERIC>(args, stream);
+    case 2: return launch_tail_one<D, PTS, 2, SHAPE_GENERIC>(args, stream);
+    case 3: return launch_tail_one<D, PTS, 3, SHAPE_GENERIC>(args, stream);
+    case 4: return launch_tail_one<D, PTS, 4, SHAPE_GENERIC>(args, stream);
+    default: return cudaErrorInvalidValue;
+    }
+}
+template <int D> static cudaError_t launch_tail_d(int shape, int points, int nt, const TailArgs &args, cudaStream_t stream) {
+    if (shape == SHAPE_GKR && points == 2 && nt == 4) return launch_tail_one<D, 2, 4, SHAPE_GKR>(args, stream);
+    if (shape == SHAPE_PRODUCT && points == nt) {
+        switch (nt) {
+        case 1: return launch_tail_one<D, 1, 1, SHAPE_PRODUCT>(args, stream);
+        case 2: return launch_tail_one<D, 2, 2, SHAPE_PRODUCT>(args, stream);
+        case 3: return launch_tail_one<D, 3, 3, SHAPE_PRODUCT>(args, stream);
+        case 4: return launch_tail_one<D, 4, 4, SHAPE_PRODUCT>(args, stream);
+        }
+    }
+    switch (points) {
+    case 1: return launch_tail_dp<D, 1>(nt, args, stream);
+    case 2: return launch_tail_dp<D, 2>(nt, args, stream);
+    case 3: return launch_tail_dp<D, 3>(nt, args, stream);
+    case 4: return launch_tail_dp<D, 4>(nt, args, stream);
+    default: return cudaErrorInvalidValue;
+    }
+}
+cudaError_t launch_tail(int D, int shape, int points, int nt_used, const TailArgs &args, cudaStream_t stream) {
+    if (D == 4) return launch_tail_d<4>(shape, points, nt_used, args, stream);
+    if (D == 8) return launch_tail_d<8>(shape, points, nt_used, args, stream);
+    return cudaErrorInvalidValue;
+}
+
+}  // namespace sc

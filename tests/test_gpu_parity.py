@@ -264,3 +264,38 @@ def test_memory_budget_is_enforced_on_the_host(prover):
         assert e.value.code == -3
     finally:
         p.close()
+
+
+@pytest.mark.parametrize("tail_bits", ["0", "6", "14"])
+def test_resident_last_rounds_match_round_per_launch(tail_bits, monkeypatch):
+    # the last rounds run in one resident launch fed by the host (SABLE_B200_TAIL_BITS: log2 of the table size
+    # it starts at; 0 turns it off): every setting gives the oracle's proof
+    monkeypatch.setenv("SABLE_B200_TAIL_BITS", tail_bits)
+    p = sb.Prover(0)
+    try:
+        for d, n, statement, nt, nc in ((4, 13, "(+ (* t0 t3) (* t1 t2) (* alpha t2 t3))", 4, 1), (8, 9, "(* t0 t1 t2)", 3, 0),
+                                        (4, 7, "(+ (* alpha t0 t1) (* 3 t1) -2)", 2, 1), (4, 1, "(* t0 t1)", 2, 0)):
+            rng = np.random.default_rng(n)
+            tables = [("t%d" % t, rng.integers(0, P, size=1 << n, dtype=np.uint32) if t % 2 == 0 else rand_ext(rng, d, 1 << n)) for t in range(nt)]
+            constants = [("alpha", rand_ext(rng, d).tolist())][:nc]
+            got, want, ta, tb = both(p, d, n, statement, tables, eq=rand_ext(rng, d, n), constants=constants)
+            assert_same(got, want, ta, tb)
+    finally:
+        p.close()
+
+
+def test_abandoned_proof_does_not_block_the_next(prover):
+    # a proof dropped in the middle of its last rounds: the next one starts cleanly
+    d, n = 4, 6
+    rng = np.random.default_rng(8)
+    tables = [("a", rand_ext(rng, d, 1 << n)), ("b", rand_ext(rng, d, 1 << n))]
+    degree, terms = sb.lower_statement("(* a b)", d, ["a", "b"])
+    prover.set_statement(d, 2, 2, terms)
+    for s, (_, t) in enumerate(tables):
+        prover.upload_table(s, t)
+    prover.begin(n)
+    prover.round()
+    prover.challenge([1, 2, 3, 4])
+    prover.round()          # the resident kernel now waits for a challenge that never comes
+    got, want, ta, tb = both(prover, d, n, "(* a b)", tables, eq=rand_ext(rng, d, n))
+    assert_same(got, want, ta, tb)
