@@ -5,13 +5,13 @@
 
 namespace sc {
 
-cudaError_t launch_round_d4(int shape, int points, int nt, bool fold, const RoundArgs &args, int grid, size_t smem, cudaStream_t stream);
-cudaError_t launch_round_d8(int shape, int points, int nt, bool fold, const RoundArgs &args, int grid, size_t smem, cudaStream_t stream);
+cudaError_t launch_round_d4(int shape, int points, int nt, int fold, const RoundArgs &args, int grid, size_t smem, cudaStream_t stream);
+cudaError_t launch_round_d8(int shape, int points, int nt, int fold, const RoundArgs &args, int grid, size_t smem, cudaStream_t stream);
 
 bool round_supported(int D, int points, int nt_used) {
     return (D == 4 || D == 8) && points >= 1 && points <= SC_MAX_POINTS && nt_used >= 1 && nt_used <= 4;
 }
-cudaError_t launch_round(int D, int shape, int points, int nt_used, bool fold, const RoundArgs &args, int grid, size_t smem, cudaStream_t stream) {
+cudaError_t launch_round(int D, int shape, int points, int nt_used, int fold, const RoundArgs &args, int grid, size_t smem, cudaStream_t stream) {
     if (D == 4) return launch_round_d4(shape, points, nt_used, fold, args, grid, smem, stream);
     if (D == 8) return launch_round_d8(shape, points, nt_used, fold, args, grid, smem, stream);
     return cudaErrorInvalidValue;

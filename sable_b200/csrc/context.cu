@@ -131,6 +131,13 @@ struct sc_ctx {
     int tail_first = 0, tail_rounds = 0, tail_bits = 12;
     u32 tail_seq = 0;
 
+    // the first two rounds from one pass over base tables (see SvArgs)
+    bool sv_ok = false;
+    u32 sv_A[SV_MAX_WORDS];          // the accumulators, canonical
+    u32 sv_rho0[8];
+    u32 eq1[8];                      // eq element 1, canonical (the weight of variable 1 in round 0's message)
+    u32 *h_sv = nullptr, *h_sv_dev = nullptr;
+
     // timing
     bool timing = false;
     std::vector<cudaEvent_t> ev;
@@ -249,6 +256,9 @@ extern "C" int sc_create(int device, sc_ctx **out) {
          cudaHostGetDevicePointer(&ctx->h_tail_dev, ctx->h_tail, 0) == cudaSuccess;
     if (!ok) { cudaGetLastError(); sc_destroy(ctx); return SC_ECUDA; }
     memset(ctx->h_tail, 0, TAIL_WORDS * 4);
+    if (cudaHostAlloc(&ctx->h_sv, (SV_MAX_WORDS + 32) * 4, cudaHostAllocMapped) != cudaSuccess ||
+        cudaHostGetDevicePointer(&ctx->h_sv_dev, ctx->h_sv, 0) != cudaSuccess) { cudaGetLastError(); sc_destroy(ctx); return SC_ECUDA; }
+    memset(ctx->h_sv, 0, (SV_MAX_WORDS + 32) * 4);
     if (const char *env = getenv("SABLE_B200_TAIL_BITS")) ctx->tail_bits = std::max(0, std::min(14, atoi(env)));
     *out = ctx;
     return SC_OK;
@@ -260,6 +270,7 @@ extern "C" int sc_destroy(sc_ctx *ctx) {
     tail_stop(ctx);
     if (ctx->stream) cudaStreamSynchronize(ctx->stream);
     if (ctx->h_tail) cudaFreeHost(ctx->h_tail);
+    if (ctx->h_sv) cudaFreeHost(ctx->h_sv);
     if (ctx->comm && g_nccl.CommDestroy) g_nccl.CommDestroy(ctx->comm);
     for (auto &t : ctx->tab) { cudaFree(t.t0); cudaFree(t.buf[0]); cudaFree(t.buf[1]); }
     for (auto p : ctx->d_gtab) cudaFree(p);
@@ -652,6 +663,16 @@ extern "C" int sc_begin(sc_ctx *ctx, int n, const uint32_t *eq, int K, const uin
     }
     // the host vectors above must outlive the copies
     CU(cudaStreamSynchronize(ctx->stream));
+    // rounds 0 and 1 from one pass, tables bound to both challenges on the way into round 2: a product of
+    // base tables, large enough for split weights, on one GPU, one block
+    {
+        const char *env = getenv("SABLE_B200_SMALL_VALUES");
+        bool ok = !(env && env[0] == '0') && ctx->shape == SHAPE_PRODUCT && ctx->world == 1 && K == 1 && n >= 3 &&
+                  small_values_supported(D, ctx->points + 1, ctx->nt_used) && ctx->plan[1].logL >= 8;
+        for (int s = 0; s < ctx->ntables && ok; s++) ok = ctx->tab[s].stride == 1;
+        ctx->sv_ok = ok;
+        if (ok && eq) for (int c = 0; c < D; c++) ctx->eq1[c] = eq[D + c] % P;
+    }
     ctx->begun = true;
     return SC_OK;
 }
@@ -704,6 +725,101 @@ static int gather_tables(sc_ctx *ctx) {
         if (r) return fail(ctx, SC_ECOMM, "ncclAllGather: %s", g_nccl.GetErrorString(r));
         t.cur = ctx->d_gtab[s]; t.cur_buf = -1; t.cur_entries *= (u64)ctx->world;
     }
+    return SC_OK;
+}
+
+// ---- host arithmetic on canonical F_p^4 elements, for the handful of products the small-value rounds need
+namespace {
+struct E4 { u32 v[4]; };
+E4 e4_mul(const E4 &a, const E4 &b) {   // REDC(a * bR) = a b
+    Ext<4> x, y;
+    for (int c = 0; c < 4; c++) { x.v[c] = a.v[c]; y.v[c] = to_mont(b.v[c]); }
+    const Ext<4> z = emul<4>(x, y);
+    E4 o; for (int c = 0; c < 4; c++) o.v[c] = z.v[c];
+    return o;
+}
+E4 e4_add(const E4 &a, const E4 &b) { E4 o; for (int c = 0; c < 4; c++) o.v[c] = fadd(a.v[c], b.v[c]); return o; }
+E4 e4_sub(const E4 &a, const E4 &b) { E4 o; for (int c = 0; c < 4; c++) o.v[c] = fsub(a.v[c], b.v[c]); return o; }
+E4 e4_base(u32 x) { E4 o = {{x, 0, 0, 0}}; return o; }
+E4 e4_scale(const E4 &a, u32 s) { E4 o; for (int c = 0; c < 4; c++) o.v[c] = (u32)(((u64)a.v[c] * s) % P); return o; }
+u32 fp_inv(u32 a) { u64 r = 1, x = a; for (u64 e = P - 2; e; e >>= 1) { if (e & 1) r = r * x % P; x = x * x % P; } return (u32)r; }
+}  // namespace
+
+// Round 0 of the small-value rounds: the pass over the tables, then g_0(X) = sum_u eq(r_1, u) A[X, u]
+// (SMALL-VALUE-SUMS with j = 0, src/sumcheck.lisp:481-494).
+static int sv_round0(sc_ctx *ctx, uint32_t *sums) {
+    const int D = ctx->D, G = ctx->points + 1, Z = G * G;
+    const RoundPlan &pl = ctx->plan[1];   // the weights of round 1 cover the variables 2 .. n-1: those of the blocks
+    SvArgs a;
+    memset(&a, 0, sizeof a);
+    u64 bytes = 0;
+    for (int k = 0; k < ctx->nt_used; k++) { a.src[k] = ctx->tab[ctx->order[k]].t0; bytes += ctx->tab[ctx->order[k]].entries * 4; }
+    a.nblocks = ctx->tab[ctx->order[0]].entries / 4;
+    a.logL = pl.logL; a.use_low = pl.use_low; a.use_high = pl.use_high;
+    a.low = ctx->d_weights + pl.low_word; a.high = ctx->d_weights + pl.high_word;
+    a.use_post = ctx->st_e > 0 || ctx->use_factor;
+    for (int c = 0; c < D; c++) a.post[c] = ctx->use_factor ? mmul(to_mont(ctx->st_factor[c]), ctx->st_re) : (c == 0 ? ctx->st_re : 0u);
+    a.partials = ctx->d_partials; a.counter = ctx->d_counter;
+    a.out_host = ctx->h_sv_dev; a.seq = ++ctx->seq;
+    const u32 lchunks = (1u << a.logL) / ROUND_THREADS;
+    const u64 NH = a.nblocks >> a.logL;
+    u64 nhg = std::max<u64>(1, (u64)ctx->sms / lchunks);
+    if (nhg > NH) nhg = NH;
+    const int grid = (int)(lchunks * nhg);
+    if (ctx->timing) {
+        while (ctx->ev.size() < 2) { cudaEvent_t e; CU(cudaEventCreate(&e)); ctx->ev.push_back(e); }
+        CU(cudaEventRecord(ctx->ev[0], ctx->stream));
+    }
+    CU(launch_small_values(D, G, ctx->nt_used, a, grid, ctx->stream));
+    ctx->launches++;
+    if (ctx->timing) CU(cudaEventRecord(ctx->ev[1], ctx->stream));
+    if (!wait_word(ctx, ctx->h_sv + SV_FLAG, a.seq)) { CU(cudaStreamSynchronize(ctx->stream)); return fail(ctx, SC_ECUDA, "the small-value pass did not finish"); }
+    if (ctx->timing) {
+        CU(cudaStreamSynchronize(ctx->stream));
+        sc_round_stat st; CU(cudaEventElapsedTime(&st.kernel_ms, ctx->ev[0], ctx->ev[1]));
+        st.bytes = bytes; st.pairs = a.nblocks * 2;
+        ctx->stats.push_back(st);
+    }
+    memcpy(ctx->sv_A, ctx->h_sv, (size_t)Z * D * 4);
+    const E4 *A = reinterpret_cast<const E4 *>(ctx->sv_A);
+    E4 w0 = e4_base(1), w1 = e4_base(1);
+    if (ctx->have_eq) { E4 r1; memcpy(r1.v, ctx->eq1, 16); w1 = r1; w0 = e4_sub(e4_base(1), r1); }
+    for (int xi = 0; xi < ctx->points; xi++) {
+        const int X = xi ? xi + 1 : 0;
+        const E4 g = e4_add(e4_mul(A[X], w0), e4_mul(A[X + G], w1));
+        memcpy(sums + (size_t)xi * D, g.v, 16);
+    }
+    ctx->have_r = false;
+    ctx->j = 1;
+    return SC_OK;
+}
+
+// Round 1: g_1(X) = sum_v L_v(rho_0) A[v, X], L_v the Lagrange basis on the nodes 0 .. d (LAGRANGE-TENSOR, :463-474).
+static int sv_round1(sc_ctx *ctx, uint32_t *sums) {
+    const int D = ctx->D, G = ctx->points + 1, d = ctx->points;
+    E4 rho; memcpy(rho.v, ctx->r, 16);
+    memcpy(ctx->sv_rho0, ctx->r, 16);
+    const E4 *A = reinterpret_cast<const E4 *>(ctx->sv_A);
+    E4 L[8];
+    for (int v = 0; v <= d; v++) {
+        E4 num = e4_base(1);
+        u32 den = 1;
+        for (int j = 0; j <= d; j++) {
+            if (j == v) continue;
+            num = e4_mul(num, e4_sub(rho, e4_base((u32)j)));
+            den = (u32)(((u64)den * (u32)((v - j + (long long)P) % P)) % P);
+        }
+        L[v] = e4_scale(num, fp_inv(den));
+    }
+    for (int xi = 0; xi < ctx->points; xi++) {
+        const int X = xi ? xi + 1 : 0;
+        E4 g = e4_base(0);
+        for (int v = 0; v <= d; v++) g = e4_add(g, e4_mul(A[v + G * X], L[v]));
+        memcpy(sums + (size_t)xi * D, g.v, 16);
+    }
+    if (ctx->timing) { sc_round_stat st; st.kernel_ms = 0; st.bytes = 0; st.pairs = 0; ctx->stats.push_back(st); }
+    ctx->have_r = false;
+    ctx->j = 2;
     return SC_OK;
 }
 
@@ -785,6 +901,9 @@ extern "C" int sc_round(sc_ctx *ctx, uint32_t *sums) {
     cudaSetDevice(ctx->device);
     const int D = ctx->D, j = ctx->j, W = ctx->points * D;
     if (ctx->tail_active) return tail_round(ctx, sums);
+    if (ctx->sv_ok && j == 0) return sv_round0(ctx, sums);
+    if (ctx->sv_ok && j == 1) return sv_round1(ctx, sums);
+    const bool bind2 = ctx->sv_ok && j == 2;   // round 2 reads the base tables and binds both challenges on the way in
     if (!round_supported(D, ctx->points, ctx->nt_used)) return fail(ctx, SC_EUNSUPPORTED, "no kernel for D=%d points=%d tables=%d", D, ctx->points, ctx->nt_used);
     int rc;
     if (ctx->world > 1 && j == ctx->gather_round) {   // the slices are small: gather them, every rank goes on alike
@@ -793,6 +912,7 @@ extern "C" int sc_round(sc_ctx *ctx, uint32_t *sums) {
     }
     const bool local = ctx->world > 1 && j < ctx->gather_round;
     const bool fold = ctx->have_r;
+    const int shrink = bind2 ? 4 : 2;   // entries in per entry out of the fold
     const RoundPlan &pl = ctx->plan[j];
     if (fold && !local && tail_wanted(ctx)) {
         if ((rc = tail_start(ctx))) return rc;
@@ -811,13 +931,19 @@ extern "C" int sc_round(sc_ctx *ctx, uint32_t *sums) {
         bytes += t.cur_entries * (u64)(t.cur_base ? 1 : D) * 4;
         if (fold) {
             const int nb = t.cur_buf == 0 ? 1 : 0;
-            if ((rc = ensure(ctx, &t.buf[nb], &t.buf_cap[nb], in_entries / 2 * D * 4))) return rc;
+            if ((rc = ensure(ctx, &t.buf[nb], &t.buf_cap[nb], in_entries / shrink * D * 4))) return rc;
             a.dst[k] = t.buf[nb];
-            bytes += in_entries / 2 * (u64)D * 4;
+            bytes += in_entries / shrink * (u64)D * 4;
         }
     }
-    a.npairs = fold ? in_entries / 4 : in_entries / 2;
+    a.npairs = fold ? in_entries / (2 * shrink) : in_entries / 2;
     if (fold) challenge_words(ctx, a.r);
+    if (bind2) {   // eq(rho0 rho1, b): bit 0 of b pairs with rho0 (EQ-TABLE, src/field.lisp:354-363)
+        E4 r0, r1; memcpy(r0.v, ctx->sv_rho0, 16); memcpy(r1.v, ctx->r, 16);
+        const E4 one = e4_base(1), n0 = e4_sub(one, r0), n1 = e4_sub(one, r1);
+        const E4 w[4] = {e4_mul(n0, n1), e4_mul(r0, n1), e4_mul(n0, r1), e4_mul(r0, r1)};
+        for (int b = 0; b < 4; b++) for (int c = 0; c < D; c++) a.bind[b][c] = to_mont(w[b].v[c]);
+    }
     a.logL = pl.logL;
     a.use_low = pl.use_low; a.use_high = pl.use_high;
     a.low = ctx->d_weights + pl.low_word;
@@ -859,7 +985,7 @@ extern "C" int sc_round(sc_ctx *ctx, uint32_t *sums) {
         memcpy(a.gcoef, ctx->gcoef, sizeof a.gcoef);
         CU(launch_round_base(D, ctx->points, ctx->nt_used, a.ngroups, a, grid, smem, ctx->stream));
     } else {
-        CU(launch_round(D, ctx->shape, ctx->points, ctx->nt_used, fold, a, grid, smem, ctx->stream));
+        CU(launch_round(D, ctx->shape, ctx->points, ctx->nt_used, bind2 ? 2 : (fold ? 1 : 0), a, grid, smem, ctx->stream));
     }
     ctx->launches++;
     if (ctx->timing) CU(cudaEventRecord(e1, ctx->stream));
@@ -905,7 +1031,7 @@ extern "C" int sc_round(sc_ctx *ctx, uint32_t *sums) {
         for (int k = 0; k < ctx->ntables; k++) {
             TableState &t = ctx->tab[ctx->order[k]];
             const int nb = t.cur_buf == 0 ? 1 : 0;
-            t.cur = t.buf[nb]; t.cur_buf = nb; t.cur_base = false; t.cur_entries = in_entries / 2;
+            t.cur = t.buf[nb]; t.cur_buf = nb; t.cur_base = false; t.cur_entries = in_entries / shrink;
         }
     }
     ctx->have_r = false;

@@ -69,6 +69,7 @@ struct RoundArgs {
     // group of terms, weighted by the eq weights, and multiplies each group's sum by its
     // coefficient at the end.  Group 0 holds the terms with base-field coefficients (their sum is a
     // base value, gcoef = 1); a term with an extension coefficient is a group of its own.
+    u32 bind[4][8];       // FOLD = 2: eq(rho0 rho1, b), b < 4, Montgomery form: entry y of the bound table is sum_b bind[b] T[4y + b]
     int ngroups;
     int product;          // 1: the statement is the product of the tables (no term table needed)
     u32 gcoef[2][8];      // Montgomery form
@@ -77,12 +78,38 @@ constexpr int MAX_GROUPS = 2;
 constexpr int PARTIAL_ROW_WORDS = MAX_GROUPS * MAX_PARTIAL_WORDS;   // words per block in the partials buffer
 
 // Launchers (defined next to their kernels).  Each returns the CUDA error of the launch.
-cudaError_t launch_round(int D, int shape, int points, int nt_used, bool fold, const RoundArgs &args, int grid, size_t smem,
+// fold: 0 the tables as they are, 1 folded by r on the way in, 2 base tables bound to two challenges at once (args.bind)
+cudaError_t launch_round(int D, int shape, int points, int nt_used, int fold, const RoundArgs &args, int grid, size_t smem,
                          cudaStream_t stream);
 bool round_supported(int D, int points, int nt_used);
 // The round on tables that are all in the base field (no fold): see RoundArgs::ngroups.
 cudaError_t launch_round_base(int D, int points, int nt_used, int ngroups, const RoundArgs &args, int grid, size_t smem,
                               cudaStream_t stream);
+
+// The first two rounds of a product of base-field tables from one pass over the tables (the
+// reference's small-value rounds with L0 = 2, src/sumcheck.lisp:319-337): for every block y of four
+// consecutive entries the tables' values on the grid {0..G-1}^2 of the two lowest variables are
+// made by additions, multiplied in the base field, and summed with the eq weights of the other
+// variables: A[z0 + G z1] = sum_y w(y) prod_t T_t(z0, z1, y).  The host reads both round messages
+// off A; the tables are then bound to both challenges at once on the way into round 2.
+struct SvArgs {
+    const u32 *src[SC_MAX_TABLES];
+    u64 nblocks;          // blocks of four entries
+    int logL;             // blocks per high weight; a thread keeps one low index and walks the high ones
+    int use_low, use_high;
+    const u32 *low;       // multipliers (ExtM layout), Montgomery form
+    const u32 *high;
+    u32 post[8];          // final factor (Montgomery form), applied when use_post
+    int use_post;
+    u32 *partials;        // gridDim.x rows of G * G * D words
+    unsigned int *counter;
+    u32 *out_host;        // G * G * D canonical words in mapped host memory, then the word below
+    u32 seq;              // posted at word SV_FLAG of out_host
+};
+constexpr int SV_MAX_WORDS = 64;   // G^2 D words: G <= 4 at D = 4
+constexpr int SV_FLAG = SV_MAX_WORDS;
+cudaError_t launch_small_values(int D, int G, int nt, const SvArgs &args, int grid, cudaStream_t stream);
+bool small_values_supported(int D, int G, int nt);
 
 // The last rounds in one launch.  Once the tables are small a round is all latency (launch,
 // completion, the trip to the host and back), so a single block runs every remaining round and

@@ -2,7 +2,7 @@
 // so that the two extension degrees compile side by side.
 #include "round_kernel.cuh"
 namespace sc {
-cudaError_t launch_round_d4(int shape, int points, int nt, bool fold, const RoundArgs &args, int grid, size_t smem, cudaStream_t stream) {
+cudaError_t launch_round_d4(int shape, int points, int nt, int fold, const RoundArgs &args, int grid, size_t smem, cudaStream_t stream) {
     return launch_round_d<4>(shape, points, nt, fold, args, grid, smem, stream);
 }
 }  // namespace sc

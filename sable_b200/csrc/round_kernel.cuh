@@ -152,14 +152,14 @@ __device__ __forceinline__ Ext<D> eval_gkr(const Ext<D> (&val)[4], const ExtM<D>
     return eadd<D>(f, g);
 }
 
-template <int D, int PTS, int NT, bool FOLD, int SHAPE>
+template <int D, int PTS, int NT, int FOLD, int SHAPE>
 __global__ void __launch_bounds__(ROUND_THREADS, FOLD ? SC_MINBLOCKS : SC_MINBLOCKS_R0) round_kernel(const __grid_constant__ RoundArgs a) {
     extern __shared__ __align__(16) u32 smem[];
     __shared__ u32 red[ROUND_THREADS / 32][PTS * D];
     __shared__ bool is_last;
     const int tid = threadIdx.x;
     const u32 L = 1u << a.logL;
-    constexpr int NE = FOLD ? 4 : 2;   // entries read per table and pair
+    constexpr int NE = FOLD == 1 ? 4 : 2;   // entries read per table and pair (FOLD = 2: two blocks of four base entries)
 
     if (a.use_low) {   // the low multipliers of this round: (v, 3v) per entry
         const uint4 *g = reinterpret_cast<const uint4 *>(a.low);
@@ -168,12 +168,31 @@ __global__ void __launch_bounds__(ROUND_THREADS, FOLD ? SC_MINBLOCKS : SC_MINBLO
         __syncthreads();
     }
     ExtM<D> rm;
-    if (FOLD) {
+    if (FOLD == 1) {
         Ext<D> r;
 #pragma unroll
         for (int c = 0; c < D; c++) r.v[c] = a.r[c];
         rm = eprep<D>(r);
     }
+    u32 bind[4][D];   // FOLD = 2: the weights of the four entries of a block
+    if (FOLD == 2) {
+#pragma unroll
+        for (int b = 0; b < 4; b++)
+#pragma unroll
+            for (int c = 0; c < D; c++) bind[b][c] = a.bind[b][c];
+    }
+    // a block of four base entries bound to two challenges at once: sum_b bind[b] e[b]  (BIND-PREFIX, src/sumcheck.lisp:496-510)
+    auto bound = [&](const Ext<D> &e4) {
+        Ext<D> o;
+#pragma unroll
+        for (int c = 0; c < D; c++) {
+            u64 acc = 0;
+#pragma unroll
+            for (int b = 0; b < 4; b++) acc += (u64)bind[b][c] * e4.v[b];
+            o.v[c] = redc4(acc);
+        }
+        return o;
+    };
     unsigned base_mask = 0;
 #pragma unroll
     for (int t = 0; t < NT; t++) base_mask |= (a.src_base[t] ? 1u : 0u) << t;
@@ -232,8 +251,12 @@ __global__ void __launch_bounds__(ROUND_THREADS, FOLD ? SC_MINBLOCKS : SC_MINBLO
             Ext<D> e[NT][NE];
 #pragma unroll
             for (int t = 0; t < NT; t++) {
-                if ((base_mask >> t) & 1) {
-                    if (FOLD) {
+                if (FOLD == 2) {
+                    const uint4 w0 = __ldcs(reinterpret_cast<const uint4 *>(a.src[t]) + 2 * i), w1 = __ldcs(reinterpret_cast<const uint4 *>(a.src[t]) + 2 * i + 1);
+                    e[t][0].v[0] = w0.x; e[t][0].v[1] = w0.y; e[t][0].v[2] = w0.z; e[t][0].v[3] = w0.w;
+                    e[t][1].v[0] = w1.x; e[t][1].v[1] = w1.y; e[t][1].v[2] = w1.z; e[t][1].v[3] = w1.w;
+                } else if ((base_mask >> t) & 1) {
+                    if (FOLD == 1) {
                         const uint4 w = __ldcs(reinterpret_cast<const uint4 *>(a.src[t]) + i);
                         e[t][0].v[0] = w.x; e[t][1].v[0] = w.y; e[t][2].v[0] = w.z; e[t][3].v[0] = w.w;
                     } else {
@@ -249,7 +272,14 @@ __global__ void __launch_bounds__(ROUND_THREADS, FOLD ? SC_MINBLOCKS : SC_MINBLO
 #pragma unroll
             for (int t = 0; t < NT; t++) {
                 const bool tb = (base_mask >> t) & 1;
-                if (!FOLD) {
+                if (FOLD == 2) {
+                    const Ext<D> lo = bound(e[t][0]), hi = bound(e[t][1]);
+                    store_ext<D>(a.dst[t] + (2 * i) * D, lo);
+                    store_ext<D>(a.dst[t] + (2 * i + 1) * D, hi);
+                    val[t] = lo;
+                    slope[t] = esub<D>(hi, lo);
+                    if (PTS == 2) slope[t] = eadd<D>(slope[t], hi);
+                } else if (!FOLD) {
                     if (tb) {
                         val[t] = lift<D>(e[t][0].v[0]);
                         const u32 sl = fsub(e[t][1].v[0], e[t][0].v[0]);
@@ -280,7 +310,16 @@ __global__ void __launch_bounds__(ROUND_THREADS, FOLD ? SC_MINBLOCKS : SC_MINBLO
                 }
             }
             // tables beyond the statement's are only folded
-            if (FOLD) {
+            if (FOLD == 2) {
+                for (int t = NT; t < a.ntables; t++) {
+                    const uint4 w0 = __ldcs(reinterpret_cast<const uint4 *>(a.src[t]) + 2 * i), w1 = __ldcs(reinterpret_cast<const uint4 *>(a.src[t]) + 2 * i + 1);
+                    Ext<D> b0, b1;
+                    b0.v[0] = w0.x; b0.v[1] = w0.y; b0.v[2] = w0.z; b0.v[3] = w0.w;
+                    b1.v[0] = w1.x; b1.v[1] = w1.y; b1.v[2] = w1.z; b1.v[3] = w1.w;
+                    store_ext<D>(a.dst[t] + (2 * i) * D, bound(b0));
+                    store_ext<D>(a.dst[t] + (2 * i + 1) * D, bound(b1));
+                }
+            } else if (FOLD == 1) {
                 for (int t = NT; t < a.ntables; t++) {
                     Ext<D> lo, hi;
                     if (a.src_base[t]) {
@@ -321,9 +360,9 @@ __global__ void __launch_bounds__(ROUND_THREADS, FOLD ? SC_MINBLOCKS : SC_MINBLO
                 }
                 bool fbase = false;
                 Ext<D> f;
-                if (SHAPE == SHAPE_PRODUCT) f = eval_product<D, NT, !FOLD>(val, base_mask, &fbase);
-                else if (SHAPE == SHAPE_GKR) f = eval_gkr<D, !FOLD>(reinterpret_cast<const Ext<D>(&)[4]>(val), lam, base_mask);
-                else f = eval_statement<D, NT, !FOLD>(a.st, val, FOLD ? 0u : base_mask, &fbase);
+                if (SHAPE == SHAPE_PRODUCT) f = eval_product<D, NT, FOLD == 0>(val, base_mask, &fbase);
+                else if (SHAPE == SHAPE_GKR) f = eval_gkr<D, FOLD == 0>(reinterpret_cast<const Ext<D>(&)[4]>(val), lam, base_mask);
+                else f = eval_statement<D, NT, FOLD == 0>(a.st, val, FOLD ? 0u : base_mask, &fbase);
                 if (a.use_low) {
                     if (!FOLD && fbase) {   // a base value times the weight: D base products (EXT-SCALE, src/sumcheck.lisp:246)
                         const u32 fb = f.v[0];
@@ -409,19 +448,28 @@ __global__ void __launch_bounds__(ROUND_THREADS, FOLD ? SC_MINBLOCKS : SC_MINBLO
 }
 
 template <int D, int PTS, int NT, int SHAPE>
-static cudaError_t launch_round_dpns(bool fold, const RoundArgs &args, int grid, size_t smem, cudaStream_t stream) {
-    if (fold) {
-        if (smem > 48 * 1024) cudaFuncSetAttribute(round_kernel<D, PTS, NT, true, SHAPE>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-        round_kernel<D, PTS, NT, true, SHAPE><<<grid, ROUND_THREADS, smem, stream>>>(args);
+static cudaError_t launch_round_dpns(int fold, const RoundArgs &args, int grid, size_t smem, cudaStream_t stream) {
+    if (fold == 1) {
+        if (smem > 48 * 1024) cudaFuncSetAttribute(round_kernel<D, PTS, NT, 1, SHAPE>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        round_kernel<D, PTS, NT, 1, SHAPE><<<grid, ROUND_THREADS, smem, stream>>>(args);
+    } else if (fold == 0) {
+        if (smem > 48 * 1024) cudaFuncSetAttribute(round_kernel<D, PTS, NT, 0, SHAPE>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        round_kernel<D, PTS, NT, 0, SHAPE><<<grid, ROUND_THREADS, smem, stream>>>(args);
     } else {
-        if (smem > 48 * 1024) cudaFuncSetAttribute(round_kernel<D, PTS, NT, false, SHAPE>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-        round_kernel<D, PTS, NT, false, SHAPE><<<grid, ROUND_THREADS, smem, stream>>>(args);
+        return cudaErrorInvalidValue;
     }
+    return cudaGetLastError();
+}
+// base tables bound to two challenges on the way in: only the product kernels have this variant
+template <int D, int NT>
+static cudaError_t launch_round_bind2(const RoundArgs &args, int grid, size_t smem, cudaStream_t stream) {
+    if (smem > 48 * 1024) cudaFuncSetAttribute(round_kernel<D, NT, NT, 2, SHAPE_PRODUCT>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    round_kernel<D, NT, NT, 2, SHAPE_PRODUCT><<<grid, ROUND_THREADS, smem, stream>>>(args);
     return cudaGetLastError();
 }
 
 template <int D, int PTS>
-static cudaError_t launch_round_dp(int nt, bool fold, const RoundArgs &args, int grid, size_t smem, cudaStream_t stream) {
+static cudaError_t launch_round_dp(int nt, int fold, const RoundArgs &args, int grid, size_t smem, cudaStream_t stream) {
     switch (nt) {
     case 1: return launch_round_dpns<D, PTS, 1, SHAPE_GENERIC>(fold, args, grid, smem, stream);
     case 2: return launch_round_dpns<D, PTS, 2, SHAPE_GENERIC>(fold, args, grid, smem, stream);
@@ -433,7 +481,16 @@ static cudaError_t launch_round_dp(int nt, bool fold, const RoundArgs &args, int
 
 // The kernels with the statement built in: a product of nt tables at nt points, the GKR layer.
 template <int D>
-static cudaError_t launch_round_shape(int shape, int points, int nt, bool fold, const RoundArgs &args, int grid, size_t smem, cudaStream_t stream) {
+static cudaError_t launch_round_shape(int shape, int points, int nt, int fold, const RoundArgs &args, int grid, size_t smem, cudaStream_t stream) {
+    if (fold == 2) {
+        if (shape != SHAPE_PRODUCT || points != nt || D != 4) return cudaErrorInvalidValue;
+        switch (nt) {
+        case 1: return launch_round_bind2<4, 1>(args, grid, smem, stream);
+        case 2: return launch_round_bind2<4, 2>(args, grid, smem, stream);
+        case 3: return launch_round_bind2<4, 3>(args, grid, smem, stream);
+        default: return cudaErrorInvalidValue;
+        }
+    }
     if (shape == SHAPE_GKR && points == 2 && nt == 4) return launch_round_dpns<D, 2, 4, SHAPE_GKR>(fold, args, grid, smem, stream);
     if (shape == SHAPE_PRODUCT && points == nt) {
         switch (nt) {
@@ -447,7 +504,7 @@ static cudaError_t launch_round_shape(int shape, int points, int nt, bool fold, 
 }
 
 template <int D>
-static cudaError_t launch_round_d(int shape, int points, int nt, bool fold, const RoundArgs &args, int grid, size_t smem, cudaStream_t stream) {
+static cudaError_t launch_round_d(int shape, int points, int nt, int fold, const RoundArgs &args, int grid, size_t smem, cudaStream_t stream) {
     if (shape != SHAPE_GENERIC) return launch_round_shape<D>(shape, points, nt, fold, args, grid, smem, stream);
     switch (points) {
     case 1: return launch_round_dp<D, 1>(nt, fold, args, grid, smem, stream);

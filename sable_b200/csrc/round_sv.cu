@@ -1,0 +1,166 @@
+// round_sv.cu -- rounds 0 and 1 of a product of base-field tables from one pass (see SvArgs).
+//
+// Work split: a thread keeps one low index l of the split eq weights and walks the high indices h
+// of its block's share, reading block y = h L + l of every table (one 128-bit load per table;
+// neighbouring threads read neighbouring blocks).  Per block it adds w_high[h] F(z) into G^2 D
+// 64-bit sums, four blocks per reduction (four products below p^2 fit 64 bits, as in REDUCED-SUM,
+// src/field.lisp:213-218); the reduced sums wait in shared memory, and the low weight multiplies
+// once at the very end.  Blocks' rows are added by the last block to finish (no waiting).
+#include "round_kernel.cuh"
+
+namespace sc {
+
+template <int D, int G, int NT>
+__global__ void __launch_bounds__(ROUND_THREADS, 1) sv_kernel(const __grid_constant__ SvArgs a) {
+    constexpr int Z = G * G, W = Z * D;
+    extern __shared__ __align__(16) u32 tot[];   // [W][ROUND_THREADS]
+    __shared__ bool is_last;
+    const int tid = threadIdx.x;
+    const u32 L = 1u << a.logL;
+    const u32 lchunks = L / ROUND_THREADS;
+    const u32 lc = blockIdx.x % lchunks, hg = blockIdx.x / lchunks, nhg = gridDim.x / lchunks;
+    const u64 NH = a.nblocks >> a.logL;
+    const u64 h0 = NH * hg / nhg, h1 = NH * (hg + 1) / nhg;
+    const u32 l = lc * ROUND_THREADS + tid;
+
+    u64 acc[Z][D];
+#pragma unroll
+    for (int z = 0; z < Z; z++)
+#pragma unroll
+        for (int c = 0; c < D; c++) acc[z][c] = 0;
+    for (int k = 0; k < W; k++) tot[k * ROUND_THREADS + tid] = 0;
+    int pending = 0;
+
+    auto reduce = [&]() {
+#pragma unroll
+        for (int z = 0; z < Z; z++)
+#pragma unroll
+            for (int c = 0; c < D; c++) {
+                u32 *slot = tot + (z * D + c) * ROUND_THREADS + tid;
+                *slot = fadd(*slot, redc4(acc[z][c]));
+                acc[z][c] = 0;
+            }
+        pending = 0;
+    };
+
+    for (u64 h = h0; h < h1; h++) {
+        const u64 i = h * L + l;
+        u32 g[NT][Z];
+#pragma unroll
+        for (int t = 0; t < NT; t++) {
+            const uint4 e = __ldcs(reinterpret_cast<const uint4 *>(a.src[t]) + i);
+            // entries (b0, b1) = e.x (0,0), e.y (1,0), e.z (0,1), e.w (1,1); extend variable 0, then variable 1, by additions
+            u32 row[2][G];
+            row[0][0] = e.x; row[0][1] = e.y; row[1][0] = e.z; row[1][1] = e.w;
+#pragma unroll
+            for (int b1 = 0; b1 < 2; b1++) {
+                const u32 s = fsub(row[b1][1], row[b1][0]);
+#pragma unroll
+                for (int z0 = 2; z0 < G; z0++) row[b1][z0] = fadd(row[b1][z0 - 1], s);
+            }
+#pragma unroll
+            for (int z0 = 0; z0 < G; z0++) {
+                const u32 s = fsub(row[1][z0], row[0][z0]);
+                g[t][z0] = row[0][z0];
+                g[t][z0 + G] = row[1][z0];
+#pragma unroll
+                for (int z1 = 2; z1 < G; z1++) g[t][z0 + G * z1] = fadd(g[t][z0 + G * (z1 - 1)], s);
+            }
+        }
+        u32 hw[D];
+        if (a.use_high) {
+            const uint4 *hp = reinterpret_cast<const uint4 *>(a.high + h * D);
+#pragma unroll
+            for (int c = 0; c < D; c += 4) { const uint4 v = __ldg(hp + c / 4); hw[c] = v.x; hw[c + 1] = v.y; hw[c + 2] = v.z; hw[c + 3] = v.w; }
+        } else {
+#pragma unroll
+            for (int c = 0; c < D; c++) hw[c] = c == 0 ? R1 : 0u;
+        }
+#pragma unroll
+        for (int z = 0; z < Z; z++) {
+            u32 f = g[0][z];
+#pragma unroll
+            for (int t = 1; t < NT; t++) f = mmul(f, g[t][z]);
+#pragma unroll
+            for (int c = 0; c < D; c++) acc[z][c] += (u64)hw[c] * f;
+        }
+        if (++pending == 4) reduce();
+    }
+    if (pending) reduce();
+
+    // the low weight, once per thread
+    if (a.use_low) {
+        const u32 *w = a.low + (size_t)l * 2 * D;
+        ExtM<D> lw;
+#pragma unroll
+        for (int c = 0; c < D; c++) { lw.v[c] = __ldg(w + c); lw.t[c] = __ldg(w + D + c); }
+        for (int z = 0; z < Z; z++) {
+            Ext<D> v;
+#pragma unroll
+            for (int c = 0; c < D; c++) v.v[c] = tot[(z * D + c) * ROUND_THREADS + tid];
+            v = emul<D>(v, lw);
+#pragma unroll
+            for (int c = 0; c < D; c++) tot[(z * D + c) * ROUND_THREADS + tid] = v.v[c];
+        }
+    }
+    __syncthreads();
+    // the block's row: word k summed over the threads
+    for (int k = tid >> 5; k < W; k += ROUND_THREADS / 32) {
+        u32 v = 0;
+        for (int j = tid & 31; j < ROUND_THREADS; j += 32) v = fadd(v, tot[k * ROUND_THREADS + j]);
+#pragma unroll
+        for (int off = 16; off > 0; off >>= 1) v = fadd(v, __shfl_down_sync(0xffffffffu, v, off));
+        if ((tid & 31) == 0) a.partials[(size_t)blockIdx.x * W + k] = v;
+    }
+    __threadfence();
+    __syncthreads();
+    if (tid == 0) is_last = atomicAdd(a.counter, 1u) == gridDim.x - 1;
+    __syncthreads();
+    if (!is_last) return;
+    __threadfence();
+    __shared__ u32 row[SV_MAX_WORDS];
+    if (tid < W) {
+        u32 v = 0;
+        for (unsigned b = 0; b < gridDim.x; b++) v = fadd(v, __ldcg(a.partials + (size_t)b * W + tid));
+        row[tid] = v;
+    }
+    __syncthreads();
+    if (tid < Z) {
+        Ext<D> s;
+#pragma unroll
+        for (int c = 0; c < D; c++) s.v[c] = row[tid * D + c];
+        if (a.use_post) {
+            Ext<D> pf;
+#pragma unroll
+            for (int c = 0; c < D; c++) pf.v[c] = a.post[c];
+            s = emul<D>(s, pf);
+        }
+#pragma unroll
+        for (int c = 0; c < D; c++) a.out_host[tid * D + c] = s.v[c];
+    }
+    __syncthreads();
+    if (tid == 0) {
+        *a.counter = 0;
+        __threadfence_system();
+        *reinterpret_cast<volatile u32 *>(a.out_host + SV_FLAG) = a.seq;
+    }
+}
+
+template <int D, int G, int NT> static cudaError_t launch_sv_one(const SvArgs &args, int grid, cudaStream_t stream) {
+    const size_t smem = (size_t)G * G * D * ROUND_THREADS * 4;
+    cudaFuncSetAttribute(sv_kernel<D, G, NT>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    sv_kernel<D, G, NT><<<grid, ROUND_THREADS, smem, stream>>>(args);
+    return cudaGetLastError();
+}
+bool small_values_supported(int D, int G, int nt) { return D == 4 && nt >= 1 && nt <= 3 && G == nt + 1; }
+cudaError_t launch_small_values(int D, int G, int nt, const SvArgs &args, int grid, cudaStream_t stream) {
+    if (!small_values_supported(D, G, nt)) return cudaErrorInvalidValue;
+    switch (nt) {
+    case 1: return launch_sv_one<4, 2, 1>(args, grid, stream);
+    case 2: return launch_sv_one<4, 3, 2>(args, grid, stream);
+    case 3: return launch_sv_one<4, 4, 3>(args, grid, stream);
+    }
+    return cudaErrorInvalidValue;
+}
+
+}  // namespace sc

@@ -299,3 +299,27 @@ def test_abandoned_proof_does_not_block_the_next(prover):
     prover.round()          # the resident kernel now waits for a challenge that never comes
     got, want, ta, tb = both(prover, d, n, "(* a b)", tables, eq=rand_ext(rng, d, n))
     assert_same(got, want, ta, tb)
+
+
+@pytest.mark.parametrize("statement,names,with_eq", [
+    ("(* t0 t1 t2)", ["t0", "t1", "t2"], True),
+    ("(* t0 t1 t2)", ["t0", "t1", "t2"], False),
+    ("(* 5 t0 t1)", ["t0", "t1"], True),
+    ("t0", ["t0"], True),
+    ("(* alpha t1 t0)", ["t0", "u", "t1"], True),       # an extension coefficient, a table outside the statement
+])
+def test_small_value_rounds_match_folding(prover, statement, names, with_eq, monkeypatch):
+    # reference tests/tests.lisp:374-395: the small-value rounds give the same proof as folding, byte for byte.
+    # Here they run for products of base tables that are large enough for split eq weights (n >= 22).
+    d, n = 4, 22
+    rng = np.random.default_rng(len(statement) + with_eq)
+    tables = [(nm, rng.integers(0, P, size=1 << n, dtype=np.uint32)) for nm in names]
+    constants = [("alpha", rand_ext(rng, d).tolist())] if "alpha" in statement else []
+    eq = rand_ext(rng, d, n) if with_eq else None
+    got, want, ta, tb = both(prover, d, n, statement, tables, eq=eq, constants=constants, threads=0)
+    assert_same(got, want, ta, tb)
+    # and the device's own folding path agrees (small values switched off)
+    monkeypatch.setenv("SABLE_B200_SMALL_VALUES", "0")
+    tc = sb.Transcript("par", d)
+    again = sb.prove(tc, n, statement, tables, eq=eq, constants=constants, prover=prover)
+    assert again == got and tc.proof() == ta.proof()
