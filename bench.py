@@ -42,6 +42,10 @@ CONFIGS = {
 }
 SEED = 1
 EQ_ID, CONST_ID = 255, 254
+# DRAM bytes moved per algorithmic byte by the fused round kernel, from an ncu capture of rounds 1 and 2 at
+# n = 24 (profiles/round_kernel_c4_n24_ncu.md: 1914.6 MB read + written against 2013.3 MB); traffic grows
+# in proportion to the pairs processed, so a launch's traffic is its algorithmic bytes times this.
+NCU_TRAFFIC_PER_ALGORITHMIC_BYTE = 0.951
 
 
 def splitmix64(x):
@@ -252,7 +256,8 @@ def main():
     achieved = fused_bytes / (fused_ms * 1e-3) / 1e9 if fused_ms > 0 else 0.0
     rounds = [{"round": j, "ms": round(s[0], 4), "GB/s": round(s[1] / (s[0] * 1e-3) / 1e9, 1)} for j, s in enumerate(stats) if s[1] >= (128 << 20) and s[0] > 0]
     roofline = {"bound": "hbm", "kernel": "round_kernel<D=%d,points,tables,fold> (rounds 1..n-1: fold by the previous challenge + round sums)" % D,
-                "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak, "peak_kind": peak_kind, "traffic": None,
+                "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak, "peak_kind": peak_kind,
+                "traffic": int(fused_bytes * NCU_TRAFFIC_PER_ALGORITHMIC_BYTE) if args.config == "C4" and D == 4 else None,
                 "launches": len(fused), "bytes_per_step": fused_bytes, "ms_per_step": fused_ms, "rounds": rounds,
                 "whole_proof_frac": algorithmic_bytes(cfg, n_loc, D) / (ms_per_step * 1e-3) / 1e9 / peak}
 

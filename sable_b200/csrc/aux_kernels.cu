@@ -195,7 +195,7 @@ cudaError_t launch_reduce_words(u32 *words, u64 count, cudaStream_t stream) {
 
 // ------------------------------------------------------------------ sum of the ranks' partial sums (canonical words)
 
-__global__ void sum_ranks_kernel(const u32 *gathered, int world, int words, u32 *out_dev, u32 *out_host, u32 seq) {
+__global__ void sum_ranks_kernel(const u32 *gathered, int world, int words, u32 *out_dev, u32 *out_host, int flag_word, u32 seq) {
     const int k = threadIdx.x;
     if (k < words) {
         u32 acc = 0;
@@ -207,11 +207,11 @@ __global__ void sum_ranks_kernel(const u32 *gathered, int world, int words, u32 
     __syncthreads();
     if (k == 0 && out_host) {
         __threadfence_system();
-        *reinterpret_cast<volatile u32 *>(out_host + MAX_PARTIAL_WORDS) = seq;
+        *reinterpret_cast<volatile u32 *>(out_host + flag_word) = seq;
     }
 }
-cudaError_t launch_sum_ranks(const u32 *gathered, int world, int words, u32 *out_dev, u32 *out_host, u32 seq, cudaStream_t stream) {
-    sum_ranks_kernel<<<1, 64, 0, stream>>>(gathered, world, words, out_dev, out_host, seq);
+cudaError_t launch_sum_ranks(const u32 *gathered, int world, int words, u32 *out_dev, u32 *out_host, int flag_word, u32 seq, cudaStream_t stream) {
+    sum_ranks_kernel<<<1, 64, 0, stream>>>(gathered, world, words, out_dev, out_host, flag_word, seq);
     return cudaGetLastError();
 }
 

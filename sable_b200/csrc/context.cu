@@ -120,7 +120,8 @@ struct sc_ctx {
     u32 *d_out = nullptr, *h_out = nullptr, *h_out_dev = nullptr;   // h_out: mapped pinned; h_out_dev its device alias
     u32 *d_export = nullptr, *h_export = nullptr;
     u64 export_cap = 0;
-    u32 *d_gather = nullptr;         // world * MAX_PARTIAL_WORDS
+    u32 *d_gather = nullptr;         // world * SV_MAX_WORDS words: the ranks' sums side by side
+    u32 *d_sv = nullptr;             // this rank's small-value accumulators
     u32 *d_gtab[SC_MAX_TABLES];      // gathered tables
     u64 gtab_cap[SC_MAX_TABLES] = {0};
     int grid_cap = 0;
@@ -130,6 +131,9 @@ struct sc_ctx {
     bool tail_active = false;
     int tail_first = 0, tail_rounds = 0, tail_bits = 12;
     u32 tail_seq = 0;
+    unsigned tail_polls = TAIL_POLL_LIMIT;
+    u64 tail_entries = 0;            // entries of the tables the first round of the launch read
+    int tail_buf0[SC_MAX_TABLES];    // per slot: which of the table's two buffers the first round wrote
 
     // the first two rounds from one pass over base tables (see SvArgs)
     bool sv_ok = false;
@@ -260,6 +264,7 @@ extern "C" int sc_create(int device, sc_ctx **out) {
         cudaHostGetDevicePointer(&ctx->h_sv_dev, ctx->h_sv, 0) != cudaSuccess) { cudaGetLastError(); sc_destroy(ctx); return SC_ECUDA; }
     memset(ctx->h_sv, 0, (SV_MAX_WORDS + 32) * 4);
     if (const char *env = getenv("SABLE_B200_TAIL_BITS")) ctx->tail_bits = std::max(0, std::min(14, atoi(env)));
+    if (const char *env = getenv("SABLE_B200_TAIL_POLLS")) ctx->tail_polls = (unsigned)std::max(1000, std::min((int)TAIL_POLL_LIMIT, atoi(env)));
     *out = ctx;
     return SC_OK;
 }
@@ -275,7 +280,7 @@ extern "C" int sc_destroy(sc_ctx *ctx) {
     for (auto &t : ctx->tab) { cudaFree(t.t0); cudaFree(t.buf[0]); cudaFree(t.buf[1]); }
     for (auto p : ctx->d_gtab) cudaFree(p);
     cudaFree(ctx->d_eq); cudaFree(ctx->d_bw); cudaFree(ctx->d_chunks); cudaFree(ctx->d_weights); cudaFree(ctx->d_descs);
-    cudaFree(ctx->d_partials); cudaFree(ctx->d_counter); cudaFree(ctx->d_out); cudaFree(ctx->d_export); cudaFree(ctx->d_gather);
+    cudaFree(ctx->d_sv); cudaFree(ctx->d_partials); cudaFree(ctx->d_counter); cudaFree(ctx->d_out); cudaFree(ctx->d_export); cudaFree(ctx->d_gather);
     if (ctx->h_out) cudaFreeHost(ctx->h_out);
     if (ctx->h_export) cudaFreeHost(ctx->h_export);
     for (auto e : ctx->ev) cudaEventDestroy(e);
@@ -667,7 +672,7 @@ extern "C" int sc_begin(sc_ctx *ctx, int n, const uint32_t *eq, int K, const uin
     // base tables, large enough for split weights, on one GPU, one block
     {
         const char *env = getenv("SABLE_B200_SMALL_VALUES");
-        bool ok = !(env && env[0] == '0') && ctx->shape == SHAPE_PRODUCT && ctx->world == 1 && K == 1 && n >= 3 &&
+        bool ok = !(env && env[0] == '0') && ctx->shape == SHAPE_PRODUCT && K == 1 && n >= 3 && ctx->gather_round > 2 &&
                   small_values_supported(D, ctx->points + 1, ctx->nt_used) && ctx->plan[1].logL >= 8;
         for (int s = 0; s < ctx->ntables && ok; s++) ok = ctx->tab[s].stride == 1;
         ctx->sv_ok = ok;
@@ -757,10 +762,20 @@ static int sv_round0(sc_ctx *ctx, uint32_t *sums) {
     a.nblocks = ctx->tab[ctx->order[0]].entries / 4;
     a.logL = pl.logL; a.use_low = pl.use_low; a.use_high = pl.use_high;
     a.low = ctx->d_weights + pl.low_word; a.high = ctx->d_weights + pl.high_word;
-    a.use_post = ctx->st_e > 0 || ctx->use_factor;
+    const bool sharded = ctx->world > 1;
+    a.use_post = ctx->st_e > 0 || ctx->use_factor || (sharded && ctx->use_post);
     for (int c = 0; c < D; c++) a.post[c] = ctx->use_factor ? mmul(to_mont(ctx->st_factor[c]), ctx->st_re) : (c == 0 ? ctx->st_re : 0u);
+    if (sharded && ctx->use_post) ext_mul_host(D, a.post, ctx->post, a.post);   // this rank's eq weight
     a.partials = ctx->d_partials; a.counter = ctx->d_counter;
-    a.out_host = ctx->h_sv_dev; a.seq = ++ctx->seq;
+    a.seq = ++ctx->seq;
+    if (sharded) {
+        int rc;
+        if (!ctx->d_sv && (rc = dev_alloc(ctx, (void **)&ctx->d_sv, SV_MAX_WORDS * 4))) return rc;
+        if (!ctx->d_gather && (rc = dev_alloc(ctx, (void **)&ctx->d_gather, (u64)ctx->world * SV_MAX_WORDS * 4))) return rc;
+        a.out_dev = ctx->d_sv;
+    } else {
+        a.out_host = ctx->h_sv_dev;
+    }
     const u32 lchunks = (1u << a.logL) / ROUND_THREADS;
     const u64 NH = a.nblocks >> a.logL;
     u64 nhg = std::max<u64>(1, (u64)ctx->sms / lchunks);
@@ -773,6 +788,12 @@ static int sv_round0(sc_ctx *ctx, uint32_t *sums) {
     CU(launch_small_values(D, G, ctx->nt_used, a, grid, ctx->stream));
     ctx->launches++;
     if (ctx->timing) CU(cudaEventRecord(ctx->ev[1], ctx->stream));
+    if (sharded) {   // every rank's accumulators, then their sum mod p
+        ncclResult_t r = g_nccl.AllGather(ctx->d_sv, ctx->d_gather, (size_t)Z * D, NCCL_UINT32, ctx->comm, ctx->stream);
+        if (r) return fail(ctx, SC_ECOMM, "ncclAllGather: %s", g_nccl.GetErrorString(r));
+        CU(launch_sum_ranks(ctx->d_gather, ctx->world, Z * D, ctx->d_sv, ctx->h_sv_dev, SV_FLAG, a.seq, ctx->stream));
+        ctx->launches++;
+    }
     if (!wait_word(ctx, ctx->h_sv + SV_FLAG, a.seq)) { CU(cudaStreamSynchronize(ctx->stream)); return fail(ctx, SC_ECUDA, "the small-value pass did not finish"); }
     if (ctx->timing) {
         CU(cudaStreamSynchronize(ctx->stream));
@@ -848,7 +869,9 @@ static int tail_start(sc_ctx *ctx) {
         if (t.cur_buf >= 0 && t.buf_cap[t.cur_buf] == 0) return fail(ctx, SC_ESTATE, "table buffer lost");
         a.src[k] = t.cur_buf >= 0 ? t.buf[t.cur_buf] : t.cur;
         a.buf[0][k] = t.buf[first]; a.buf[1][k] = t.buf[first ^ 1];
+        ctx->tail_buf0[ctx->order[k]] = first;
     }
+    ctx->tail_entries = entries;
     for (int k = 0; k < a.nrounds; k++) {
         const RoundPlan &pl = ctx->plan[j + k];
         if (pl.logL != 0 || pl.use_low) return fail(ctx, SC_ESTATE, "a split round in the tail");
@@ -865,6 +888,7 @@ static int tail_start(sc_ctx *ctx) {
     ctx->seq += TAIL_MAX_ROUNDS + 2;
     a.seq = ctx->tail_seq;
     a.host = ctx->h_tail_dev;
+    a.poll_limit = ctx->tail_polls;
     ((volatile u32 *)ctx->h_tail)[TAIL_STATUS] = 0;
     std::atomic_thread_fence(std::memory_order_seq_cst);
     CU(launch_tail(D, ctx->shape, ctx->points, ctx->nt_used, a, ctx->stream));
@@ -876,11 +900,27 @@ static int tail_start(sc_ctx *ctx) {
     return SC_OK;
 }
 
+// The resident kernel gave up waiting for the challenge of its round DONE - 1 (the host was too slow, or
+// launches are serialised, as under a profiler): the tables are as that round's fold left them, so the
+// proof goes on with one launch per round, and the context stops using the resident kernel.
+static bool tail_recover(sc_ctx *ctx, int done) {
+    if (ctx->h_tail[TAIL_STATUS] != 2 || done < 1) return false;
+    for (int s = 0; s < ctx->ntables; s++) {
+        TableState &t = ctx->tab[s];
+        const int b = ctx->tail_buf0[s] ^ ((done - 1) & 1);
+        t.cur = t.buf[b]; t.cur_buf = b; t.cur_base = false; t.cur_entries = ctx->tail_entries >> done;
+    }
+    ctx->tail_active = false;
+    ctx->tail_bits = 0;
+    return true;
+}
+
 // A round of the resident kernel: wait for its sums to be posted.
 static int tail_round(sc_ctx *ctx, uint32_t *sums) {
     const int k = ctx->j - ctx->tail_first;
     const u32 *slot = ctx->h_tail + (size_t)k * TAIL_SLOT_WORDS;
     if (!wait_word(ctx, slot + 32, ctx->tail_seq + (u32)k)) {
+        if (tail_recover(ctx, k)) return sc_round(ctx, sums);
         ctx->tail_active = false;
         ctx->begun = false;
         return fail(ctx, SC_ESTATE, "the device stopped waiting for a challenge (status %u)", ctx->h_tail[TAIL_STATUS]);
@@ -990,10 +1030,10 @@ extern "C" int sc_round(sc_ctx *ctx, uint32_t *sums) {
     ctx->launches++;
     if (ctx->timing) CU(cudaEventRecord(e1, ctx->stream));
     if (local) {   // the whole job's sums: all-gather of the ranks' words, then their sum mod p
-        if (!ctx->d_gather) { if ((rc = dev_alloc(ctx, (void **)&ctx->d_gather, (u64)ctx->world * MAX_PARTIAL_WORDS * 4))) return rc; }
+        if (!ctx->d_gather) { if ((rc = dev_alloc(ctx, (void **)&ctx->d_gather, (u64)ctx->world * SV_MAX_WORDS * 4))) return rc; }
         ncclResult_t r = g_nccl.AllGather(ctx->d_out, ctx->d_gather, (size_t)W, NCCL_UINT32, ctx->comm, ctx->stream);
         if (r) return fail(ctx, SC_ECOMM, "ncclAllGather: %s", g_nccl.GetErrorString(r));
-        CU(launch_sum_ranks(ctx->d_gather, ctx->world, W, ctx->d_out, ctx->h_out_dev, a.seq, ctx->stream));
+        CU(launch_sum_ranks(ctx->d_gather, ctx->world, W, ctx->d_out, ctx->h_out_dev, MAX_PARTIAL_WORDS, a.seq, ctx->stream));
         ctx->launches++;
     }
     const auto tr2 = std::chrono::steady_clock::now();
@@ -1065,13 +1105,19 @@ extern "C" int sc_finish(sc_ctx *ctx, uint32_t *folded) {
     if (ctx->tail_active) {   // the resident kernel folds by the last challenge and posts the final entries
         const bool ok = wait_word(ctx, ctx->h_tail + TAIL_FINALS - 1, ctx->tail_seq);
         CU(cudaStreamSynchronize(ctx->stream));
-        ctx->tail_active = false;
-        ctx->begun = false;
-        if (!ok) return fail(ctx, SC_ESTATE, "the device stopped waiting for a challenge (status %u)", ctx->h_tail[TAIL_STATUS]);
-        if (folded)
-            for (int k = 0; k < ctx->ntables; k++)
-                memcpy(folded + (size_t)ctx->order[k] * ctx->D, ctx->h_tail + TAIL_FINALS + (size_t)k * ctx->D, 4 * (size_t)ctx->D);
-        return SC_OK;
+        if (ok) {
+            ctx->tail_active = false;
+            ctx->begun = false;
+            if (folded)
+                for (int k = 0; k < ctx->ntables; k++)
+                    memcpy(folded + (size_t)ctx->order[k] * ctx->D, ctx->h_tail + TAIL_FINALS + (size_t)k * ctx->D, 4 * (size_t)ctx->D);
+            return SC_OK;
+        }
+        if (!tail_recover(ctx, ctx->tail_rounds)) {   // else: the last fold below, by the challenge it did not wait for
+            ctx->tail_active = false;
+            ctx->begun = false;
+            return fail(ctx, SC_ESTATE, "the device stopped waiting for a challenge (status %u)", ctx->h_tail[TAIL_STATUS]);
+        }
     }
     if (ctx->n > 0 && (rc = fold_all(ctx))) return rc;
     if (folded && ctx->ntables) {

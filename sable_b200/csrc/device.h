@@ -103,7 +103,8 @@ struct SvArgs {
     int use_post;
     u32 *partials;        // gridDim.x rows of G * G * D words
     unsigned int *counter;
-    u32 *out_host;        // G * G * D canonical words in mapped host memory, then the word below
+    u32 *out_dev;         // G * G * D canonical words (for the all-gather of several GPUs; may be NULL)
+    u32 *out_host;        // the same in mapped host memory (may be NULL), then the word below
     u32 seq;              // posted at word SV_FLAG of out_host
 };
 constexpr int SV_MAX_WORDS = 64;   // G^2 D words: G <= 4 at D = 4
@@ -127,7 +128,7 @@ constexpr int TAIL_STATUS = TAIL_MAX_ROUNDS * TAIL_SLOT_WORDS;
 constexpr int TAIL_STOP = TAIL_STATUS + 1;
 constexpr int TAIL_FINALS = TAIL_STATUS + 16;
 constexpr int TAIL_WORDS = TAIL_FINALS + SC_MAX_TABLES * 8;
-constexpr unsigned TAIL_POLL_LIMIT = 4000000u;   // polls of mapped host memory (about a microsecond each) before giving up
+constexpr unsigned TAIL_POLL_LIMIT = 1500000u;   // polls of mapped host memory (about a microsecond each) before giving up
 struct TailRound {
     u64 npairs;
     u64 high_word;     // offset of the round's weights in the weights buffer
@@ -147,6 +148,7 @@ struct TailArgs {
     int use_post;
     u32 seq;
     u32 *host;                         // the mapped buffer (device address)
+    unsigned poll_limit;               // polls before the block gives up on a challenge
 };
 cudaError_t launch_tail(int D, int shape, int points, int nt_used, const TailArgs &args, cudaStream_t stream);
 
@@ -194,7 +196,8 @@ cudaError_t launch_weight_tables(int D, const u32 *chunks, const WeightDesc *des
                                  u32 *weights, u64 total_entries, cudaStream_t stream);
 
 // out[k] = sum over ranks of gathered[rank * words + k] mod p, to device and mapped host memory.
-cudaError_t launch_sum_ranks(const u32 *gathered, int world, int words, u32 *out_dev, u32 *out_host, u32 seq,
+// The launch number SEQ is posted at word FLAG_WORD of out_host once the sums are visible.
+cudaError_t launch_sum_ranks(const u32 *gathered, int world, int words, u32 *out_dev, u32 *out_host, int flag_word, u32 seq,
                              cudaStream_t stream);
 
 }  // namespace sc

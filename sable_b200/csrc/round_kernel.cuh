@@ -24,9 +24,6 @@
 #ifndef SC_MINBLOCKS_R0
 #define SC_MINBLOCKS_R0 2
 #endif
-#ifndef SC_PREFETCH
-#define SC_PREFETCH 0
-#endif
 
 namespace sc {
 
@@ -233,20 +230,6 @@ __global__ void __launch_bounds__(ROUND_THREADS, FOLD ? SC_MINBLOCKS : SC_MINBLO
                 if (cur_h != ~0ull) flush();
                 cur_h = h;
             }
-#if SC_PREFETCH
-            {   // pull the next pair of this thread towards L2 while this one is computed
-                const u64 nx = (q + ROUND_THREADS < chunk) ? i + ROUND_THREADS : i + (u64)gridDim.x * chunk - q + tid;
-                if (nx < a.npairs && (tid & 1) == 0) {
-#pragma unroll
-                    for (int t = 0; t < NT; t++) {
-                        const char *pp = ((base_mask >> t) & 1) ? reinterpret_cast<const char *>(a.src[t]) + nx * (NE * 4)
-                                                                : reinterpret_cast<const char *>(a.src[t]) + nx * (NE * D * 4);
-                        const int bytes = ((base_mask >> t) & 1) ? NE * 4 * 2 : NE * D * 4 * 2;
-                        for (int o = 0; o < bytes; o += 128) asm volatile("prefetch.global.L2 [%0];" ::"l"(pp + o));
-                    }
-                }
-            }
-#endif
             // every load of the pair first, so that they are all in flight together
             Ext<D> e[NT][NE];
 #pragma unroll

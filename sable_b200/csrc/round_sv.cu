@@ -136,13 +136,18 @@ __global__ void __launch_bounds__(ROUND_THREADS, 1) sv_kernel(const __grid_const
             s = emul<D>(s, pf);
         }
 #pragma unroll
-        for (int c = 0; c < D; c++) a.out_host[tid * D + c] = s.v[c];
+        for (int c = 0; c < D; c++) {
+            if (a.out_dev) a.out_dev[tid * D + c] = s.v[c];
+            if (a.out_host) a.out_host[tid * D + c] = s.v[c];
+        }
     }
     __syncthreads();
     if (tid == 0) {
         *a.counter = 0;
-        __threadfence_system();
-        *reinterpret_cast<volatile u32 *>(a.out_host + SV_FLAG) = a.seq;
+        if (a.out_host) {
+            __threadfence_system();
+            *reinterpret_cast<volatile u32 *>(a.out_host + SV_FLAG) = a.seq;
+        }
     }
 }
 

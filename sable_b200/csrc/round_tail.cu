@@ -6,7 +6,7 @@
 // weights are not split).  What differs is that the block stays resident between rounds and gets
 // each challenge from the host through mapped memory, so a round costs a few microseconds
 // instead of a launch and a completion.  Every wait is bounded: a block that hears nothing for
-// TAIL_POLL_LIMIT polls, or is told to stop, records why and returns.
+// its limit of polls, or is told to stop, records why and returns.
 #include "round_kernel.cuh"
 
 namespace sc {
@@ -130,7 +130,7 @@ __global__ void __launch_bounds__(ROUND_THREADS) tail_kernel(const __grid_consta
             st_sys(slot + 32, a.seq + (u32)k);
             // wait for the challenge, a bounded number of polls
             int ok = 0;
-            for (unsigned poll = 0; poll < TAIL_POLL_LIMIT; poll++) {
+            for (unsigned poll = 0; poll < a.poll_limit; poll++) {
                 if (ld_sys(slot + 48) == a.seq + (u32)k) { ok = 1; break; }
                 if ((poll & 63) == 63 && ld_sys(a.host + TAIL_STOP) == a.seq) { ok = -1; break; }
             }

@@ -23,6 +23,7 @@ CASES = [
     (8, 7, "(+ (* alpha t0 t1) (* 3 t1) -2)", [0, 1], ["alpha"], False),
     (4, 3, "(* t0 t1)", [0, 0], [], True),
     (4, 17, "(+ (* t0 t3) (* t1 t2) (* lam t2 t3))", [1, 1, 0, 0], ["lam"], True),   # sharded rounds before the gather
+    (4, 23, "(* t0 t1 t2)", [1, 1, 1], [], True),   # large enough for the small-value rounds on every rank
 ]
 
 
@@ -69,7 +70,7 @@ def main():
         if rank == 0:
             from oracle import pyoracle as orc
             tb = orc.Transcript("multi", d)
-            want = orc.prove(tb, n, statement, full, eq=eq, constants=constants)
+            want = orc.prove(tb, n, statement, full, eq=eq, constants=constants, threads=0)
             ok = rho == want[0] and finals == [want[1][nm] for nm, _ in full] and tr.proof() == tb.proof()
             results.append({"case": statement, "n": n, "d": d, "ok": bool(ok)})
         else:

@@ -323,3 +323,37 @@ def test_small_value_rounds_match_folding(prover, statement, names, with_eq, mon
     tc = sb.Transcript("par", d)
     again = sb.prove(tc, n, statement, tables, eq=eq, constants=constants, prover=prover)
     assert again == got and tc.proof() == ta.proof()
+
+
+def test_slow_host_falls_back_to_a_launch_per_round(monkeypatch):
+    # the resident kernel of the last rounds waits a bounded time for each challenge; when the host is
+    # slower than that (here: a short limit and a pause) it returns and the proof goes on, launch by launch
+    import time
+    monkeypatch.setenv("SABLE_B200_TAIL_POLLS", "2000")
+    p = sb.Prover(0)
+    try:
+        d, n = 4, 8
+        rng = np.random.default_rng(4)
+        tables = [("a", rand_ext(rng, d, 1 << n)), ("b", rng.integers(0, P, size=1 << n, dtype=np.uint32))]
+        eq = rand_ext(rng, d, n)
+        degree, terms = sb.lower_statement("(* a b)", d, ["a", "b"])
+        for pause_at in (2, n - 1):      # a pause in the middle, and one before the last challenge
+            p.set_statement(d, 2, 2, terms)
+            for s, (_, t) in enumerate(tables):
+                p.upload_table(s, t)
+            p.begin(n, eq=eq)
+            tr = sb.Transcript("slow", d)
+            tr.absorb(b"sc|" + n.to_bytes(2, "little") + (2).to_bytes(2, "little") + (1).to_bytes(4, "little"))
+            rho = []
+            for j in range(n):
+                tr.send(p.round())
+                if j == pause_at:
+                    time.sleep(0.5)
+                rho.append(tr.challenge())
+                p.challenge(rho[-1])
+            finals = p.finish(2)[:, 0, :].tolist()
+            tb = orc.Transcript("slow", d)
+            want = orc.prove(tb, n, "(* a b)", tables, eq=eq)
+            assert rho == want[0] and finals == [want[1]["a"], want[1]["b"]] and tr.proof() == tb.proof()
+    finally:
+        p.close()
