@@ -21,6 +21,9 @@
 #ifndef SC_MINBLOCKS
 #define SC_MINBLOCKS 2
 #endif
+#ifndef SC_MINBLOCKS_D8
+#define SC_MINBLOCKS_D8 2
+#endif
 #ifndef SC_MINBLOCKS_R0
 #define SC_MINBLOCKS_R0 2
 #endif
@@ -150,7 +153,7 @@ __device__ __forceinline__ Ext<D> eval_gkr(const Ext<D> (&val)[4], const ExtM<D>
 }
 
 template <int D, int PTS, int NT, int FOLD, int SHAPE>
-__global__ void __launch_bounds__(ROUND_THREADS, FOLD ? SC_MINBLOCKS : SC_MINBLOCKS_R0) round_kernel(const __grid_constant__ RoundArgs a) {
+__global__ void __launch_bounds__(ROUND_THREADS, D == 8 ? SC_MINBLOCKS_D8 : (FOLD ? SC_MINBLOCKS : SC_MINBLOCKS_R0)) round_kernel(const __grid_constant__ RoundArgs a) {
     extern __shared__ __align__(16) u32 smem[];
     __shared__ u32 red[ROUND_THREADS / 32][PTS * D];
     __shared__ bool is_last;
@@ -230,33 +233,40 @@ __global__ void __launch_bounds__(ROUND_THREADS, FOLD ? SC_MINBLOCKS : SC_MINBLO
                 if (cur_h != ~0ull) flush();
                 cur_h = h;
             }
-            // every load of the pair first, so that they are all in flight together
-            Ext<D> e[NT][NE];
-#pragma unroll
-            for (int t = 0; t < NT; t++) {
+            // F_p^4: every load of the pair first, so that they are all in flight together; F_p^8: table by
+            // table (the entries of four tables at once would not fit the register file)
+            constexpr bool HOIST = D == 4;
+            auto load_table = [&](int t, Ext<D> (&et)[NE]) {
                 if (FOLD == 2) {
                     const uint4 w0 = __ldcs(reinterpret_cast<const uint4 *>(a.src[t]) + 2 * i), w1 = __ldcs(reinterpret_cast<const uint4 *>(a.src[t]) + 2 * i + 1);
-                    e[t][0].v[0] = w0.x; e[t][0].v[1] = w0.y; e[t][0].v[2] = w0.z; e[t][0].v[3] = w0.w;
-                    e[t][1].v[0] = w1.x; e[t][1].v[1] = w1.y; e[t][1].v[2] = w1.z; e[t][1].v[3] = w1.w;
+                    et[0].v[0] = w0.x; et[0].v[1] = w0.y; et[0].v[2] = w0.z; et[0].v[3] = w0.w;
+                    et[1].v[0] = w1.x; et[1].v[1] = w1.y; et[1].v[2] = w1.z; et[1].v[3] = w1.w;
                 } else if ((base_mask >> t) & 1) {
                     if (FOLD == 1) {
                         const uint4 w = __ldcs(reinterpret_cast<const uint4 *>(a.src[t]) + i);
-                        e[t][0].v[0] = w.x; e[t][1].v[0] = w.y; e[t][2].v[0] = w.z; e[t][3].v[0] = w.w;
+                        et[0].v[0] = w.x; et[1 % NE].v[0] = w.y; et[2 % NE].v[0] = w.z; et[3 % NE].v[0] = w.w;
                     } else {
                         const uint2 w = __ldcs(reinterpret_cast<const uint2 *>(a.src[t]) + i);
-                        e[t][0].v[0] = w.x; e[t][1].v[0] = w.y;
+                        et[0].v[0] = w.x; et[1].v[0] = w.y;
                     }
                 } else {
 #pragma unroll
-                    for (int k = 0; k < NE; k++) e[t][k] = load_ext<D>(a.src[t] + (NE * i + k) * D);
+                    for (int k = 0; k < NE; k++) et[k] = load_ext<D>(a.src[t] + (NE * i + k) * D);
                 }
+            };
+            Ext<D> e[HOIST ? NT : 1][NE];
+            if (HOIST) {
+#pragma unroll
+                for (int t = 0; t < NT; t++) load_table(t, e[HOIST ? t : 0]);
             }
             Ext<D> val[NT], slope[NT];
 #pragma unroll
             for (int t = 0; t < NT; t++) {
                 const bool tb = (base_mask >> t) & 1;
+                if (!HOIST) load_table(t, e[0]);
+                Ext<D> (&et)[NE] = e[HOIST ? t : 0];
                 if (FOLD == 2) {
-                    const Ext<D> lo = bound(e[t][0]), hi = bound(e[t][1]);
+                    const Ext<D> lo = bound(et[0]), hi = bound(et[1]);
                     store_ext<D>(a.dst[t] + (2 * i) * D, lo);
                     store_ext<D>(a.dst[t] + (2 * i + 1) * D, hi);
                     val[t] = lo;
@@ -264,26 +274,26 @@ __global__ void __launch_bounds__(ROUND_THREADS, FOLD ? SC_MINBLOCKS : SC_MINBLO
                     if (PTS == 2) slope[t] = eadd<D>(slope[t], hi);
                 } else if (!FOLD) {
                     if (tb) {
-                        val[t] = lift<D>(e[t][0].v[0]);
-                        const u32 sl = fsub(e[t][1].v[0], e[t][0].v[0]);
-                        slope[t] = lift<D>(PTS == 2 ? fadd(sl, e[t][1].v[0]) : sl);
+                        val[t] = lift<D>(et[0].v[0]);
+                        const u32 sl = fsub(et[1].v[0], et[0].v[0]);
+                        slope[t] = lift<D>(PTS == 2 ? fadd(sl, et[1].v[0]) : sl);
                     } else {
-                        val[t] = e[t][0];
-                        slope[t] = esub<D>(e[t][1], e[t][0]);
-                        if (PTS == 2) slope[t] = eadd<D>(slope[t], e[t][1]);
+                        val[t] = et[0];
+                        slope[t] = esub<D>(et[1], et[0]);
+                        if (PTS == 2) slope[t] = eadd<D>(slope[t], et[1]);
                     }
                 } else {
                     // fold entries 4i .. 4i+3 by r: e0 + r (e1 - e0), e2 + r (e3 - e2)  (FOLD-FLAT-TABLE, src/sumcheck.lisp:84-104)
                     Ext<D> lo, hi;
                     if (tb) {   // the slope is a base element: D base products (:96-98)
-                        const u32 s0 = fsub(e[t][1].v[0], e[t][0].v[0]), s1 = fsub(e[t][3].v[0], e[t][2].v[0]);
+                        const u32 s0 = fsub(et[1].v[0], et[0].v[0]), s1 = fsub(et[3 % NE].v[0], et[2 % NE].v[0]);
 #pragma unroll
                         for (int c = 0; c < D; c++) { lo.v[c] = mmul(rm.v[c], s0); hi.v[c] = mmul(rm.v[c], s1); }
-                        lo.v[0] = fadd(lo.v[0], e[t][0].v[0]);
-                        hi.v[0] = fadd(hi.v[0], e[t][2].v[0]);
+                        lo.v[0] = fadd(lo.v[0], et[0].v[0]);
+                        hi.v[0] = fadd(hi.v[0], et[2 % NE].v[0]);
                     } else {
-                        lo = eadd<D>(e[t][0], emul<D>(esub<D>(e[t][1], e[t][0]), rm));
-                        hi = eadd<D>(e[t][2], emul<D>(esub<D>(e[t][3], e[t][2]), rm));
+                        lo = eadd<D>(et[0], emul<D>(esub<D>(et[1], et[0]), rm));
+                        hi = eadd<D>(et[2 % NE], emul<D>(esub<D>(et[3 % NE], et[2 % NE]), rm));
                     }
                     store_ext<D>(a.dst[t] + (2 * i) * D, lo);
                     store_ext<D>(a.dst[t] + (2 * i + 1) * D, hi);
