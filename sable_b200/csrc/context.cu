@@ -450,7 +450,8 @@ extern "C" int sc_set_statement(sc_ctx *ctx, int D, int points, int ntables, int
             else if (tm.ckind == CK_EXT) ok = false;          // an extension constant term
             else base_terms++;
         }
-        if (ext_terms > 1 || nterms == 0) ok = false;
+        if (ext_terms > 1 || nterms == 0 || nterms > BASE_MAX_TERMS) ok = false;
+        for (int t = 0; t < nterms; t++) if (ctx->st.terms[t].nf > BASE_MAX_FACTORS) ok = false;
         ctx->base_groups = ok ? (base_terms > 0) + ext_terms : 0;
         memset(ctx->gcoef, 0, sizeof ctx->gcoef);
         ctx->gcoef[0][0] = R1;

@@ -75,6 +75,8 @@ struct RoundArgs {
     u32 gcoef[2][8];      // Montgomery form
 };
 constexpr int MAX_GROUPS = 2;
+constexpr int BASE_MAX_TERMS = 4;      // the base-table kernel keeps its term descriptors in registers:
+constexpr int BASE_MAX_FACTORS = 4;    // statements beyond these run the general kernel
 constexpr int PARTIAL_ROW_WORDS = MAX_GROUPS * MAX_PARTIAL_WORDS;   // words per block in the partials buffer
 
 // Launchers (defined next to their kernels).  Each returns the CUDA error of the launch.

@@ -35,6 +35,20 @@ __global__ void __launch_bounds__(ROUND_THREADS, 2) round_base_kernel(const __gr
         __syncthreads();
     }
 
+    // term descriptors in registers: factors | kind | group | table positions, and the base coefficient
+    const int nterms = a.st.nterms;
+    u32 desc[BASE_MAX_TERMS], coef[BASE_MAX_TERMS];
+#pragma unroll
+    for (int t = 0; t < BASE_MAX_TERMS; t++) {
+        desc[t] = 0; coef[t] = 0;
+        if (t < nterms) {
+            const DevTerm &tm = a.st.terms[t];
+            u32 ds = (u32)tm.nf | ((u32)tm.ckind << 4) | ((u32)tm.group << 6);
+            for (int k = 0; k < BASE_MAX_FACTORS && k < tm.nf; k++) ds |= (u32)tm.f[k] << (8 + 4 * k);
+            desc[t] = ds;
+            coef[t] = tm.coeff[0];
+        }
+    }
     u32 total[NG][PTS][D];
     u64 acc[NG][PTS][D];
 #pragma unroll
@@ -90,11 +104,28 @@ __global__ void __launch_bounds__(ROUND_THREADS, 2) round_base_kernel(const __gr
         have_inner = false;
     };
 
-    const u64 chunk = L > (u32)ROUND_THREADS ? L : ROUND_THREADS;
+    // two neighbouring pairs per thread and iteration: one 128-bit load per table keeps twice the bytes in flight
+    const u64 chunk = L > (u32)(2 * ROUND_THREADS) ? L : 2 * ROUND_THREADS;
     for (u64 base = (u64)blockIdx.x * chunk; base < a.npairs; base += (u64)gridDim.x * chunk) {
-        for (u64 q = tid; q < chunk; q += ROUND_THREADS) {
-            const u64 i = base + q;
-            if (i >= a.npairs) break;
+        for (u64 q = 2 * (u64)tid; q < chunk; q += 2 * ROUND_THREADS) {
+            const u64 i0 = base + q;
+            if (i0 >= a.npairs) break;
+            const bool two = i0 + 1 < a.npairs;
+            u32 lo2[2][NT], hi2[2][NT];
+#pragma unroll
+            for (int t = 0; t < NT; t++) {
+                if (two) {
+                    const uint4 w = __ldcs(reinterpret_cast<const uint4 *>(a.src[t] + 2 * i0));
+                    lo2[0][t] = w.x; hi2[0][t] = w.y; lo2[1][t] = w.z; hi2[1][t] = w.w;
+                } else {
+                    const uint2 w = __ldcs(reinterpret_cast<const uint2 *>(a.src[t]) + i0);
+                    lo2[0][t] = w.x; hi2[0][t] = w.y; lo2[1][t] = 0; hi2[1][t] = 0;
+                }
+            }
+#pragma unroll
+            for (int pp = 0; pp < 2; pp++) {
+            if (pp == 1 && !two) break;
+            const u64 i = i0 + pp;
             const u64 h = i >> a.logL;
             if (h != cur_h) {
                 if (cur_h != ~0ull) flush();
@@ -103,9 +134,8 @@ __global__ void __launch_bounds__(ROUND_THREADS, 2) round_base_kernel(const __gr
             u32 val[NT], slope[NT];
 #pragma unroll
             for (int t = 0; t < NT; t++) {
-                const uint2 w = __ldcs(reinterpret_cast<const uint2 *>(a.src[t]) + i);
-                val[t] = w.x;
-                slope[t] = fsub(w.y, w.x);
+                val[t] = lo2[pp][t];
+                slope[t] = fsub(hi2[pp][t], lo2[pp][t]);
             }
             u32 lw[D];
             if (a.use_low) {
@@ -137,17 +167,24 @@ __global__ void __launch_bounds__(ROUND_THREADS, 2) round_base_kernel(const __gr
                     for (int t = 1; t < NT; t++) pr = mmul(pr, val[t]);
                     m[0] = pr;
                 } else {
-                    for (int t = 0; t < a.st.nterms; t++) {
-                        const DevTerm &tm = a.st.terms[t];
-                        u32 pr;
-                        if (tm.nf == 0) pr = tm.coeff[0];
-                        else {
-                            pr = pick_base<NT>(val, tm.f[0]);
-                            for (int k = 1; k < tm.nf; k++) pr = mmul(pr, pick_base<NT>(val, tm.f[k]));
-                            if (tm.ckind == CK_BASE) pr = mmul(pr, tm.coeff[0]);
+                    // the terms, from the descriptors held in registers (see BASE_MAX_TERMS)
+#pragma unroll
+                    for (int t = 0; t < BASE_MAX_TERMS; t++) {
+                        if (t < nterms) {
+                            const u32 ds = desc[t];
+                            const int nf = ds & 15, ckind = (ds >> 4) & 3, group = (ds >> 6) & 3;
+                            u32 pr;
+                            if (nf == 0) pr = coef[t];
+                            else {
+                                pr = pick_base<NT>(val, (ds >> 8) & 15);
+#pragma unroll
+                                for (int k = 1; k < BASE_MAX_FACTORS; k++)
+                                    if (k < nf) pr = mmul(pr, pick_base<NT>(val, (ds >> (8 + 4 * k)) & 15));
+                                if (ckind == CK_BASE) pr = mmul(pr, coef[t]);
+                            }
+                            if (NG == 1 || group == 0) m[0] = fadd(m[0], pr);
+                            else m[NG - 1] = fadd(m[NG - 1], pr);
                         }
-                        if (NG == 1 || tm.group == 0) m[0] = fadd(m[0], pr);
-                        else m[NG - 1] = fadd(m[NG - 1], pr);
                     }
                 }
 #pragma unroll
@@ -156,6 +193,7 @@ __global__ void __launch_bounds__(ROUND_THREADS, 2) round_base_kernel(const __gr
                     for (int c = 0; c < D; c++) acc[g][x][c] += (u64)lw[c] * m[g];
             }
             if (++pending == 4) reduce();
+            }
         }
     }
     if (cur_h != ~0ull) flush();

@@ -43,12 +43,24 @@ __global__ void __launch_bounds__(ROUND_THREADS, 1) sv_kernel(const __grid_const
         pending = 0;
     };
 
+    // the next block's entries are asked for before this block's arithmetic starts
+    uint4 next[NT];
+    if (h0 < h1) {
+#pragma unroll
+        for (int t = 0; t < NT; t++) next[t] = __ldcs(reinterpret_cast<const uint4 *>(a.src[t]) + (h0 * L + l));
+    }
     for (u64 h = h0; h < h1; h++) {
-        const u64 i = h * L + l;
+        uint4 cur[NT];
+#pragma unroll
+        for (int t = 0; t < NT; t++) cur[t] = next[t];
+        if (h + 1 < h1) {
+#pragma unroll
+            for (int t = 0; t < NT; t++) next[t] = __ldcs(reinterpret_cast<const uint4 *>(a.src[t]) + ((h + 1) * L + l));
+        }
         u32 g[NT][Z];
 #pragma unroll
         for (int t = 0; t < NT; t++) {
-            const uint4 e = __ldcs(reinterpret_cast<const uint4 *>(a.src[t]) + i);
+            const uint4 e = cur[t];
             // entries (b0, b1) = e.x (0,0), e.y (1,0), e.z (0,1), e.w (1,1); extend variable 0, then variable 1, by additions
             u32 row[2][G];
             row[0][0] = e.x; row[0][1] = e.y; row[1][0] = e.z; row[1][1] = e.w;
