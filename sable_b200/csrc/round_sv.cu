@@ -6,13 +6,19 @@
 // 64-bit sums, four blocks per reduction (four products below p^2 fit 64 bits, as in REDUCED-SUM,
 // src/field.lisp:213-218); the reduced sums wait in shared memory, and the low weight multiplies
 // once at the very end.  Blocks' rows are added by the last block to finish (no waiting).
+// With G > 2 the grid is cut in two along its second variable (blockIdx.y): rows z1 < 2, which
+// are the entries' own rows, and rows z1 >= 2; half the sums per thread lets two blocks share an SM.
 #include "round_kernel.cuh"
 
 namespace sc {
 
 template <int D, int G, int NT>
-__global__ void __launch_bounds__(ROUND_THREADS, 1) sv_kernel(const __grid_constant__ SvArgs a) {
-    constexpr int Z = G * G, W = Z * D;
+__global__ void __launch_bounds__(ROUND_THREADS, G > 2 ? 2 : 1) sv_kernel(const __grid_constant__ SvArgs a) {
+    constexpr int ROWS1 = 2;                      // rows of the grid (values of z1) a block handles, at most
+    constexpr int Z = G * ROWS1, W = Z * D;       // this block's share of the accumulators
+    constexpr int WALL = G * G * D;               // all of them
+    const int z1lo = blockIdx.y * ROWS1;          // its first row
+    const int nrows = (G - z1lo) < ROWS1 ? (G - z1lo) : ROWS1;
     extern __shared__ __align__(16) u32 tot[];   // [W][ROUND_THREADS]
     __shared__ bool is_last;
     const int tid = threadIdx.x;
@@ -72,11 +78,14 @@ __global__ void __launch_bounds__(ROUND_THREADS, 1) sv_kernel(const __grid_const
             }
 #pragma unroll
             for (int z0 = 0; z0 < G; z0++) {
-                const u32 s = fsub(row[1][z0], row[0][z0]);
-                g[t][z0] = row[0][z0];
-                g[t][z0 + G] = row[1][z0];
-#pragma unroll
-                for (int z1 = 2; z1 < G; z1++) g[t][z0 + G * z1] = fadd(g[t][z0 + G * (z1 - 1)], s);
+                if (z1lo == 0) {           // rows 0 and 1: the entries' own rows
+                    g[t][z0] = row[0][z0];
+                    g[t][z0 + G] = row[1][z0];
+                } else {                   // rows 2 and 3: row 1 plus one and two slopes
+                    const u32 s = fsub(row[1][z0], row[0][z0]);
+                    g[t][z0] = fadd(row[1][z0], s);
+                    g[t][z0 + G] = fadd(g[t][z0], s);
+                }
             }
         }
         u32 hw[D];
@@ -116,28 +125,28 @@ __global__ void __launch_bounds__(ROUND_THREADS, 1) sv_kernel(const __grid_const
         }
     }
     __syncthreads();
-    // the block's row: word k summed over the threads
-    for (int k = tid >> 5; k < W; k += ROUND_THREADS / 32) {
+    // the block's share of its row of partial sums: word k summed over the threads
+    for (int k = tid >> 5; k < nrows * G * D; k += ROUND_THREADS / 32) {
         u32 v = 0;
         for (int j = tid & 31; j < ROUND_THREADS; j += 32) v = fadd(v, tot[k * ROUND_THREADS + j]);
 #pragma unroll
         for (int off = 16; off > 0; off >>= 1) v = fadd(v, __shfl_down_sync(0xffffffffu, v, off));
-        if ((tid & 31) == 0) a.partials[(size_t)blockIdx.x * W + k] = v;
+        if ((tid & 31) == 0) a.partials[(size_t)blockIdx.x * WALL + z1lo * G * D + k] = v;
     }
     __threadfence();
     __syncthreads();
-    if (tid == 0) is_last = atomicAdd(a.counter, 1u) == gridDim.x - 1;
+    if (tid == 0) is_last = atomicAdd(a.counter, 1u) == gridDim.x * gridDim.y - 1;
     __syncthreads();
     if (!is_last) return;
     __threadfence();
     __shared__ u32 row[SV_MAX_WORDS];
-    if (tid < W) {
+    if (tid < WALL) {
         u32 v = 0;
-        for (unsigned b = 0; b < gridDim.x; b++) v = fadd(v, __ldcg(a.partials + (size_t)b * W + tid));
+        for (unsigned b = 0; b < gridDim.x; b++) v = fadd(v, __ldcg(a.partials + (size_t)b * WALL + tid));
         row[tid] = v;
     }
     __syncthreads();
-    if (tid < Z) {
+    if (tid < G * G) {
         Ext<D> s;
 #pragma unroll
         for (int c = 0; c < D; c++) s.v[c] = row[tid * D + c];
@@ -164,9 +173,9 @@ __global__ void __launch_bounds__(ROUND_THREADS, 1) sv_kernel(const __grid_const
 }
 
 template <int D, int G, int NT> static cudaError_t launch_sv_one(const SvArgs &args, int grid, cudaStream_t stream) {
-    const size_t smem = (size_t)G * G * D * ROUND_THREADS * 4;
+    const size_t smem = (size_t)G * 2 * D * ROUND_THREADS * 4;
     cudaFuncSetAttribute(sv_kernel<D, G, NT>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-    sv_kernel<D, G, NT><<<grid, ROUND_THREADS, smem, stream>>>(args);
+    sv_kernel<D, G, NT><<<dim3(grid, G > 2 ? 2 : 1), ROUND_THREADS, smem, stream>>>(args);
     return cudaGetLastError();
 }
 bool small_values_supported(int D, int G, int nt) { return D == 4 && nt >= 1 && nt <= 3 && G == nt + 1; }
