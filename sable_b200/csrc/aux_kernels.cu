@@ -8,10 +8,18 @@ namespace sc {
 cudaError_t launch_round_d4(int shape, int points, int nt, int fold, const RoundArgs &args, int grid, size_t smem, cudaStream_t stream);
 cudaError_t launch_round_d8(int shape, int points, int nt, int fold, const RoundArgs &args, int grid, size_t smem, cudaStream_t stream);
 
+cudaError_t launch_round_d4w(int points, int nt, int fold, const RoundArgs &args, int grid, size_t smem, cudaStream_t stream);
+cudaError_t launch_round_d8w(int points, int nt, int fold, const RoundArgs &args, int grid, size_t smem, cudaStream_t stream);
+
 bool round_supported(int D, int points, int nt_used) {
-    return (D == 4 || D == 8) && points >= 1 && points <= SC_MAX_POINTS && nt_used >= 1 && nt_used <= 4;
+    return (D == 4 || D == 8) && points >= 1 && points <= SC_MAX_POINTS && nt_used >= 1 && nt_used <= 8;
 }
 cudaError_t launch_round(int D, int shape, int points, int nt_used, int fold, const RoundArgs &args, int grid, size_t smem, cudaStream_t stream) {
+    if (nt_used > 4) {   // kernels exist for six and eight tables
+        const int nt = nt_used <= 6 ? 6 : 8;
+        if (fold == 2) return cudaErrorInvalidValue;
+        return D == 4 ? launch_round_d4w(points, nt, fold, args, grid, smem, stream) : launch_round_d8w(points, nt, fold, args, grid, smem, stream);
+    }
     if (D == 4) return launch_round_d4(shape, points, nt_used, fold, args, grid, smem, stream);
     if (D == 8) return launch_round_d8(shape, points, nt_used, fold, args, grid, smem, stream);
     return cudaErrorInvalidValue;

@@ -338,6 +338,29 @@ static void ext_mul_host(int D, const u32 *a, const u32 *b, u32 *o) {
     }
 }
 
+// 1/a for a nonzero element in Montgomery form, as a^(p^D - 2) (the same element as the reference's norm
+// descent, INV*, src/field.lisp:236-243); used once per statement at most
+static void ext_inv_host(int D, const u32 *a, u32 *o) {
+    u32 ex[9] = {1, 0, 0, 0, 0, 0, 0, 0, 0};   // p^D - 2, little-endian 32-bit words
+    int len = 1;
+    for (int k = 0; k < D; k++) {
+        u64 carry = 0;
+        for (int i = 0; i < len; i++) { const u64 t = (u64)ex[i] * P + carry; ex[i] = (u32)t; carry = t >> 32; }
+        if (carry) ex[len++] = (u32)carry;
+    }
+    for (int i = 0, borrow = 2; i < len && borrow; i++) {
+        if (ex[i] >= (u32)borrow) { ex[i] -= (u32)borrow; borrow = 0; } else { ex[i] -= (u32)borrow; borrow = 1; }
+    }
+    u32 r[8] = {R1, 0, 0, 0, 0, 0, 0, 0}, base[8];
+    memcpy(base, a, 4 * (size_t)D);
+    for (int i = 0; i < len; i++)
+        for (int b = 0; b < 32; b++) {
+            if ((ex[i] >> b) & 1) ext_mul_host(D, r, base, r);
+            ext_mul_host(D, base, base, base);
+        }
+    memcpy(o, r, 4 * (size_t)D);
+}
+
 // R^k mod p for any integer k (R = 2^32)
 static u32 pow_r(int k) {
     auto pw = [](u32 b, u64 ex) { u64 r = 1, x = b; for (; ex; ex >>= 1) { if (ex & 1) r = r * x % P; x = x * x % P; } return (u32)r; };
@@ -369,12 +392,20 @@ extern "C" int sc_set_statement(sc_ctx *ctx, int D, int points, int ntables, int
     for (int t = 0; t < nterms; t++) for (int k = term_ptr[t]; k < term_ptr[t + 1]; k++) occurrences[term_tables[k]]++;
     int nt_used = 0;
     for (int s = 0; s < ntables; s++) nt_used += used[s];
-    if (nt_used > 4) return fail(ctx, SC_EUNSUPPORTED, "the statement multiplies %d different tables: at most 4", nt_used);
+    if (nt_used > 8) return fail(ctx, SC_EUNSUPPORTED, "the statement multiplies %d different tables: at most 8", nt_used);
 
     // statements with a kernel of their own (see Shape)
-    int shape = SHAPE_GENERIC, lam_term = -1;
+    int shape = SHAPE_GENERIC, lam_term = -1, a_term = -1, b_term = -1;
     int first[SC_MAX_TABLES];
     int nfirst = 0;
+    auto same_coefficient = [&](int t, int u) {
+        bool nonzero = false;
+        for (int c = 0; c < D; c++) {
+            if (coeffs[(size_t)t * D + c] % P != coeffs[(size_t)u * D + c] % P) return false;
+            nonzero = nonzero || coeffs[(size_t)t * D + c] % P != 0;
+        }
+        return nonzero;
+    };
     auto is_one = [&](int t) {
         for (int c = 0; c < D; c++) if (coeffs[(size_t)t * D + c] % P != (c == 0 ? 1u : 0u)) return false;
         return true;
@@ -395,10 +426,13 @@ extern "C" int sc_set_statement(sc_ctx *ctx, int D, int points, int ntables, int
             for (int t = 0; t < 3; t++) {
                 const int x = term_tables[term_ptr[t]], y = term_tables[term_ptr[t] + 1];
                 if ((x == c && y == d) || (x == d && y == c)) lam_term = t;
-                else if ((x == d || y == d) && is_one(t)) a = (x == d) ? y : x;
-                else if ((x == c || y == c) && is_one(t)) b = (x == c) ? y : x;
+                else if (x == d || y == d) { a = (x == d) ? y : x; a_term = t; }
+                else if (x == c || y == c) { b = (x == c) ? y : x; b_term = t; }
             }
-            if (lam_term >= 0 && a >= 0 && b >= 0 && a != b && occurrences[a] == 1 && occurrences[b] == 1) {
+            // the two single products must carry one and the same coefficient: it is taken out in front
+            // (reference LAYER-STATEMENT: a (p0 q1 + p1 q0) + (a lambda) q0 q1, src/gkr.lisp:30-41)
+            if (lam_term >= 0 && a >= 0 && b >= 0 && a != b && occurrences[a] == 1 && occurrences[b] == 1 &&
+                same_coefficient(a_term, b_term)) {
                 shape = SHAPE_GKR;
                 first[0] = a; first[1] = b; first[2] = c; first[3] = d; nfirst = 4;
             }
@@ -432,6 +466,21 @@ extern "C" int sc_set_statement(sc_ctx *ctx, int D, int points, int ntables, int
             c[k] = (u32)(((u64)(coeffs[(size_t)t * D + k] % P) * scale) % P);
             if (k && c[k]) upper = true;
         }
+        if (shape == SHAPE_GKR && !is_one(a_term)) {
+            // a common coefficient ca in front: terms a and b become 1, lam becomes c_lam / ca, ca waits for the final factor
+            if (t == lam_term) {
+                u32 ca[8], inv[8], cl[8];
+                for (int k = 0; k < D; k++) { ca[k] = to_mont(coeffs[(size_t)a_term * D + k] % P); cl[k] = c[k]; }
+                ext_inv_host(D, ca, inv);
+                ext_mul_host(D, cl, inv, c);   // canonical * Montgomery -> canonical
+                upper = false;
+                for (int k = 1; k < D; k++) upper = upper || c[k];
+            } else {
+                for (int k = 0; k < D; k++) { ctx->st_factor[k] = c[k]; c[k] = k == 0 ? 1u : 0u; }
+                ctx->use_factor = true;
+                upper = false;
+            }
+        }
         tm.ckind = upper ? CK_EXT : (c[0] == 1 ? CK_ONE : CK_BASE);
         for (int k = 0; k < D; k++) tm.coeff[k] = tm.nf ? to_mont(c[k]) : c[k];
         if (shape == SHAPE_PRODUCT) {   // the coefficient waits for the final factor
@@ -450,7 +499,7 @@ extern "C" int sc_set_statement(sc_ctx *ctx, int D, int points, int ntables, int
             else if (tm.ckind == CK_EXT) ok = false;          // an extension constant term
             else base_terms++;
         }
-        if (ext_terms > 1 || nterms == 0 || nterms > BASE_MAX_TERMS) ok = false;
+        if (ext_terms > 1 || nterms == 0 || nterms > BASE_MAX_TERMS || nt_used > 4) ok = false;
         for (int t = 0; t < nterms; t++) if (ctx->st.terms[t].nf > BASE_MAX_FACTORS) ok = false;
         ctx->base_groups = ok ? (base_terms > 0) + ext_terms : 0;
         memset(ctx->gcoef, 0, sizeof ctx->gcoef);
@@ -848,7 +897,7 @@ static int sv_round1(sc_ctx *ctx, uint32_t *sums) {
 // The last rounds run in one resident launch when the tables are small, there is one block of
 // weights, and nobody asked for per-round timing.
 static bool tail_wanted(const sc_ctx *ctx) {
-    if (ctx->tail_bits <= 0 || ctx->K != 1 || ctx->timing || ctx->ntables < 1) return false;
+    if (ctx->tail_bits <= 0 || ctx->K != 1 || ctx->timing || ctx->ntables < 1 || ctx->nt_used > 4) return false;
     if (ctx->n - ctx->j > TAIL_MAX_ROUNDS) return false;
     return ctx->tab[ctx->order[0]].cur_entries <= (1ull << ctx->tail_bits);
 }
@@ -977,6 +1026,8 @@ extern "C" int sc_round(sc_ctx *ctx, uint32_t *sums) {
             bytes += in_entries / shrink * (u64)D * 4;
         }
     }
+    // a statement over five or seven tables runs the kernel for six or eight: the spare position repeats position 0
+    for (int k = ctx->ntables; k < SC_MAX_TABLES; k++) { a.src[k] = a.src[0]; a.dst[k] = a.dst[0]; a.src_base[k] = a.src_base[0]; }
     a.npairs = fold ? in_entries / (2 * shrink) : in_entries / 2;
     if (fold) challenge_words(ctx, a.r);
     if (bind2) {   // eq(rho0 rho1, b): bit 0 of b pairs with rho0 (EQ-TABLE, src/field.lisp:354-363)

@@ -153,7 +153,7 @@ __device__ __forceinline__ Ext<D> eval_gkr(const Ext<D> (&val)[4], const ExtM<D>
 }
 
 template <int D, int PTS, int NT, int FOLD, int SHAPE>
-__global__ void __launch_bounds__(ROUND_THREADS, D == 8 ? SC_MINBLOCKS_D8 : (FOLD ? SC_MINBLOCKS : SC_MINBLOCKS_R0)) round_kernel(const __grid_constant__ RoundArgs a) {
+__global__ void __launch_bounds__(ROUND_THREADS, NT > 4 ? 1 : (D == 8 ? SC_MINBLOCKS_D8 : (FOLD ? SC_MINBLOCKS : SC_MINBLOCKS_R0))) round_kernel(const __grid_constant__ RoundArgs a) {
     extern __shared__ __align__(16) u32 smem[];
     __shared__ u32 red[ROUND_THREADS / 32][PTS * D];
     __shared__ bool is_last;
@@ -235,7 +235,7 @@ __global__ void __launch_bounds__(ROUND_THREADS, D == 8 ? SC_MINBLOCKS_D8 : (FOL
             }
             // F_p^4: every load of the pair first, so that they are all in flight together; F_p^8: table by
             // table (the entries of four tables at once would not fit the register file)
-            constexpr bool HOIST = D == 4;
+            constexpr bool HOIST = D == 4 && NT <= 4;
             auto load_table = [&](int t, Ext<D> (&et)[NE]) {
                 if (FOLD == 2) {
                     const uint4 w0 = __ldcs(reinterpret_cast<const uint4 *>(a.src[t]) + 2 * i), w1 = __ldcs(reinterpret_cast<const uint4 *>(a.src[t]) + 2 * i + 1);
@@ -494,6 +494,25 @@ static cudaError_t launch_round_shape(int shape, int points, int nt, int fold, c
         }
     }
     return cudaErrorInvalidValue;
+}
+
+// Statements over five to eight tables: the term-table kernel for six or eight tables (a statement
+// over five or seven gets one more position, a copy of position 0 that no term names).
+template <int D, int PTS>
+static cudaError_t launch_round_wide_p(int nt, int fold, const RoundArgs &args, int grid, size_t smem, cudaStream_t stream) {
+    if (nt == 6) return launch_round_dpns<D, PTS, 6, SHAPE_GENERIC>(fold, args, grid, smem, stream);
+    if (nt == 8) return launch_round_dpns<D, PTS, 8, SHAPE_GENERIC>(fold, args, grid, smem, stream);
+    return cudaErrorInvalidValue;
+}
+template <int D>
+static cudaError_t launch_round_wide(int points, int nt, int fold, const RoundArgs &args, int grid, size_t smem, cudaStream_t stream) {
+    switch (points) {
+    case 1: return launch_round_wide_p<D, 1>(nt, fold, args, grid, smem, stream);
+    case 2: return launch_round_wide_p<D, 2>(nt, fold, args, grid, smem, stream);
+    case 3: return launch_round_wide_p<D, 3>(nt, fold, args, grid, smem, stream);
+    case 4: return launch_round_wide_p<D, 4>(nt, fold, args, grid, smem, stream);
+    default: return cudaErrorInvalidValue;
+    }
 }
 
 template <int D>

@@ -357,3 +357,46 @@ def test_slow_host_falls_back_to_a_launch_per_round(monkeypatch):
             assert rho == want[0] and finals == [want[1]["a"], want[1]["b"]] and tr.proof() == tb.proof()
     finally:
         p.close()
+
+
+def layer_statement(lookups):
+    """The LogUp-GKR layer statement (reference LAYER-STATEMENT, src/gkr.lisp:30-41)."""
+    terms, tables, constants = [], [], []
+    for l in range(lookups):
+        p0, p1, q0, q1, a, al = ("%s%d" % (nm, l) for nm in ("p0-", "p1-", "q0-", "q1-", "a", "al"))
+        tables += [p0, p1, q0, q1]
+        constants += [a, al]
+        terms += ["(* %s %s %s)" % (a, p0, q1), "(* %s %s %s)" % (a, p1, q0), "(* %s %s %s)" % (al, q0, q1)]
+    return "(+ %s)" % " ".join(terms), tables, constants
+
+
+@pytest.mark.parametrize("d", [4, 8])
+@pytest.mark.parametrize("lookups", [1, 2])
+def test_gkr_layer_statements(prover, d, lookups):
+    # one lookup: the coefficient a in front of both single products is taken out (built-in kernel);
+    # two lookups: eight tables, the term-table kernel for eight tables; with block weights as the caller uses them
+    statement, names, cnames = layer_statement(lookups)
+    rng = np.random.default_rng(40 + d + lookups)
+    for n, K, kinds in ((10, 1, "ext"), (14, 1, "mixed"), (5, 3, "ext"), (1, 1, "base")):
+        tables = []
+        for t, nm in enumerate(names):
+            base = kinds == "base" or (kinds == "mixed" and t % 4 < 2)
+            tables.append((nm, rng.integers(0, P, size=K << n, dtype=np.uint32) if base else rand_ext(rng, d, K << n)))
+        constants = [(c, rand_ext(rng, d).tolist()) for c in cnames]
+        bw = rand_ext(rng, d, K) if K > 1 else None
+        got, want, ta, tb = both(prover, d, n, statement, tables, eq=rand_ext(rng, d, n), constants=constants,
+                                 block_weights=bw, label="gkr", degree=2, threads=0)
+        assert_same(got, want, ta, tb)
+
+
+@pytest.mark.parametrize("nt", [5, 6, 7, 8])
+def test_statements_over_more_than_four_tables(prover, nt):
+    d = 4
+    rng = np.random.default_rng(nt)
+    names = ["t%d" % t for t in range(nt)]
+    statement = "(+ %s (* 3 %s %s) -1)" % (" ".join("(* %s %s)" % (names[t], names[(t + 1) % nt]) for t in range(nt)), names[0], names[nt - 1])
+    for n in (1, 6, 13):
+        tables = [(nm, rng.integers(0, P, size=1 << n, dtype=np.uint32) if t % 3 == 0 else rand_ext(rng, d, 1 << n)) for t, nm in enumerate(names)]
+        tables.append(("unused", rand_ext(rng, d, 1 << n)))
+        got, want, ta, tb = both(prover, d, n, statement, tables[:8], eq=rand_ext(rng, d, n))
+        assert_same(got, want, ta, tb)
