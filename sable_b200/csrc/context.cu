@@ -208,7 +208,7 @@ static bool wait_word(sc_ctx *ctx, const u32 *word, u32 want) {
     const auto t0 = std::chrono::steady_clock::now();
     for (u64 spin = 0;; spin++) {
         if (*w == want) { std::atomic_thread_fence(std::memory_order_acquire); return true; }
-        if ((spin & 0xfff) == 0xfff) {
+        if ((spin & 0xfffff) == 0xfffff) {
             if (cudaStreamQuery(ctx->stream) != cudaErrorNotReady) {
                 cudaStreamSynchronize(ctx->stream);
                 std::atomic_thread_fence(std::memory_order_acquire);
@@ -1098,7 +1098,7 @@ extern "C" int sc_round(sc_ctx *ctx, uint32_t *sums) {
         bool seen = false;
         for (u64 spin = 0; !seen; spin++) {
             if (*flag == a.seq) { seen = true; break; }
-            if ((spin & 0xfff) == 0xfff) {
+            if ((spin & 0xfffff) == 0xfffff) {
                 cudaError_t q = cudaStreamQuery(ctx->stream);
                 if (q != cudaErrorNotReady) break;   // finished (the flag is about to show) or failed
                 if (std::chrono::steady_clock::now() - t0 > std::chrono::seconds(20)) break;

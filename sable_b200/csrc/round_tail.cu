@@ -134,9 +134,13 @@ __global__ void __launch_bounds__(ROUND_THREADS) tail_kernel(const __grid_consta
                 if (ld_sys(slot + 48) == a.seq + (u32)k) { ok = 1; break; }
                 if ((poll & 63) == 63 && ld_sys(a.host + TAIL_STOP) == a.seq) { ok = -1; break; }
             }
-            if (ok == 1) {
+            if (ok == 1) {   // the challenge in one 128-bit read per four words (each read is a trip over PCIe)
 #pragma unroll
-                for (int c = 0; c < D; c++) chal[c] = ld_sys(slot + 40 + c);
+                for (int c = 0; c < D; c += 4) {
+                    uint4 v;
+                    asm volatile("ld.volatile.global.v4.u32 {%0, %1, %2, %3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "l"(slot + 40 + c));
+                    chal[c] = v.x; chal[c + 1] = v.y; chal[c + 2] = v.z; chal[c + 3] = v.w;
+                }
             } else {
                 st_sys(a.host + TAIL_STATUS, ok == 0 ? 2u : 3u);
             }
