@@ -73,7 +73,7 @@ def algorithmic_bytes(cfg, n, D):
 
 
 class ClockSampler:
-    """nvidia-smi clocks and throttle reasons every 200 ms while the timed region runs."""
+    """nvidia-smi clocks and throttle reasons every 50 ms from the first timed step to the last end-to-end step."""
     FIELDS = "index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown," \
              "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap"
 
@@ -82,7 +82,7 @@ class ClockSampler:
 
     def start(self):
         try:
-            self.proc = subprocess.Popen(["nvidia-smi", "--query-gpu=" + self.FIELDS, "--format=csv,noheader,nounits", "-lms", "200"],
+            self.proc = subprocess.Popen(["nvidia-smi", "--query-gpu=" + self.FIELDS, "--format=csv,noheader,nounits", "-lms", "50"],
                                          stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
             threading.Thread(target=self._read, daemon=True).start()
         except OSError:
@@ -239,7 +239,6 @@ def main():
     if rank == 0:
         sampler.start()
     ms, wall, launches, tr, out = timed(resident, args.steps)
-    clocks = sampler.stop() if rank == 0 else None
     ms_per_step = ms / args.steps
     value = (1 << n) / (ms_per_step * 1e-3) / 1e6
     proof_bytes = tr.proof()
@@ -281,6 +280,7 @@ def main():
         e2e = {"value": (1 << n) / (ewall / e2e_steps * 1e-3) / 1e6, "unit": "Mentries/s", "h2d_bytes_per_step": h2d * world,
                "d2h_bytes_per_step": d2h, "steps": e2e_steps, "ms_per_step": ewall / e2e_steps}
 
+    clocks = sampler.stop() if rank == 0 else None
     cpu = None
     if rank == 0 and world == 1 and not args.no_cpu:
         n_sample = min(n, args.cpu_n)

@@ -32,6 +32,7 @@ struct Nccl {
     ncclResult_t (*GetUniqueId)(ncclUniqueId *) = nullptr;
     ncclResult_t (*CommInitRank)(ncclComm_t *, int, ncclUniqueId, int) = nullptr;
     ncclResult_t (*CommDestroy)(ncclComm_t) = nullptr;
+    ncclResult_t (*CommAbort)(ncclComm_t) = nullptr;
     ncclResult_t (*AllGather)(const void *, void *, size_t, int, ncclComm_t, cudaStream_t) = nullptr;
     const char *(*GetErrorString)(ncclResult_t) = nullptr;
     bool load() {
@@ -45,9 +46,10 @@ struct Nccl {
         GetUniqueId = (decltype(GetUniqueId))dlsym(handle, "ncclGetUniqueId");
         CommInitRank = (decltype(CommInitRank))dlsym(handle, "ncclCommInitRank");
         CommDestroy = (decltype(CommDestroy))dlsym(handle, "ncclCommDestroy");
+        CommAbort = (decltype(CommAbort))dlsym(handle, "ncclCommAbort");
         AllGather = (decltype(AllGather))dlsym(handle, "ncclAllGather");
         GetErrorString = (decltype(GetErrorString))dlsym(handle, "ncclGetErrorString");
-        return GetUniqueId && CommInitRank && CommDestroy && AllGather && GetErrorString;
+        return GetUniqueId && CommInitRank && CommDestroy && CommAbort && AllGather && GetErrorString;
     }
 } g_nccl;
 }  // namespace
@@ -150,6 +152,7 @@ struct sc_ctx {
     // communicator
     ncclComm_t comm = nullptr;
     int rank = 0, world = 1, logw = 0;
+    int comm_timeout_s = 30;         // a round whose exchange has not finished after this long aborts the communicator
 };
 
 static int fail(sc_ctx *c, int code, const char *fmt, ...) {
@@ -201,8 +204,18 @@ static void tail_stop(sc_ctx *ctx) {
     ctx->tail_active = false;
 }
 
+// A collective that does not finish (a rank left, a link went down) is ended from the host: the
+// communicator is aborted, which makes its kernels return, and the context goes back to one GPU.
+static void comm_abort(sc_ctx *ctx) {
+    if (!ctx->comm) return;
+    g_nccl.CommAbort(ctx->comm);
+    ctx->comm = nullptr;
+    ctx->world = 1; ctx->rank = 0; ctx->logw = 0;
+    ctx->begun = false;
+}
+
 // Wait until a word of mapped memory holds WANT.  Bounded: the stream finishing without the word
-// showing, or 30 seconds passing, ends the wait.
+// showing, or the time limit passing, ends the wait (with a communicator, by aborting it).
 static bool wait_word(sc_ctx *ctx, const u32 *word, u32 want) {
     volatile const u32 *w = word;
     const auto t0 = std::chrono::steady_clock::now();
@@ -214,7 +227,10 @@ static bool wait_word(sc_ctx *ctx, const u32 *word, u32 want) {
                 std::atomic_thread_fence(std::memory_order_acquire);
                 return *w == want;
             }
-            if (std::chrono::steady_clock::now() - t0 > std::chrono::seconds(30)) return false;
+            if (std::chrono::steady_clock::now() - t0 > std::chrono::seconds(ctx->comm_timeout_s)) {
+                comm_abort(ctx);
+                return false;
+            }
         }
     }
 }
@@ -264,6 +280,7 @@ extern "C" int sc_create(int device, sc_ctx **out) {
         cudaHostGetDevicePointer(&ctx->h_sv_dev, ctx->h_sv, 0) != cudaSuccess) { cudaGetLastError(); sc_destroy(ctx); return SC_ECUDA; }
     memset(ctx->h_sv, 0, (SV_MAX_WORDS + 32) * 4);
     if (const char *env = getenv("SABLE_B200_TAIL_BITS")) ctx->tail_bits = std::max(0, std::min(14, atoi(env)));
+    if (const char *env = getenv("SABLE_B200_COMM_TIMEOUT_S")) ctx->comm_timeout_s = std::max(1, atoi(env));
     if (const char *env = getenv("SABLE_B200_TAIL_POLLS")) ctx->tail_polls = (unsigned)std::max(1000, std::min((int)TAIL_POLL_LIMIT, atoi(env)));
     *out = ctx;
     return SC_OK;
@@ -844,7 +861,11 @@ static int sv_round0(sc_ctx *ctx, uint32_t *sums) {
         CU(launch_sum_ranks(ctx->d_gather, ctx->world, Z * D, ctx->d_sv, ctx->h_sv_dev, SV_FLAG, a.seq, ctx->stream));
         ctx->launches++;
     }
-    if (!wait_word(ctx, ctx->h_sv + SV_FLAG, a.seq)) { CU(cudaStreamSynchronize(ctx->stream)); return fail(ctx, SC_ECUDA, "the small-value pass did not finish"); }
+    if (!wait_word(ctx, ctx->h_sv + SV_FLAG, a.seq)) {
+        const bool aborted = sharded && !ctx->comm;
+        CU(cudaStreamSynchronize(ctx->stream));
+        return fail(ctx, aborted ? SC_ECOMM : SC_ECUDA, aborted ? "the exchange between the GPUs did not finish; the communicator was aborted" : "the small-value pass did not finish");
+    }
     if (ctx->timing) {
         CU(cudaStreamSynchronize(ctx->stream));
         sc_round_stat st; CU(cudaEventElapsedTime(&st.kernel_ms, ctx->ev[0], ctx->ev[1]));
@@ -1090,22 +1111,16 @@ extern "C" int sc_round(sc_ctx *ctx, uint32_t *sums) {
     }
     const auto tr2 = std::chrono::steady_clock::now();
     // wait for the sums: poll the word the kernel posts after them (a stream synchronize costs several
-    // microseconds more per round); the wait is bounded and falls back to the synchronize, which also
-    // reports any fault
+    // microseconds more per round); the wait is bounded
     {
-        volatile u32 *flag = ctx->h_out + MAX_PARTIAL_WORDS;
-        const auto t0 = std::chrono::steady_clock::now();
-        bool seen = false;
-        for (u64 spin = 0; !seen; spin++) {
-            if (*flag == a.seq) { seen = true; break; }
-            if ((spin & 0xfffff) == 0xfffff) {
-                cudaError_t q = cudaStreamQuery(ctx->stream);
-                if (q != cudaErrorNotReady) break;   // finished (the flag is about to show) or failed
-                if (std::chrono::steady_clock::now() - t0 > std::chrono::seconds(20)) break;
-            }
+        const bool had_comm = ctx->comm != nullptr;
+        const bool seen = wait_word(ctx, ctx->h_out + MAX_PARTIAL_WORDS, a.seq);
+        if (!seen && had_comm && !ctx->comm) {
+            cudaStreamSynchronize(ctx->stream);
+            return fail(ctx, SC_ECOMM, "round %d: the exchange between the GPUs did not finish in %d s; the communicator was aborted", j, ctx->comm_timeout_s);
         }
         if (!seen || ctx->timing) CU(cudaStreamSynchronize(ctx->stream));
-        std::atomic_thread_fence(std::memory_order_acquire);
+        if (!seen && *(volatile u32 *)(ctx->h_out + MAX_PARTIAL_WORDS) != a.seq) return fail(ctx, SC_ECUDA, "round %d: the kernel did not post its sums", j);
     }
     memcpy(sums, ctx->h_out, (size_t)W * 4);
     if (trace) {

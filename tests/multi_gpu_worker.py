@@ -27,6 +27,39 @@ CASES = [
 ]
 
 
+def lost_rank(prover, rank, out_file):
+    """Rank 1 leaves between two rounds; rank 0's next exchange must end with SC_ECOMM, not hang."""
+    d, n = 4, 20
+    rng = np.random.default_rng(3)
+    size = (1 << n) // 2
+    tables = [rng.integers(0, P, size=1 << n, dtype=np.uint32)[rank * size:(rank + 1) * size] for _ in range(2)]
+    degree, terms = sb.lower_statement("(* a b)", d, ["a", "b"])
+    prover.set_statement(d, 2, 2, terms)
+    for slot, t in enumerate(tables):
+        prover.upload_table(slot, t)
+    prover.begin(n, eq=rng.integers(0, P, size=(n, d), dtype=np.uint32))
+    tr = sb.Transcript("lost", d)
+    for _ in range(2):
+        tr.send(prover.round())
+        prover.challenge(tr.challenge())
+    if rank == 1:
+        json.dump({"left": True}, open(out_file, "w"))
+        os._exit(0)      # between rounds, nothing of this rank in flight
+    result = {"code": 0}
+    t0 = time.time()
+    try:
+        prover.round()
+    except sb.SumcheckError as e:
+        result = {"code": e.code, "seconds": time.time() - t0, "text": str(e)}
+    # the context is usable again, on its own GPU
+    small = [rng.integers(0, P, size=16, dtype=np.uint32) for _ in range(2)]
+    tr2 = sb.Transcript("after", d)
+    sb.prove(tr2, 4, "(* a b)", [("a", small[0]), ("b", small[1])], prover=prover)
+    result["after"] = len(tr2.messages)
+    json.dump(result, open(out_file, "w"))
+    prover.close()
+
+
 def main():
     rank, world, id_file, out_file = int(sys.argv[1]), int(sys.argv[2]), sys.argv[3], sys.argv[4]
     logw = world.bit_length() - 1
@@ -41,6 +74,8 @@ def main():
             raise SystemExit("no communicator id after 60 s")
         time.sleep(0.05)
     prover.comm_init(open(id_file, "rb").read(), rank, world)
+    if len(sys.argv) > 5 and sys.argv[5] == "lost-rank":
+        return lost_rank(prover, rank, out_file)
     results = []
     for d, n, statement, strides, consts, with_eq in CASES + [(4, logw, "(* t0 t1)", [1, 0], [], True)]:
         rng = np.random.default_rng(1000 + n)     # the same stream on every rank

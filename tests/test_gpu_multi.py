@@ -46,3 +46,28 @@ def test_sharded_proof_equals_the_oracle(world, gather_bits):
         # every rank ends with the same transcript and the same finals
         for r in range(2, world):
             assert res[r] == res[1]
+
+
+def test_a_rank_that_leaves_is_reported_not_waited_for():
+    # failure detection on the host: rank 1 exits between two rounds; rank 0's next exchange runs into the
+    # time limit, the communicator is aborted, the call returns SC_ECOMM and the context works again alone
+    if gpu_count() < 2:
+        pytest.skip("needs 2 GPUs")
+    with tempfile.TemporaryDirectory() as tmp:
+        env = dict(os.environ, NCCL_NVLS_ENABLE="0", SABLE_B200_COMM_TIMEOUT_S="3")
+        procs = [subprocess.Popen([sys.executable, os.path.join(ROOT, "tests", "multi_gpu_worker.py"), str(r), "2",
+                                   os.path.join(tmp, "id"), os.path.join(tmp, "out%d.json" % r), "lost-rank"], env=env,
+                                  stdout=subprocess.PIPE, stderr=subprocess.STDOUT, text=True) for r in range(2)]
+        outs = []
+        for p in procs:
+            try:
+                out, _ = p.communicate(timeout=120)
+            except subprocess.TimeoutExpired:
+                for q in procs:
+                    q.kill()
+                raise
+            outs.append(out)
+        assert procs[0].returncode == 0, outs[0][-3000:]
+        res = json.load(open(os.path.join(tmp, "out0.json")))
+        assert res["code"] == -6, res
+        assert res["seconds"] < 30 and res["after"] == 4, res
