@@ -152,6 +152,10 @@ struct sc_ctx {
     // communicator
     ncclComm_t comm = nullptr;
     int rank = 0, world = 1, logw = 0;
+    // mailboxes for the exchange of the round sums by peer stores (see RoundArgs::mail)
+    u32 *mail[8] = {nullptr, nullptr, nullptr, nullptr, nullptr, nullptr, nullptr, nullptr};
+    bool p2p = false;
+    u32 xseq = 0;
     int comm_timeout_s = 30;         // a round whose exchange has not finished after this long aborts the communicator
 };
 
@@ -210,6 +214,13 @@ static void comm_abort(sc_ctx *ctx) {
     if (!ctx->comm) return;
     g_nccl.CommAbort(ctx->comm);
     ctx->comm = nullptr;
+    cudaStreamSynchronize(ctx->stream);
+    for (int r = 0; r < 8; r++) {
+        if (!ctx->mail[r]) continue;
+        if (r == ctx->rank) cudaFree(ctx->mail[r]); else cudaIpcCloseMemHandle(ctx->mail[r]);
+        ctx->mail[r] = nullptr;
+    }
+    ctx->p2p = false;
     ctx->world = 1; ctx->rank = 0; ctx->logw = 0;
     ctx->begun = false;
 }
@@ -220,12 +231,12 @@ static bool wait_word(sc_ctx *ctx, const u32 *word, u32 want) {
     volatile const u32 *w = word;
     const auto t0 = std::chrono::steady_clock::now();
     for (u64 spin = 0;; spin++) {
-        if (*w == want) { std::atomic_thread_fence(std::memory_order_acquire); return true; }
+        if ((*w & ~EXCHANGE_FAILED) == want) { std::atomic_thread_fence(std::memory_order_acquire); return true; }
         if ((spin & 0xfffff) == 0xfffff) {
             if (cudaStreamQuery(ctx->stream) != cudaErrorNotReady) {
                 cudaStreamSynchronize(ctx->stream);
                 std::atomic_thread_fence(std::memory_order_acquire);
-                return *w == want;
+                return (*w & ~EXCHANGE_FAILED) == want;
             }
             if (std::chrono::steady_clock::now() - t0 > std::chrono::seconds(ctx->comm_timeout_s)) {
                 comm_abort(ctx);
@@ -293,6 +304,10 @@ extern "C" int sc_destroy(sc_ctx *ctx) {
     if (ctx->stream) cudaStreamSynchronize(ctx->stream);
     if (ctx->h_tail) cudaFreeHost(ctx->h_tail);
     if (ctx->h_sv) cudaFreeHost(ctx->h_sv);
+    for (int r = 0; r < 8; r++) {
+        if (!ctx->mail[r]) continue;
+        if (r == ctx->rank || ctx->world == 1) cudaFree(ctx->mail[r]); else cudaIpcCloseMemHandle(ctx->mail[r]);
+    }
     if (ctx->comm && g_nccl.CommDestroy) g_nccl.CommDestroy(ctx->comm);
     for (auto &t : ctx->tab) { cudaFree(t.t0); cudaFree(t.buf[0]); cudaFree(t.buf[1]); }
     for (auto p : ctx->d_gtab) cudaFree(p);
@@ -1075,6 +1090,16 @@ extern "C" int sc_round(sc_ctx *ctx, uint32_t *sums) {
     a.partials = ctx->d_partials; a.counter = ctx->d_counter;
     a.out_dev = ctx->d_out;
     a.out_host = local ? nullptr : ctx->h_out_dev;
+    bool all_base = !fold && ctx->base_groups > 0 && !getenv("SABLE_B200_GENERIC");
+    for (int k = 0; k < ctx->nt_used && all_base; k++) all_base = a.src_base[k];
+    // sharded rounds: the last block exchanges the sums with the other ranks itself (peer stores), unless the
+    // ranks could not open each other's memory or the round runs the base-table kernel: then NCCL carries them
+    const bool fused_exchange = local && ctx->p2p && !all_base;
+    if (fused_exchange) {
+        for (int r = 0; r < ctx->world; r++) a.mail[r] = ctx->mail[r];
+        a.world = ctx->world; a.rank = ctx->rank; a.xseq = ++ctx->xseq;
+        a.out_host = ctx->h_out_dev;
+    }
 
     const u64 chunk = (1ull << a.logL) > (u64)ROUND_THREADS ? (1ull << a.logL) : (u64)ROUND_THREADS;
     u64 chunks = (a.npairs + chunk - 1) / chunk;
@@ -1090,8 +1115,6 @@ extern "C" int sc_round(sc_ctx *ctx, uint32_t *sums) {
         CU(cudaEventRecord(e0, ctx->stream));
     }
     const auto tr1 = std::chrono::steady_clock::now();
-    bool all_base = !fold && ctx->base_groups > 0 && !getenv("SABLE_B200_GENERIC");
-    for (int k = 0; k < ctx->nt_used && all_base; k++) all_base = a.src_base[k];
     if (all_base) {
         a.ngroups = ctx->base_groups;
         a.product = ctx->shape == SHAPE_PRODUCT;
@@ -1102,7 +1125,7 @@ extern "C" int sc_round(sc_ctx *ctx, uint32_t *sums) {
     }
     ctx->launches++;
     if (ctx->timing) CU(cudaEventRecord(e1, ctx->stream));
-    if (local) {   // the whole job's sums: all-gather of the ranks' words, then their sum mod p
+    if (local && !fused_exchange) {   // the whole job's sums: all-gather of the ranks' words, then their sum mod p
         if (!ctx->d_gather) { if ((rc = dev_alloc(ctx, (void **)&ctx->d_gather, (u64)ctx->world * SV_MAX_WORDS * 4))) return rc; }
         ncclResult_t r = g_nccl.AllGather(ctx->d_out, ctx->d_gather, (size_t)W, NCCL_UINT32, ctx->comm, ctx->stream);
         if (r) return fail(ctx, SC_ECOMM, "ncclAllGather: %s", g_nccl.GetErrorString(r));
@@ -1119,8 +1142,13 @@ extern "C" int sc_round(sc_ctx *ctx, uint32_t *sums) {
             cudaStreamSynchronize(ctx->stream);
             return fail(ctx, SC_ECOMM, "round %d: the exchange between the GPUs did not finish in %d s; the communicator was aborted", j, ctx->comm_timeout_s);
         }
+        if (seen && (*(volatile u32 *)(ctx->h_out + MAX_PARTIAL_WORDS) & EXCHANGE_FAILED)) {
+            CU(cudaStreamSynchronize(ctx->stream));
+            comm_abort(ctx);
+            return fail(ctx, SC_ECOMM, "round %d: another rank's sums never arrived; the communicator was aborted", j);
+        }
         if (!seen || ctx->timing) CU(cudaStreamSynchronize(ctx->stream));
-        if (!seen && *(volatile u32 *)(ctx->h_out + MAX_PARTIAL_WORDS) != a.seq) return fail(ctx, SC_ECUDA, "round %d: the kernel did not post its sums", j);
+        if (!seen && (*(volatile u32 *)(ctx->h_out + MAX_PARTIAL_WORDS) & ~EXCHANGE_FAILED) != a.seq) return fail(ctx, SC_ECUDA, "round %d: the kernel did not post its sums", j);
     }
     memcpy(sums, ctx->h_out, (size_t)W * 4);
     if (trace) {
@@ -1228,6 +1256,34 @@ extern "C" int sc_comm_init(sc_ctx *ctx, const void *nccl_id128, int rank, int w
     ctx->logw = 0;
     while ((1 << ctx->logw) < world) ctx->logw++;
     ctx->begun = false;
+    // mailboxes: every rank makes one, the handles go round with an all-gather, every rank opens the others'
+    const char *env = getenv("SABLE_B200_P2P");
+    if (world > 1 && world <= 8 && !(env && env[0] == '0')) {
+        const size_t bytes = (size_t)2 * world * MAIL_WORDS * 4;
+        u32 *own = nullptr, *d_handles = nullptr;
+        cudaIpcMemHandle_t mine, all[8];
+        bool ok = cudaMalloc(&own, bytes) == cudaSuccess && cudaMemset(own, 0, bytes) == cudaSuccess &&
+                  cudaIpcGetMemHandle(&mine, own) == cudaSuccess &&
+                  cudaMalloc(&d_handles, (size_t)(world + 1) * sizeof mine) == cudaSuccess &&
+                  cudaMemcpy(d_handles + (size_t)world * (sizeof mine / 4), &mine, sizeof mine, cudaMemcpyHostToDevice) == cudaSuccess;
+        if (ok) ok = g_nccl.AllGather(d_handles + (size_t)world * (sizeof mine / 4), d_handles, sizeof mine / 4, NCCL_UINT32, ctx->comm, ctx->stream) == 0 &&
+                     cudaStreamSynchronize(ctx->stream) == cudaSuccess &&
+                     cudaMemcpy(all, d_handles, (size_t)world * sizeof mine, cudaMemcpyDeviceToHost) == cudaSuccess;
+        for (int p = 0; p < world && ok; p++) {
+            if (p == rank) { ctx->mail[p] = own; continue; }
+            void *ptr = nullptr;
+            ok = cudaIpcOpenMemHandle(&ptr, all[p], cudaIpcMemLazyEnablePeerAccess) == cudaSuccess;
+            ctx->mail[p] = (u32 *)ptr;
+        }
+        if (d_handles) cudaFree(d_handles);
+        if (!ok) {   // no peer access: the sums go through NCCL instead
+            cudaGetLastError();
+            for (int p = 0; p < world; p++) { if (ctx->mail[p] && p != rank) cudaIpcCloseMemHandle(ctx->mail[p]); ctx->mail[p] = nullptr; }
+            if (own) cudaFree(own);
+        }
+        ctx->p2p = ok;
+        ctx->xseq = 0;
+    }
     return SC_OK;
 }
 

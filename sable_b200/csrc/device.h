@@ -69,11 +69,21 @@ struct RoundArgs {
     // group of terms, weighted by the eq weights, and multiplies each group's sum by its
     // coefficient at the end.  Group 0 holds the terms with base-field coefficients (their sum is a
     // base value, gcoef = 1); a term with an extension coefficient is a group of its own.
+    // Several GPUs: the last block hands this rank's sums to every rank and adds up what the others hand it,
+    // through mailboxes in device memory that the ranks opened to each other (peer stores over NVLink): rank r's
+    // mailbox holds, for each parity of the exchange number and each sender, MAIL_WORDS words: the sums, then at
+    // word MAIL_FLAG the exchange number, written last.  xseq = 0: no exchange (one GPU, or the caller exchanges).
+    u32 *mail[8];         // the ranks' mailboxes, mail[rank] this rank's own
+    int world, rank;
+    u32 xseq;
     u32 bind[4][8];       // FOLD = 2: eq(rho0 rho1, b), b < 4, Montgomery form: entry y of the bound table is sum_b bind[b] T[4y + b]
     int ngroups;
     int product;          // 1: the statement is the product of the tables (no term table needed)
     u32 gcoef[2][8];      // Montgomery form
 };
+constexpr int MAIL_WORDS = 64, MAIL_FLAG = 32;
+constexpr unsigned MAIL_POLL_LIMIT = 20000000u;   // polls (with a short sleep each) a rank waits for the others' sums
+constexpr u32 EXCHANGE_FAILED = 0x80000000u;      // or-ed into the posted launch number when a rank's sums never came
 constexpr int MAX_GROUPS = 2;
 constexpr int BASE_MAX_TERMS = 4;      // the base-table kernel keeps its term descriptors in registers:
 constexpr int BASE_MAX_FACTORS = 4;    // statements beyond these run the general kernel

@@ -426,16 +426,46 @@ __global__ void __launch_bounds__(ROUND_THREADS, NT > 4 ? 1 : (D == 8 ? SC_MINBL
                 s = emul<D>(s, pf);
             }
 #pragma unroll
-            for (int c = 0; c < D; c++) {
-                a.out_dev[tid * D + c] = s.v[c];
-                if (a.out_host) a.out_host[tid * D + c] = s.v[c];
-            }
-            __threadfence_system();
+            for (int c = 0; c < D; c++) red[0][tid * D + c] = s.v[c];
         }
         __syncthreads();
-        if (tid == 0 && a.out_host) {   // the host polls this word: the sums above are visible before it
+        u32 posted = a.seq;
+        if (a.xseq) {
+            // hand the sums to every rank (this one included), the exchange number after them
+            const size_t box = ((size_t)(a.xseq & 1) * a.world + a.rank) * MAIL_WORDS;
+            if (tid < W)
+                for (int r = 0; r < a.world; r++) a.mail[r][box + tid] = red[0][tid];
             __threadfence_system();
-            *reinterpret_cast<volatile u32 *>(a.out_host + MAX_PARTIAL_WORDS) = a.seq;
+            __syncthreads();
+            if (tid < a.world) *reinterpret_cast<volatile u32 *>(a.mail[tid] + box + MAIL_FLAG) = a.xseq;
+            // wait for every rank's number in this rank's own mailbox: bounded
+            __shared__ int missing;
+            if (tid == 0) missing = 0;
+            __syncthreads();
+            if (tid < a.world) {
+                const volatile u32 *flag = a.mail[a.rank] + ((size_t)(a.xseq & 1) * a.world + tid) * MAIL_WORDS + MAIL_FLAG;
+                unsigned poll = 0;
+                while (*flag != a.xseq && ++poll < MAIL_POLL_LIMIT) __nanosleep(64);
+                if (*flag != a.xseq) atomicAdd(&missing, 1);
+            }
+            __syncthreads();
+            if (missing) posted |= EXCHANGE_FAILED;
+            else if (tid < W) {
+                u32 v = 0;
+                for (int r = 0; r < a.world; r++)
+                    v = fadd(v, *reinterpret_cast<const volatile u32 *>(a.mail[a.rank] + ((size_t)(a.xseq & 1) * a.world + r) * MAIL_WORDS + tid));
+                red[0][tid] = v;
+            }
+            __syncthreads();
+        }
+        if (tid < W) {
+            a.out_dev[tid] = red[0][tid];
+            if (a.out_host) a.out_host[tid] = red[0][tid];
+        }
+        __syncthreads();
+        if (tid == 0 && a.out_host) {   // the host polls this word: the sums above are visible before it (the fence is cumulative)
+            __threadfence_system();
+            *reinterpret_cast<volatile u32 *>(a.out_host + MAX_PARTIAL_WORDS) = posted;
         }
     }
 }

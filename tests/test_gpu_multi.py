@@ -27,6 +27,7 @@ def test_sharded_proof_equals_the_oracle(world, gather_bits):
         env = dict(os.environ, NCCL_NVLS_ENABLE="0")
         if gather_bits is not None:
             env["SABLE_B200_GATHER_BITS"] = str(gather_bits)
+            env["SABLE_B200_P2P"] = "0"       # these runs carry the sums with NCCL, the others with peer stores
         procs = [subprocess.Popen([sys.executable, os.path.join(ROOT, "tests", "multi_gpu_worker.py"), str(r), str(world),
                                    os.path.join(tmp, "id"), os.path.join(tmp, "out%d.json" % r)], env=env,
                                   stdout=subprocess.PIPE, stderr=subprocess.STDOUT, text=True) for r in range(world)]
