@@ -42,7 +42,7 @@ extern "C" {
 #define SC_MAX_TABLES 8
 #define SC_MAX_TERMS 16
 #define SC_MAX_FACTORS 8
-#define SC_MAX_POINTS 4
+#define SC_MAX_POINTS 8
 
 typedef struct sc_ctx sc_ctx;
 
@@ -67,7 +67,9 @@ const char *sc_last_error(const sc_ctx *ctx);
    (ROUND-KERNEL-CODE, src/sumcheck.lisp:190-258, and STATEMENT-FUNCTION, :108-110).
      D          extension degree, 4 or 8 (TRANSCRIPT-DEGREE)
      points     max(degree, 1): the round message has POINTS rows, X = 0, 2, .., POINTS (:186-188)
-     ntables    number of table slots; tables that occur in no term are still folded (:528, :562)
+     ntables    number of table slots (at most SC_MAX_TABLES); tables that occur in no term are still
+                folded (:528, :562).  A statement may multiply up to eight different tables at degree
+                <= 4, up to four at degree 5 to 8; otherwise SC_EUNSUPPORTED
      coeffs     nterms * D canonical words
      term_ptr   nterms + 1 offsets into term_tables (CSR); term t multiplies tables
                 term_tables[term_ptr[t] .. term_ptr[t+1]), repeated indices for powers */
@@ -149,8 +151,8 @@ int sc_comm_info(const sc_ctx *ctx, int *rank, int *world);
    (a cudaStream_t, or NULL).
    Scratch: the per-block partial sums and a block counter live in one fixed array in the
    library's device image (256.25 KiB, held by every GPU that loads the library until exit),
-   one row per 65 536 pairs and at most 2 048 rows, so ENTRIES may be at most 2^28; more is
-   refused with SC_EINVAL and a message naming the limit.  The first call on a device looks up
+   one row of 32 words per 65 536 pairs and at most 2 048 rows, so ENTRIES may be at most 2^28
+   and POINTS * D at most 32; more is refused with an error code and a message naming the limit.  The first call on a device looks up
    the array's device address (cudaGetSymbolAddress), so make that first call before any stream
    capture begins.  All calls share the array: the counter is cleared at the start of each call,
    the rows are overwritten, and two calls that run on the GPU at the same time race -- order

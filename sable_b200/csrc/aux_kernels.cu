@@ -11,10 +11,18 @@ cudaError_t launch_round_d8(int shape, int points, int nt, int fold, const Round
 cudaError_t launch_round_d4w(int points, int nt, int fold, const RoundArgs &args, int grid, size_t smem, cudaStream_t stream);
 cudaError_t launch_round_d8w(int points, int nt, int fold, const RoundArgs &args, int grid, size_t smem, cudaStream_t stream);
 
+cudaError_t launch_round_d4h(int points, int nt, int fold, const RoundArgs &args, int grid, size_t smem, cudaStream_t stream);
+cudaError_t launch_round_d8h(int points, int nt, int fold, const RoundArgs &args, int grid, size_t smem, cudaStream_t stream);
+
 bool round_supported(int D, int points, int nt_used) {
-    return (D == 4 || D == 8) && points >= 1 && points <= SC_MAX_POINTS && nt_used >= 1 && nt_used <= 8;
+    if (!(D == 4 || D == 8) || points < 1 || points > SC_MAX_POINTS || nt_used < 1 || nt_used > 8) return false;
+    return points <= FAST_POINTS || nt_used <= 4;   // degree above four: at most four tables in the statement
 }
 cudaError_t launch_round(int D, int shape, int points, int nt_used, int fold, const RoundArgs &args, int grid, size_t smem, cudaStream_t stream) {
+    if (points > FAST_POINTS) {
+        if (fold == 2 || nt_used > 4) return cudaErrorInvalidValue;
+        return D == 4 ? launch_round_d4h(points, nt_used, fold, args, grid, smem, stream) : launch_round_d8h(points, nt_used, fold, args, grid, smem, stream);
+    }
     if (nt_used > 4) {   // kernels exist for six and eight tables
         const int nt = nt_used <= 6 ? 6 : 8;
         if (fold == 2) return cudaErrorInvalidValue;

@@ -474,6 +474,8 @@ extern "C" int sc_set_statement(sc_ctx *ctx, int D, int points, int ntables, int
     for (int k = 0; k < nfirst; k++) { ctx->order[npos] = first[k]; pos_of[first[k]] = npos++; placed[first[k]] = true; }
     for (int s = 0; s < ntables; s++) if (used[s] && !placed[s]) { ctx->order[npos] = s; pos_of[s] = npos++; placed[s] = true; }
     for (int s = 0; s < ntables; s++) if (!placed[s]) { ctx->order[npos] = s; pos_of[s] = npos++; }
+    if (!round_supported(D, points, nt_used > 0 ? nt_used : 1))
+        return fail(ctx, SC_EUNSUPPORTED, "no kernel for degree %d over %d tables (degree above 4: at most 4 tables)", points, nt_used);
     if (getenv("SABLE_B200_GENERIC")) shape = SHAPE_GENERIC;   // run every statement through the term-table kernel (for cross-checks)
     ctx->shape = shape;
     ctx->D = D; ctx->points = points; ctx->ntables = ntables; ctx->nt_used = nt_used > 0 ? nt_used : 1;
@@ -531,7 +533,7 @@ extern "C" int sc_set_statement(sc_ctx *ctx, int D, int points, int ntables, int
             else if (tm.ckind == CK_EXT) ok = false;          // an extension constant term
             else base_terms++;
         }
-        if (ext_terms > 1 || nterms == 0 || nterms > BASE_MAX_TERMS || nt_used > 4) ok = false;
+        if (ext_terms > 1 || nterms == 0 || nterms > BASE_MAX_TERMS || nt_used > 4 || points > FAST_POINTS) ok = false;
         for (int t = 0; t < nterms; t++) if (ctx->st.terms[t].nf > BASE_MAX_FACTORS) ok = false;
         ctx->base_groups = ok ? (base_terms > 0) + ext_terms : 0;
         memset(ctx->gcoef, 0, sizeof ctx->gcoef);
@@ -933,7 +935,7 @@ static int sv_round1(sc_ctx *ctx, uint32_t *sums) {
 // The last rounds run in one resident launch when the tables are small, there is one block of
 // weights, and nobody asked for per-round timing.
 static bool tail_wanted(const sc_ctx *ctx) {
-    if (ctx->tail_bits <= 0 || ctx->K != 1 || ctx->timing || ctx->ntables < 1 || ctx->nt_used > 4) return false;
+    if (ctx->tail_bits <= 0 || ctx->K != 1 || ctx->timing || ctx->ntables < 1 || ctx->nt_used > 4 || ctx->points > FAST_POINTS) return false;
     if (ctx->n - ctx->j > TAIL_MAX_ROUNDS) return false;
     return ctx->tab[ctx->order[0]].cur_entries <= (1ull << ctx->tail_bits);
 }
@@ -1301,7 +1303,8 @@ namespace {
 constexpr int STATIC_ROWS = 2048;                 // blocks a call may launch: one partial row each
 constexpr u64 STATIC_PAIRS_PER_ROW = 65536;       // pairs a block sums
 constexpr int STATIC_HEAD_WORDS = 64;             // the counter, in 256 bytes of its own
-constexpr int STATIC_WORDS = STATIC_HEAD_WORDS + STATIC_ROWS * MAX_PARTIAL_WORDS;   // 64 + 2048 * 32 words = 256.25 KiB
+constexpr int STATIC_ROW_WORDS = 32;              // points * D words per row: degree <= 4 at D = 8, <= 8 at D = 4
+constexpr int STATIC_WORDS = STATIC_HEAD_WORDS + STATIC_ROWS * STATIC_ROW_WORDS;   // 64 + 2048 * 32 words = 256.25 KiB
 static __device__ __align__(256) u32 g_static_scratch[STATIC_WORDS];
 constexpr int STATIC_MAX_DEVICES = 64;
 u32 *g_static_ptr[STATIC_MAX_DEVICES];            // the array's device address, per device ordinal (0 = not asked yet)
@@ -1335,6 +1338,7 @@ static int round_sums_static(sc_ctx *ctx, int D, int points, int ntables, const 
         return fail(ctx, SC_EINVAL, "%llu entries need %llu rows of scratch: the static array holds %d (at most %llu entries per table)",
                     (unsigned long long)entries, (unsigned long long)rows, STATIC_ROWS,
                     (unsigned long long)(2 * STATIC_PAIRS_PER_ROW * STATIC_ROWS));
+    if ((u64)points * (u64)D > (u64)STATIC_ROW_WORDS) return fail(ctx, SC_EUNSUPPORTED, "points * D = %d: the static rows hold %d words", points * D, STATIC_ROW_WORDS);
     int rc = sc_set_statement(ctx, D, points, ntables, nterms, coeffs, term_ptr, term_tables);
     if (rc) return rc;
     if (!round_supported(D, ctx->points, ctx->nt_used)) return fail(ctx, SC_EUNSUPPORTED, "no kernel for D=%d points=%d tables=%d", D, points, ctx->nt_used);

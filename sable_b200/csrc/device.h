@@ -81,13 +81,14 @@ struct RoundArgs {
     int product;          // 1: the statement is the product of the tables (no term table needed)
     u32 gcoef[2][8];      // Montgomery form
 };
-constexpr int MAIL_WORDS = 64, MAIL_FLAG = 32;
+constexpr int MAIL_WORDS = 128, MAIL_FLAG = 64;
 constexpr unsigned MAIL_POLL_LIMIT = 20000000u;   // polls (with a short sleep each) a rank waits for the others' sums
 constexpr u32 EXCHANGE_FAILED = 0x80000000u;      // or-ed into the posted launch number when a rank's sums never came
+constexpr int FAST_POINTS = 4;         // the built-in statements, the base-table, small-value and resident kernels: degree <= 4
 constexpr int MAX_GROUPS = 2;
 constexpr int BASE_MAX_TERMS = 4;      // the base-table kernel keeps its term descriptors in registers:
 constexpr int BASE_MAX_FACTORS = 4;    // statements beyond these run the general kernel
-constexpr int PARTIAL_ROW_WORDS = MAX_GROUPS * MAX_PARTIAL_WORDS;   // words per block in the partials buffer
+constexpr int PARTIAL_ROW_WORDS = MAX_PARTIAL_WORDS > MAX_GROUPS * FAST_POINTS * 8 ? MAX_PARTIAL_WORDS : MAX_GROUPS * FAST_POINTS * 8;   // words per block in the partials buffer
 
 // Launchers (defined next to their kernels).  Each returns the CUDA error of the launch.
 // fold: 0 the tables as they are, 1 folded by r on the way in, 2 base tables bound to two challenges at once (args.bind)

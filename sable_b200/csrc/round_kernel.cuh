@@ -383,8 +383,9 @@ __global__ void __launch_bounds__(ROUND_THREADS, NT > 4 ? 1 : (D == 8 ? SC_MINBL
             if (lane == 0) red[warp][x * D + c] = v;
         }
     __syncthreads();
-    constexpr int W = PTS * D;                 // <= 32 words
+    constexpr int W = PTS * D;                 // <= 64 words
     constexpr int ROWS = ROUND_THREADS / 32;
+    constexpr int KW = W > 32 ? 64 : 32;       // threads across a row of partial sums
     if (gridDim.x > 1) {
         if (tid < W) {
             u32 v = red[0][tid];
@@ -399,12 +400,14 @@ __global__ void __launch_bounds__(ROUND_THREADS, NT > 4 ? 1 : (D == 8 ? SC_MINBL
         if (!is_last) return;
         __threadfence();
         // the last block: add the partials (a single block has its rows in shared memory already)
-        const int k = tid & 31, row = tid >> 5;
+        const int k = tid % KW, row = tid / KW;
+        constexpr int NROW = ROUND_THREADS / KW;
         u32 v = 0;
         if (k < W)
-            for (unsigned g = row; g < gridDim.x; g += ROWS) v = fadd(v, __ldcg(a.partials + (size_t)g * W + k));
+            for (unsigned g = row; g < gridDim.x; g += NROW) v = fadd(v, __ldcg(a.partials + (size_t)g * W + k));
         __syncthreads();
         if (k < W) red[row][k] = v;
+        if (k < W && NROW < ROWS) for (int w = NROW + row; w < ROWS; w += NROW) red[w][k] = 0;
         __syncthreads();
         if (tid == 0) *a.counter = 0;
     }
@@ -541,6 +544,18 @@ static cudaError_t launch_round_wide(int points, int nt, int fold, const RoundAr
     case 2: return launch_round_wide_p<D, 2>(nt, fold, args, grid, smem, stream);
     case 3: return launch_round_wide_p<D, 3>(nt, fold, args, grid, smem, stream);
     case 4: return launch_round_wide_p<D, 4>(nt, fold, args, grid, smem, stream);
+    default: return cudaErrorInvalidValue;
+    }
+}
+
+// Degrees five to eight: the term-table kernel with more points.
+template <int D>
+static cudaError_t launch_round_high(int points, int nt, int fold, const RoundArgs &args, int grid, size_t smem, cudaStream_t stream) {
+    switch (points) {
+    case 5: return launch_round_dp<D, 5>(nt, fold, args, grid, smem, stream);
+    case 6: return launch_round_dp<D, 6>(nt, fold, args, grid, smem, stream);
+    case 7: return launch_round_dp<D, 7>(nt, fold, args, grid, smem, stream);
+    case 8: return launch_round_dp<D, 8>(nt, fold, args, grid, smem, stream);
     default: return cudaErrorInvalidValue;
     }
 }

@@ -45,11 +45,45 @@ __global__ void __launch_bounds__(ROUND_THREADS) tail_kernel(const __grid_consta
 #pragma unroll
         for (int x = 0; x < PTS; x++) total[x] = ezero<D>();
         for (u64 i = tid; i < rd.npairs; i += ROUND_THREADS) {
-            Ext<D> val[NT], slope[NT];
-            for (int t = 0; t < a.ntables; t++) {
+            // the weight and every table's entries are asked for first: a round here is a chain of latencies
+            Ext<D> hw;
+            if (rd.use_high) hw = *reinterpret_cast<const Ext<D> *>(a.weights + rd.high_word + i * D);
+            Ext<D> e[NT][4];
+#pragma unroll
+            for (int t = 0; t < NT; t++) {
                 const u32 *src = k == 0 ? a.src[t] : a.buf[out ^ 1][t];
+                if (k == 0 && a.src_base[t]) {
+                    const uint4 w = *reinterpret_cast<const uint4 *>(src + 4 * i);
+                    e[t][0].v[0] = w.x; e[t][1].v[0] = w.y; e[t][2].v[0] = w.z; e[t][3].v[0] = w.w;
+                } else {
+#pragma unroll
+                    for (int q = 0; q < 4; q++) e[t][q] = load_ext<D>(src + (4 * i + q) * D);
+                }
+            }
+            Ext<D> val[NT], slope[NT];
+#pragma unroll
+            for (int t = 0; t < NT; t++) {
                 Ext<D> lo, hi;
                 if (k == 0 && a.src_base[t]) {   // base entries: D base products (FOLD-FLAT-TABLE, src/sumcheck.lisp:95-98)
+                    const u32 s0 = fsub(e[t][1].v[0], e[t][0].v[0]), s1 = fsub(e[t][3].v[0], e[t][2].v[0]);
+#pragma unroll
+                    for (int c = 0; c < D; c++) { lo.v[c] = mmul(rm.v[c], s0); hi.v[c] = mmul(rm.v[c], s1); }
+                    lo.v[0] = fadd(lo.v[0], e[t][0].v[0]);
+                    hi.v[0] = fadd(hi.v[0], e[t][2].v[0]);
+                } else {
+                    lo = eadd<D>(e[t][0], emul<D>(esub<D>(e[t][1], e[t][0]), rm));
+                    hi = eadd<D>(e[t][2], emul<D>(esub<D>(e[t][3], e[t][2]), rm));
+                }
+                u32 *dst = a.buf[out][t];
+                store_ext<D>(dst + (2 * i) * D, lo);
+                store_ext<D>(dst + (2 * i + 1) * D, hi);
+                val[t] = lo;
+                slope[t] = esub<D>(hi, lo);
+            }
+            for (int t = NT; t < a.ntables; t++) {   // tables outside the statement are only folded
+                const u32 *src = k == 0 ? a.src[t] : a.buf[out ^ 1][t];
+                Ext<D> lo, hi;
+                if (k == 0 && a.src_base[t]) {
                     const uint4 w = *reinterpret_cast<const uint4 *>(src + 4 * i);
                     const u32 s0 = fsub(w.y, w.x), s1 = fsub(w.w, w.z);
 #pragma unroll
@@ -57,17 +91,13 @@ __global__ void __launch_bounds__(ROUND_THREADS) tail_kernel(const __grid_consta
                     lo.v[0] = fadd(lo.v[0], w.x);
                     hi.v[0] = fadd(hi.v[0], w.z);
                 } else {
-                    const u32 *e = src + 4 * i * D;
-                    const Ext<D> e0 = load_ext<D>(e), e1 = load_ext<D>(e + D), e2 = load_ext<D>(e + 2 * D), e3 = load_ext<D>(e + 3 * D);
+                    const u32 *ee = src + 4 * i * D;
+                    const Ext<D> e0 = load_ext<D>(ee), e1 = load_ext<D>(ee + D), e2 = load_ext<D>(ee + 2 * D), e3 = load_ext<D>(ee + 3 * D);
                     lo = eadd<D>(e0, emul<D>(esub<D>(e1, e0), rm));
                     hi = eadd<D>(e2, emul<D>(esub<D>(e3, e2), rm));
                 }
-                u32 *dst = a.buf[out][t];
-                store_ext<D>(dst + (2 * i) * D, lo);
-                store_ext<D>(dst + (2 * i + 1) * D, hi);
-#pragma unroll
-                for (int u = 0; u < NT; u++)
-                    if (u == t) { val[u] = lo; slope[u] = esub<D>(hi, lo); }
+                store_ext<D>(a.buf[out][t] + (2 * i) * D, lo);
+                store_ext<D>(a.buf[out][t] + (2 * i + 1) * D, hi);
             }
             Ext<D> sum[PTS];
 #pragma unroll
@@ -85,7 +115,6 @@ __global__ void __launch_bounds__(ROUND_THREADS) tail_kernel(const __grid_consta
                 else sum[x] = eval_statement<D, NT, false>(a.st, val, 0u, &unused);
             }
             if (rd.use_high) {
-                const Ext<D> hw = *reinterpret_cast<const Ext<D> *>(a.weights + rd.high_word + i * D);
                 const ExtM<D> hm = eprep<D>(hw);
 #pragma unroll
                 for (int x = 0; x < PTS; x++) total[x] = eadd<D>(total[x], emul<D>(sum[x], hm));

@@ -400,3 +400,18 @@ def test_statements_over_more_than_four_tables(prover, nt):
         tables.append(("unused", rand_ext(rng, d, 1 << n)))
         got, want, ta, tb = both(prover, d, n, statement, tables[:8], eq=rand_ext(rng, d, n))
         assert_same(got, want, ta, tb)
+
+
+@pytest.mark.parametrize("d", [4, 8])
+def test_degrees_five_to_eight(prover, d):
+    rng = np.random.default_rng(80 + d)
+    cases = [("(expt t0 5)", 1), ("(* t0 t1 t2 t3 (expt t0 2))", 4), ("(+ (expt t0 8) (* 3 t1) (* alpha t1 t0))", 2),
+             ("(- (* (expt t0 3) (expt t1 4)) (* 2 t2))", 3)]
+    for statement, nt in cases:
+        for n, base in ((1, False), (7, True), (12, False)):
+            tables = [("t%d" % t, rng.integers(0, P, size=1 << n, dtype=np.uint32) if (base and t % 2 == 0) else rand_ext(rng, d, 1 << n))
+                      for t in range(nt)]
+            constants = [("alpha", rand_ext(rng, d).tolist())] if "alpha" in statement else []
+            got, want, ta, tb = both(prover, d, n, statement, tables, eq=rand_ext(rng, d, n), constants=constants)
+            assert_same(got, want, ta, tb)
+            assert ta.messages[0].shape[0] >= 5
