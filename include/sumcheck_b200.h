@@ -87,7 +87,9 @@ int sc_generate_table(sc_ctx *ctx, int slot, uint64_t seed, int table_id, uint64
                       int stride, int nonzero);
 
 /* The current (folded) contents of table SLOT as canonical extension elements, for tests.
-   Writes min(entries, CAP) entries of D words; *ENTRIES gets the table's size. */
+   Writes min(entries, CAP) entries of D words; *ENTRIES gets the table's size.  SC_ESTATE while the
+   folded table does not exist in memory: during the small-value rounds (rounds 1 and 2 of a product
+   of base tables) and once the resident last-rounds kernel runs. */
 int sc_download_table(sc_ctx *ctx, int slot, uint32_t *host, uint64_t cap, uint64_t *entries);
 
 /* Start a proof of N rounds over the uploaded tables (each K * 2^N entries, K = 1 when

@@ -635,6 +635,8 @@ extern "C" int sc_download_table(sc_ctx *ctx, int slot, uint32_t *host, uint64_t
     TableState &t = ctx->tab[slot];
     if (!t.t0) return fail(ctx, SC_ESTATE, "table %d was never uploaded", slot);
     if (ctx->tail_active) return fail(ctx, SC_ESTATE, "the last rounds are running on the device: the folded tables are not available");
+    if (ctx->begun && ctx->sv_ok && (ctx->j == 1 || ctx->j == 2))
+        return fail(ctx, SC_ESTATE, "the first two rounds ran from one pass over the tables: nothing is folded before round 2");
     cudaSetDevice(ctx->device);
     if (!ctx->begun) { t.cur = t.t0; t.cur_base = t.stride == 1; t.cur_entries = t.entries; t.cur_buf = -1; }
     if (entries) *entries = t.cur_entries;

@@ -325,6 +325,25 @@ def test_small_value_rounds_match_folding(prover, statement, names, with_eq, mon
     assert again == got and tc.proof() == ta.proof()
 
 
+def test_download_gives_the_table_back_and_refuses_in_the_small_value_rounds(prover):
+    d, n = 4, 22
+    rng = np.random.default_rng(77)
+    a = rng.integers(0, P, size=1 << n, dtype=np.uint32)
+    b = rng.integers(0, P, size=1 << n, dtype=np.uint32)
+    degree, terms = sb.lower_statement("(* a b)", d, ["a", "b"])
+    prover.set_statement(d, 2, 2, terms)
+    prover.upload_table(0, a)
+    prover.upload_table(1, b)
+    back = prover.download_table(1, d, cap=1000)
+    assert back.shape == (1000, d) and (back[:, 0] == b[:1000]).all() and not back[:, 1:].any()
+    prover.begin(n, eq=rand_ext(rng, d, n))
+    prover.round()
+    prover.challenge([5, 6, 7, 8])
+    with pytest.raises(sb.SumcheckError) as e:   # rounds 0 and 1 came from one pass: no folded table exists yet
+        prover.download_table(0, d, cap=16)
+    assert e.value.code == -5
+
+
 def test_slow_host_falls_back_to_a_launch_per_round(monkeypatch):
     # the resident kernel of the last rounds waits a bounded time for each challenge; when the host is
     # slower than that (here: a short limit and a pause) it returns and the proof goes on, launch by launch
