@@ -747,9 +747,22 @@ int orc_hypercube_sum(int D, int n, const char *statement_text, int nt, const ch
 
 /* verify (:147-163) with next-claim (:137-145).  messages: n arrays (points, D), row-major, one
    after the other.  Returns 0 and writes the challenges (n*D) and the reduced claim (D). */
+static int verify_on(orc_tr *tr, int D, int n, int degree, const u32 *claim_in, const u32 *eq,
+                     int blocks, const char *label, const u32 *messages, u32 *challenges, u32 *reduced);
 int orc_verify(const u8 *tr_label, int tr_label_len, int D, int n, int degree, const u32 *claim_in, const u32 *eq,
                int blocks, const char *label, const u32 *messages, u32 *challenges, u32 *reduced) {
     orc_tr *tr = orc_tr_new(tr_label, tr_label_len, D);
+    int rc = verify_on(tr, D, n, degree, claim_in, eq, blocks, label, messages, challenges, reduced);
+    orc_tr_free(tr);
+    return rc;
+}
+/* the same on a transcript that already holds earlier messages (a caller's protocol around the sumcheck) */
+int orc_verify_tr(orc_tr *tr, int n, int degree, const u32 *claim_in, const u32 *eq, int blocks, const char *label,
+                  const u32 *messages, u32 *challenges, u32 *reduced) {
+    return verify_on(tr, tr->D, n, degree, claim_in, eq, blocks, label, messages, challenges, reduced);
+}
+static int verify_on(orc_tr *tr, int D, int n, int degree, const u32 *claim_in, const u32 *eq,
+                     int blocks, const char *label, const u32 *messages, u32 *challenges, u32 *reduced) {
     int points = degree > 1 ? degree : 1;
     u8 hdr[300]; size_t hl = make_header(label, n, degree, (u32)blocks, hdr);
     orc_tr_absorb(tr, hdr, hl);
@@ -770,7 +783,6 @@ int orc_verify(const u8 *tr_label, int tr_label_len, int D, int n, int degree, c
         ecopy(D, r, challenges + D * j);
     }
     ecopy(D, claim, reduced);
-    orc_tr_free(tr);
     return 0;
 }
 
@@ -785,6 +797,30 @@ int orc_check_final(int D, const char *statement_text, int nt, const char *const
     int ok = memcmp(f, reduced, 4 * (size_t)D) == 0;
     free(vals); stmt_free(&st);
     return ok;
+}
+
+/* evaluate (src/forms.lisp:214-217): the statement's value at the given tables' and constants' values */
+int orc_evaluate(int D, const char *statement_text, int nt, const char *const *tnames, const u32 *tvals,
+                 int nc, const char *const *cnames, const u32 *cvals, u32 *out) {
+    statement st; int rc = stmt_parse(&st, statement_text, nt, tnames, nc, cnames);
+    if (rc) { stmt_free(&st); return rc; }
+    const u32 **vals = malloc(sizeof(u32 *) * (size_t)(st.syms.n + 1));
+    for (int v = 0; v < st.syms.n; v++) { int s = st.slot_of_var[v]; vals[v] = s < nt ? tvals + D * s : cvals + D * (s - nt); }
+    eval_ext(st.root, D, vals, out);
+    free(vals); stmt_free(&st);
+    return 0;
+}
+
+/* One layer of a fraction tree (FRACTION-TREES, src/gkr.lisp:149-188): p/q = p0/q0 + p1/q1 entry
+   by entry, so p = p0 q1 + p1 q0 and q = q0 q1.  COUNT entries of D words in each array. */
+void orc_fraction_layer(int D, u64 count, const u32 *p0, const u32 *p1, const u32 *q0, const u32 *q1, u32 *p, u32 *q) {
+#pragma omp parallel for schedule(static) if (count > 4096)
+    for (u64 i = 0; i < count; i++) {
+        u32 a[MAXD], b[MAXD];
+        emul(D, p0 + D * i, q1 + D * i, a); emul(D, p1 + D * i, q0 + D * i, b);
+        eadd(D, a, b, p + D * i);
+        emul(D, q0 + D * i, q1 + D * i, a); ecopy(D, a, q + D * i);
+    }
 }
 
 /* The seeded table generator shared with the device (splitmix64 of seed, table, coordinate and
