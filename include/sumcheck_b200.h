@@ -86,6 +86,14 @@ int sc_upload_table(sc_ctx *ctx, int slot, const uint32_t *host, uint64_t entrie
 int sc_generate_table(sc_ctx *ctx, int slot, uint64_t seed, int table_id, uint64_t first, uint64_t entries,
                       int stride, int nonzero);
 
+/* Table SLOT is the caller's own device memory: ENTRIES entries of STRIDE words, canonical (every
+   word below p; nothing reduces them), starting on a 16-byte boundary, on the context's device.
+   Nothing is copied: the first rounds read the table where it lies, and it must stay unchanged
+   and allocated until another table takes the slot (the folded tables are the context's own).
+   The context never writes or frees it.  For callers whose tables are made on the device (the layers of a fraction tree,
+   sc_gkr_prove_upper).  No reference counterpart: Lisp tables live in host memory. */
+int sc_borrow_table(sc_ctx *ctx, int slot, const uint32_t *table_dev, uint64_t entries, int stride);
+
 /* The current (folded) contents of table SLOT as canonical extension elements, for tests.
    Writes min(entries, CAP) entries of D words; *ENTRIES gets the table's size.  SC_ESTATE while the
    folded table does not exist in memory: during the small-value rounds (rounds 1 and 2 of a product
@@ -173,6 +181,7 @@ typedef struct sc_transcript sc_transcript;
 /* MAKE-TRANSCRIPT (src/transcript.lisp:75-84), prover side: B3S over "LLM-SUMCHECK-v6-O|" | label. */
 sc_transcript *sc_transcript_new(const uint8_t *label, size_t label_len, int degree);
 void sc_transcript_free(sc_transcript *tr);
+int sc_transcript_degree(const sc_transcript *tr);   /* TRANSCRIPT-DEGREE */
 /* ABSORB (:95-100), SEND of a field array (:133-135), CHALLENGE-BASE (:166-172), B3S-DIGEST of the state */
 int sc_transcript_absorb(sc_transcript *tr, const uint8_t *data, uint64_t len);
 int sc_transcript_send(sc_transcript *tr, const uint32_t *values, int rows, int cols);
@@ -204,6 +213,22 @@ int sc_prove(sc_ctx *ctx, sc_transcript *tr, int n, const char *statement, int n
              int nconstants, const char *const *constant_names, const uint32_t *constant_values, const char *label,
              int K, const uint32_t *block_weights, int degree, uint32_t *challenges, uint32_t *finals,
              uint32_t *folded);
+
+/* PROVE-UPPER (src/gkr.lisp:215-272): the upper layers of the batched LogUp-GKR fraction trees.
+   A domain has K blocks of 2^N leaf fractions p/q for each of LOOKUPS lookups; LEAVES_P[l] and
+   LEAVES_Q[l] are K * 2^N entries of D words, block-major (host memory, or device memory when
+   LEAVES_ON_DEVICE is nonzero; they are only read).  Builds the fraction trees on the device
+   (FRACTION-TREES, :149-188), sends the roots and proves every layer down to the leaves' parents
+   on TR, exactly the messages and challenges of the reference.  CTXS holds one context per lookup,
+   all on the current device and without a communicator: the layer statement is a sum over the
+   lookups, and lookup l's share of each round's sums is computed on CTXS[l].  Tables 0..4 of the
+   contexts are overwritten.  N >= 1.  Device memory: about 4 * K * 2^N * D words per lookup for
+   the trees, besides the contexts' own.
+   Outputs (any may be NULL): RI (N - 1) * D words (the in-block point), RB ceil(log2 K) * D (the
+   block point), CP and CQ LOOKUPS * D each (the claims on the leaf layer). */
+int sc_gkr_prove_upper(sc_ctx *const *ctxs, int lookups, sc_transcript *tr, int n, int K, const uint32_t *const *leaves_p,
+                       const uint32_t *const *leaves_q, int leaves_on_device, const char *label, uint32_t *ri, uint32_t *rb,
+                       uint32_t *cp, uint32_t *cq);
 
 #ifdef __cplusplus
 }

@@ -31,7 +31,7 @@ SYMBOLS = [
     "sc_transcript_new", "sc_transcript_free", "sc_transcript_absorb", "sc_transcript_send",
     "sc_transcript_challenge_base", "sc_transcript_challenge_bits", "sc_transcript_digest",
     "sc_transcript_message_count", "sc_transcript_message", "sc_transcript_sent_bytes", "sc_transcript_encode",
-    "sc_lower_statement", "sc_prove",
+    "sc_lower_statement", "sc_prove", "sc_borrow_table", "sc_transcript_degree", "sc_gkr_prove_upper",
 ]
 
 
@@ -407,3 +407,41 @@ def prove(tr, n, statement, tables, eq=None, constants=(), label="sc", block_wei
     _check(code, prover._h)
     return (ch[:n].tolist(), {nm: fin[i].tolist() for i, nm in enumerate(names)},
             {nm: fol[i].tolist() for i, nm in enumerate(names)})
+
+
+_gkr_provers = []
+
+
+def gkr_prove_upper(tr, n, k, leaves, label="gkr", provers=None):
+    """The reference's (prove-upper tr n k leaves :label label), src/gkr.lisp:215-272.
+
+    leaves: a list, one (p, q) per lookup, of arrays of shape (k 2^n, D), block-major.  provers: one
+    Prover per lookup (made and kept when not given).  Returns (ri, rb, cp, cq) as lists of D-word lists.
+    """
+    D = tr.degree
+    lookups = len(leaves)
+    if provers is None:
+        while len(_gkr_provers) < lookups:
+            _gkr_provers.append(Prover(0))
+        provers = _gkr_provers[:lookups]
+    ps = [_u32(p).reshape(-1, D) for p, _ in leaves]
+    qs = [_u32(q).reshape(-1, D) for _, q in leaves]
+    for a in ps + qs:
+        if a.shape[0] != k << n:
+            raise InvalidParameter(-1, "leaves of %d entries: expected %d" % (a.shape[0], k << n))
+    lk = (k - 1).bit_length()
+    ri = np.zeros((max(n - 1, 1), D), dtype=np.uint32)
+    rb = np.zeros((max(lk, 1), D), dtype=np.uint32)
+    cp = np.zeros((lookups, D), dtype=np.uint32)
+    cq = np.zeros((lookups, D), dtype=np.uint32)
+    ctxs = (C.c_void_p * lookups)(*[p._h.value for p in provers])
+    pp = (_u32p * lookups)(*[_ptr(a) for a in ps])
+    qp = (_u32p * lookups)(*[_ptr(a) for a in qs])
+    rc = library().sc_gkr_prove_upper(ctxs, lookups, C.c_void_p(tr._h), n, k, pp, qp, 0, label.encode(), _ptr(ri), _ptr(rb), _ptr(cp), _ptr(cq))
+    if rc:
+        for p in provers:      # the context that failed holds the message
+            detail = library().sc_last_error(p._h).decode()
+            if detail:
+                _check(rc, p._h)
+        _check(rc)
+    return ri[:n - 1].tolist(), rb[:lk].tolist(), cp.tolist(), cq.tolist()

@@ -59,6 +59,7 @@ struct Nccl {
 struct TableState {
     u32 *t0 = nullptr;          // the caller's table on the device (canonical words)
     u64 t0_cap = 0;             // bytes allocated
+    bool borrowed = false;      // t0 is the caller's device memory (sc_borrow_table): never freed or written here
     u64 entries = 0;
     int stride = 0;
     u32 *buf[2] = {nullptr, nullptr};   // ping-pong buffers of the folded table (D canonical words per entry)
@@ -309,7 +310,7 @@ extern "C" int sc_destroy(sc_ctx *ctx) {
         if (r == ctx->rank || ctx->world == 1) cudaFree(ctx->mail[r]); else cudaIpcCloseMemHandle(ctx->mail[r]);
     }
     if (ctx->comm && g_nccl.CommDestroy) g_nccl.CommDestroy(ctx->comm);
-    for (auto &t : ctx->tab) { cudaFree(t.t0); cudaFree(t.buf[0]); cudaFree(t.buf[1]); }
+    for (auto &t : ctx->tab) { if (!t.borrowed) cudaFree(t.t0); cudaFree(t.buf[0]); cudaFree(t.buf[1]); }
     for (auto p : ctx->d_gtab) cudaFree(p);
     cudaFree(ctx->d_eq); cudaFree(ctx->d_bw); cudaFree(ctx->d_chunks); cudaFree(ctx->d_weights); cudaFree(ctx->d_descs);
     cudaFree(ctx->d_sv); cudaFree(ctx->d_partials); cudaFree(ctx->d_counter); cudaFree(ctx->d_out); cudaFree(ctx->d_export); cudaFree(ctx->d_gather);
@@ -563,8 +564,25 @@ static int table_slot(sc_ctx *ctx, int slot, uint64_t entries, int stride) {
     cudaSetDevice(ctx->device);
     tail_stop(ctx);
     TableState &t = ctx->tab[slot];
+    if (t.borrowed) { t.t0 = nullptr; t.t0_cap = 0; t.borrowed = false; }
     int rc = ensure(ctx, &t.t0, &t.t0_cap, entries * (u64)stride * 4);
     if (rc) return rc;
+    t.entries = entries; t.stride = stride;
+    ctx->begun = false;
+    return SC_OK;
+}
+
+extern "C" int sc_borrow_table(sc_ctx *ctx, int slot, const uint32_t *table_dev, uint64_t entries, int stride) {
+    if (!ctx) return SC_EINVAL;
+    if (slot < 0 || slot >= SC_MAX_TABLES) return fail(ctx, SC_EINVAL, "table slot %d: expected 0..%d", slot, SC_MAX_TABLES - 1);
+    if (stride != 1 && stride != 4 && stride != 8) return fail(ctx, SC_EINVAL, "stride %d: expected 1 or the extension degree", stride);
+    if (!table_dev || entries == 0) return fail(ctx, SC_EINVAL, "empty table");
+    if ((uintptr_t)table_dev % 16) return fail(ctx, SC_EINVAL, "a borrowed table must start on a 16-byte boundary");
+    cudaSetDevice(ctx->device);
+    tail_stop(ctx);
+    TableState &t = ctx->tab[slot];
+    if (!t.borrowed) dev_free(ctx, t.t0, t.t0_cap);
+    t.t0 = const_cast<u32 *>(table_dev); t.t0_cap = 0; t.borrowed = true;
     t.entries = entries; t.stride = stride;
     ctx->begun = false;
     return SC_OK;

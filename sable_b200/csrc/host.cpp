@@ -270,6 +270,7 @@ extern "C" sc_transcript *sc_transcript_new(const uint8_t *label, size_t label_l
     return tr;
 }
 extern "C" void sc_transcript_free(sc_transcript *tr) { delete tr; }
+extern "C" int sc_transcript_degree(const sc_transcript *tr) { return tr ? tr->degree : 0; }
 extern "C" int sc_transcript_absorb(sc_transcript *tr, const uint8_t *data, uint64_t len) {
     if (!tr || (len && !data)) return SC_EINVAL;
     tr->absorb(data, len);
