@@ -137,6 +137,86 @@ def cpu_port(cfg, D, n_sample, steps, warmup, threads=0):
     return (1 << n_sample) / mean / 1e6, mean, cores, tr.proof()
 
 
+def gkr_bench(args):
+    """LogUp-GKR upper layers (sc_gkr_prove_upper): one step is one whole PROVE-UPPER of LOOKUPS trees of
+    K blocks of 2^n leaf fractions, trees and host transcript included; value = leaves / time."""
+    import numpy as np
+    import torch
+    import sable_b200 as sb
+    D, n, K, L = args.degree, args.n or 22, args.blocks, args.gkr
+    torch.cuda.set_device(0)
+    gen = torch.Generator(device="cuda").manual_seed(SEED)
+    leaves = []
+    for _ in range(L):
+        p = torch.randint(0, P, ((K << n), D), generator=gen, device="cuda", dtype=torch.int64).to(torch.int32)
+        q = torch.randint(0, P, ((K << n), D), generator=gen, device="cuda", dtype=torch.int64).to(torch.int32)
+        q[:, 0] |= 1
+        leaves.append((p.contiguous(), q.contiguous()))
+    provers = [sb.Prover(0) for _ in range(L)]
+
+    def run(lv):
+        tr = sb.Transcript("bench", D)
+        out = sb.gkr_prove_upper(tr, n, K, lv, provers=provers)
+        return tr, out
+
+    def timed(lv, steps):
+        torch.cuda.synchronize()
+        t0 = time.perf_counter()
+        for _ in range(steps):
+            tr, _ = run(lv)
+        torch.cuda.synchronize()
+        return (time.perf_counter() - t0) / steps, tr
+
+    for _ in range(args.warmup):
+        run(leaves)
+    before = sum(p.launches for p in provers)
+    sampler = ClockSampler(0)
+    sampler.start()
+    mean, tr = timed(leaves, args.steps)
+    launches = (sum(p.launches for p in provers) - before) // args.steps
+    e2e = None
+    if not args.no_e2e:
+        host = [(p.cpu().numpy().view(np.uint32), q.cpu().numpy().view(np.uint32)) for p, q in leaves]
+        run(host)
+        emean, etr = timed(host, max(1, args.steps // 2))
+        assert etr.proof() == tr.proof()
+        e2e = {"value": L * (K << n) / emean / 1e6, "unit": "Mleaves/s", "ms_per_step": emean * 1e3,
+               "h2d_bytes_per_step": 2 * L * (K << n) * D * 4, "d2h_bytes_per_step": len(tr.proof())}
+    clocks = sampler.stop()
+    # bytes the layers must move: the tree pass reads a layer and writes the one above (3/2 of a layer); the
+    # layer's sumcheck reads its tables in rounds 0 and 1 and a geometric tail of folded tables after (4 x in all)
+    entry = 4 * D
+    tree = sum(2 * L * (K << m) * entry * 3 // 2 for m in range(1, n + 1))
+    proofs = sum(2 * L * (K << m) * entry * 4 for m in range(1, n))
+    cpu = None
+    if not args.no_cpu:
+        from oracle import gkr_oracle as gkr, pyoracle as orc
+        ns = min(n, 18)
+        rng = np.random.default_rng(SEED)
+        lv = []
+        for _ in range(L):
+            p = rng.integers(0, P, size=(K << ns, D), dtype=np.uint32)
+            q = rng.integers(0, P, size=(K << ns, D), dtype=np.uint32)
+            q[:, 0] |= 1
+            lv.append((p, q))
+        t0 = time.perf_counter()
+        gkr.prove_upper(orc.Transcript("bench", D), ns, K, lv, threads=0)
+        dt = time.perf_counter() - t0
+        cpu = {"value": L * (K << ns) / dt / 1e6, "unit": "Mleaves/s", "cores": orc.max_threads(), "kind": "port",
+               "sample": "the same trees at n=%d, all host threads in the sumchecks" % ns}
+    print(json.dumps({
+        "metric": "gkr prove-upper Mleaves/s", "value": L * (K << n) / mean / 1e6, "unit": "Mleaves/s", "n_gpus": 1, "steps": args.steps,
+        "warmup": args.warmup, "ms_per_step": mean * 1e3, "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "u32",
+        "data": "synthetic", "config": {"workload": "LogUp-GKR upper layers: %d lookups, K=%d blocks of 2^%d leaf fractions, D=%d" % (L, K, n, D),
+                                        "l2": "inputs larger than L2" if 2 * L * (K << n) * entry > (126 << 20) else "inputs fit L2"},
+        "e2e": e2e, "gpu_launches": launches, "clocks": clocks,
+        "roofline": {"bound": "hbm", "achieved": (tree + proofs) / mean / 1e9, "peak": measured_peak()[0], "unit": "GB/s",
+                     "frac": (tree + proofs) / mean / 1e9 / measured_peak()[0], "traffic": None,
+                     "note": "whole PROVE-UPPER: algorithmic bytes of all tree passes and all layers' sumchecks over wall time, %d rounds of latency included" % (n * (n - 1) // 2)},
+        "cpu_baseline": cpu, "proof_sha256": hashlib.sha256(tr.proof()).hexdigest(),
+    }))
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -149,7 +229,11 @@ def main():
     ap.add_argument("--cpu-n", type=int, default=24, help="n of the CPU sample")
     ap.add_argument("--no-e2e", action="store_true")
     ap.add_argument("--no-cpu", action="store_true")
+    ap.add_argument("--gkr", type=int, default=0, metavar="LOOKUPS", help="time LogUp-GKR PROVE-UPPER of this many lookups instead (one GPU; --n leaf bits, default 22)")
+    ap.add_argument("--blocks", type=int, default=1, help="K of --gkr")
     args = ap.parse_args()
+    if args.gkr:
+        return gkr_bench(args)
 
     rank = int(os.environ.get("RANK", "0"))
     world = int(os.environ.get("WORLD_SIZE", "1"))

@@ -94,6 +94,16 @@ int sc_generate_table(sc_ctx *ctx, int slot, uint64_t seed, int table_id, uint64
    sc_gkr_prove_upper).  No reference counterpart: Lisp tables live in host memory. */
 int sc_borrow_table(sc_ctx *ctx, int slot, const uint32_t *table_dev, uint64_t entries, int stride);
 
+/* Room ahead of a run of proofs of growing size (the layers of a tree, smallest first): the folded
+   tables' buffers and the weight tables for proofs of extension degree D with up to N variables
+   over K blocks and NTABLES tables, so that no proof of the run frees and allocates again.
+   Optional; counted in the memory budget.  No reference counterpart. */
+int sc_reserve(sc_ctx *ctx, int D, int n, int K, int ntables);
+/* BYTES of device memory of the context's own for the caller's scratch, at *OUT: grow-only (a
+   larger request frees and allocates, the contents are lost), freed with the context, counted in
+   the memory budget.  No reference counterpart. */
+int sc_workspace(sc_ctx *ctx, uint64_t bytes, void **out);
+
 /* The current (folded) contents of table SLOT as canonical extension elements, for tests.
    Writes min(entries, CAP) entries of D words; *ENTRIES gets the table's size.  SC_ESTATE while the
    folded table does not exist in memory: during the small-value rounds (rounds 1 and 2 of a product
@@ -223,7 +233,8 @@ int sc_prove(sc_ctx *ctx, sc_transcript *tr, int n, const char *statement, int n
    all on the current device and without a communicator: the layer statement is a sum over the
    lookups, and lookup l's share of each round's sums is computed on CTXS[l].  Tables 0..4 of the
    contexts are overwritten.  N >= 1.  Device memory: about 4 * K * 2^N * D words per lookup for
-   the trees, besides the contexts' own.
+   the trees, taken from the first context's workspace (sc_workspace) and kept by it for the next
+   call, besides the contexts' own buffers.
    Outputs (any may be NULL): RI (N - 1) * D words (the in-block point), RB ceil(log2 K) * D (the
    block point), CP and CQ LOOKUPS * D each (the claims on the leaf layer). */
 int sc_gkr_prove_upper(sc_ctx *const *ctxs, int lookups, sc_transcript *tr, int n, int K, const uint32_t *const *leaves_p,

@@ -31,7 +31,7 @@ SYMBOLS = [
     "sc_transcript_new", "sc_transcript_free", "sc_transcript_absorb", "sc_transcript_send",
     "sc_transcript_challenge_base", "sc_transcript_challenge_bits", "sc_transcript_digest",
     "sc_transcript_message_count", "sc_transcript_message", "sc_transcript_sent_bytes", "sc_transcript_encode",
-    "sc_lower_statement", "sc_prove", "sc_borrow_table", "sc_transcript_degree", "sc_gkr_prove_upper",
+    "sc_lower_statement", "sc_prove", "sc_borrow_table", "sc_transcript_degree", "sc_gkr_prove_upper", "sc_reserve", "sc_workspace",
 ]
 
 
@@ -234,6 +234,10 @@ class Prover:
         """Upload from raw host memory (for example pinned memory) at ``address``."""
         self._call("sc_upload_table", slot, C.cast(C.c_void_p(address), _u32p), C.c_uint64(entries), stride)
 
+    def borrow_table(self, slot, address, entries, stride):
+        """Table ``slot`` is the caller's device memory at ``address`` (canonical words); nothing is copied."""
+        self._call("sc_borrow_table", slot, C.cast(C.c_void_p(address), _u32p), C.c_uint64(entries), stride)
+
     def generate_table(self, slot, seed, table_id, entries, stride, first=0, nonzero=False):
         self._call("sc_generate_table", slot, C.c_uint64(seed), table_id, C.c_uint64(first), C.c_uint64(entries), stride,
                    1 if nonzero else 0)
@@ -415,7 +419,8 @@ _gkr_provers = []
 def gkr_prove_upper(tr, n, k, leaves, label="gkr", provers=None):
     """The reference's (prove-upper tr n k leaves :label label), src/gkr.lisp:215-272.
 
-    leaves: a list, one (p, q) per lookup, of arrays of shape (k 2^n, D), block-major.  provers: one
+    leaves: a list, one (p, q) per lookup, of arrays of shape (k 2^n, D), block-major (numpy arrays,
+    or CUDA tensors of 32-bit words, which are read where they lie).  provers: one
     Prover per lookup (made and kept when not given).  Returns (ri, rb, cp, cq) as lists of D-word lists.
     """
     D = tr.degree
@@ -424,20 +429,29 @@ def gkr_prove_upper(tr, n, k, leaves, label="gkr", provers=None):
         while len(_gkr_provers) < lookups:
             _gkr_provers.append(Prover(0))
         provers = _gkr_provers[:lookups]
-    ps = [_u32(p).reshape(-1, D) for p, _ in leaves]
-    qs = [_u32(q).reshape(-1, D) for _, q in leaves]
-    for a in ps + qs:
-        if a.shape[0] != k << n:
-            raise InvalidParameter(-1, "leaves of %d entries: expected %d" % (a.shape[0], k << n))
+    on_device = all(hasattr(a, "data_ptr") for pq in leaves for a in pq)   # device tensors (uint32/int32, contiguous): read in place
+    if on_device:
+        ps, qs = [p for p, _ in leaves], [q for _, q in leaves]
+        for a in ps + qs:
+            if not a.is_cuda or not a.is_contiguous() or a.element_size() != 4 or a.numel() != (k << n) * D:
+                raise InvalidParameter(-1, "device leaves: expected contiguous 32-bit tensors of %d words" % ((k << n) * D))
+        address = lambda a: C.cast(C.c_void_p(a.data_ptr()), _u32p)
+    else:
+        ps = [_u32(p).reshape(-1, D) for p, _ in leaves]
+        qs = [_u32(q).reshape(-1, D) for _, q in leaves]
+        for a in ps + qs:
+            if a.shape[0] != k << n:
+                raise InvalidParameter(-1, "leaves of %d entries: expected %d" % (a.shape[0], k << n))
+        address = _ptr
     lk = (k - 1).bit_length()
     ri = np.zeros((max(n - 1, 1), D), dtype=np.uint32)
     rb = np.zeros((max(lk, 1), D), dtype=np.uint32)
     cp = np.zeros((lookups, D), dtype=np.uint32)
     cq = np.zeros((lookups, D), dtype=np.uint32)
     ctxs = (C.c_void_p * lookups)(*[p._h.value for p in provers])
-    pp = (_u32p * lookups)(*[_ptr(a) for a in ps])
-    qp = (_u32p * lookups)(*[_ptr(a) for a in qs])
-    rc = library().sc_gkr_prove_upper(ctxs, lookups, C.c_void_p(tr._h), n, k, pp, qp, 0, label.encode(), _ptr(ri), _ptr(rb), _ptr(cp), _ptr(cq))
+    pp = (_u32p * lookups)(*[address(a) for a in ps])
+    qp = (_u32p * lookups)(*[address(a) for a in qs])
+    rc = library().sc_gkr_prove_upper(ctxs, lookups, C.c_void_p(tr._h), n, k, pp, qp, 1 if on_device else 0, label.encode(), _ptr(ri), _ptr(rb), _ptr(cp), _ptr(cq))
     if rc:
         for p in provers:      # the context that failed holds the message
             detail = library().sc_last_error(p._h).decode()

@@ -123,6 +123,8 @@ struct sc_ctx {
     u32 *d_out = nullptr, *h_out = nullptr, *h_out_dev = nullptr;   // h_out: mapped pinned; h_out_dev its device alias
     u32 *d_export = nullptr, *h_export = nullptr;
     u64 export_cap = 0;
+    void *d_work = nullptr;          // a caller's scratch (sc_workspace), grow-only
+    u64 work_cap = 0;
     u32 *d_gather = nullptr;         // world * SV_MAX_WORDS words: the ranks' sums side by side
     u32 *d_sv = nullptr;             // this rank's small-value accumulators
     u32 *d_gtab[SC_MAX_TABLES];      // gathered tables
@@ -313,7 +315,7 @@ extern "C" int sc_destroy(sc_ctx *ctx) {
     for (auto &t : ctx->tab) { if (!t.borrowed) cudaFree(t.t0); cudaFree(t.buf[0]); cudaFree(t.buf[1]); }
     for (auto p : ctx->d_gtab) cudaFree(p);
     cudaFree(ctx->d_eq); cudaFree(ctx->d_bw); cudaFree(ctx->d_chunks); cudaFree(ctx->d_weights); cudaFree(ctx->d_descs);
-    cudaFree(ctx->d_sv); cudaFree(ctx->d_partials); cudaFree(ctx->d_counter); cudaFree(ctx->d_out); cudaFree(ctx->d_export); cudaFree(ctx->d_gather);
+    cudaFree(ctx->d_sv); cudaFree(ctx->d_partials); cudaFree(ctx->d_counter); cudaFree(ctx->d_out); cudaFree(ctx->d_export); cudaFree(ctx->d_gather); cudaFree(ctx->d_work);
     if (ctx->h_out) cudaFreeHost(ctx->h_out);
     if (ctx->h_export) cudaFreeHost(ctx->h_export);
     for (auto e : ctx->ev) cudaEventDestroy(e);
@@ -674,6 +676,48 @@ static int split_bits(int D, int v) {
     if (v < 20) return 0;
     int a = v - 12;
     return a < low_bits_cap(D) ? a : low_bits_cap(D);
+}
+
+// Device memory of the context's own for a caller's scratch: grow-only, freed with the context, counted in
+// the memory budget.  The contents survive until the next call that asks for more.
+extern "C" int sc_workspace(sc_ctx *ctx, uint64_t bytes, void **out) {
+    if (!ctx || !out) return SC_EINVAL;
+    cudaSetDevice(ctx->device);
+    int rc = ensure(ctx, &ctx->d_work, &ctx->work_cap, bytes);
+    if (rc) return rc;
+    *out = ctx->d_work;
+    return SC_OK;
+}
+
+// Make room ahead of a run of proofs of growing size (the layers of a tree, smallest first): the folded
+// tables' buffers and the weight tables for proofs of up to N variables over K blocks and NTABLES tables,
+// so that no proof of the run has to free and allocate again.
+extern "C" int sc_reserve(sc_ctx *ctx, int D, int n, int K, int ntables) {
+    if (!ctx) return SC_EINVAL;
+    if (D != 4 && D != 8) return fail(ctx, SC_EINVAL, "extension degree %d: expected 4 or 8", D);
+    if (n < 0 || n > 40 || K < 1 || ntables < 1 || ntables > SC_MAX_TABLES) return fail(ctx, SC_EINVAL, "sc_reserve: n = %d, K = %d, %d tables", n, K, ntables);
+    cudaSetDevice(ctx->device);
+    tail_stop(ctx);
+    const u64 entries = (u64)K << n;
+    int rc;
+    for (int s = 0; s < ntables; s++) {
+        TableState &t = ctx->tab[s];
+        if (t.cur_buf >= 0) { t.cur = nullptr; t.cur_buf = -1; ctx->begun = false; }   // a buffer in use may move
+        if ((rc = ensure(ctx, &t.buf[0], &t.buf_cap[0], entries / 2 * D * 4))) return rc;
+        if ((rc = ensure(ctx, &t.buf[1], &t.buf_cap[1], entries / 4 * D * 4))) return rc;
+    }
+    u64 words = 0;
+    for (int j = 0; j < n; j++) {   // as sc_begin lays the weights out, with eq and block weights present
+        const int v = n - 1 - j, a = split_bits(D, v);
+        if (a > 0) words += ((u64)1 << a) * 2 * D;
+        words += ((u64)1 << (v - a)) * (u64)K * D;
+    }
+    if ((rc = ensure(ctx, &ctx->d_weights, &ctx->weights_cap, (words ? words : 4) * 4))) return rc;
+    if ((rc = ensure(ctx, &ctx->d_chunks, &ctx->chunks_cap, (u64)(n > 0 ? n : 1) * 512 * D * 4))) return rc;
+    if ((rc = ensure(ctx, &ctx->d_eq, &ctx->eq_cap, (u64)(n > 0 ? n : 1) * D * 4))) return rc;
+    if ((rc = ensure(ctx, &ctx->d_bw, &ctx->bw_cap, (u64)K * D * 4))) return rc;
+    if ((rc = ensure(ctx, &ctx->d_descs, &ctx->descs_cap, (u64)(2 * n + 1) * sizeof(WeightDesc)))) return rc;
+    return SC_OK;
 }
 
 extern "C" int sc_begin(sc_ctx *ctx, int n, const uint32_t *eq, int K, const uint32_t *block_weights) {

@@ -14,6 +14,9 @@
 // statement: lookup l runs in its own context with the built-in kernel of that four-table
 // statement, and the host adds the L rows of sums before it sends them.  The tiny sumchecks over
 // the block index (top tree, "-blk") run the same way with tables uploaded from the host.
+#include <chrono>
+#include <cstdio>
+#include <cstdlib>
 #include <cstring>
 #include <string>
 #include <vector>
@@ -106,14 +109,16 @@ struct HostField {
     }
 };
 
-struct DeviceArrays {   // frees what a proof allocated, on every way out
-    std::vector<void *> owned;
-    ~DeviceArrays() { for (void *p : owned) cudaFree(p); }
+struct DeviceArrays {   // the trees' arrays, carved out of one block of the first context's workspace
+    char *base = nullptr;
+    u64 used = 0, cap = 0;
+    static u64 round_up(u64 words) { return ((words ? words : 4) * 4 + 255) & ~(u64)255; }
     cudaError_t get(u32 **p, u64 words) {
-        void *q = nullptr;
-        cudaError_t e = cudaMalloc(&q, (words ? words : 4) * 4);
-        if (e == cudaSuccess) { owned.push_back(q); *p = (u32 *)q; }
-        return e;
+        const u64 bytes = round_up(words);
+        if (used + bytes > cap) return cudaErrorMemoryAllocation;
+        *p = (u32 *)(base + used);
+        used += bytes;
+        return cudaSuccess;
     }
 };
 
@@ -216,7 +221,18 @@ extern "C" int sc_gkr_prove_upper(sc_ctx *const *ctxs, int lookups, sc_transcrip
 
     // ---- the trees (FRACTION-TREES): layer m >= 1 as halves, layer 0 (the blocks' roots) as one array
     DeviceArrays mem;
-    // on every way out the contexts get tables of their own again, before the trees' arrays are freed
+    {
+        u64 bytes = 0;
+        for (int m = n; m >= 1; m--) bytes += 4 * DeviceArrays::round_up(((u64)K << (m - 1)) * D);
+        bytes += 2 * DeviceArrays::round_up((u64)K * D);
+        bytes *= (u64)L;
+        void *base = nullptr;
+        if ((rc = sc_workspace(ctxs[0], bytes, &base))) return rc;
+        mem.base = (char *)base; mem.cap = bytes;
+        // the layers' proofs grow from one entry to K 2^(n-2): make the contexts' room for the largest once
+        if (n >= 2) for (int l = 0; l < L; l++) if ((rc = sc_reserve(ctxs[l], D, n - 2, K, 4))) return rc;
+    }
+    // on every way out the contexts get tables of their own again: the trees' arrays are scratch of the first context
     struct Unborrow {
         sc_ctx *const *ctxs; int L, D;
         ~Unborrow() {
@@ -234,8 +250,15 @@ extern "C" int sc_gkr_prove_upper(sc_ctx *const *ctxs, int lookups, sc_transcrip
         for (int which = 0; which < 2; which++) {
             const u32 *src = which ? leaves_q[l] : leaves_p[l];
             Halves &h = which ? LQ[l][n] : LP[l][n];
-            GK(cudaMemcpy2DAsync(h.lo, width, src, 2 * width, width, (size_t)K, kind, stream));
-            GK(cudaMemcpy2DAsync(h.hi, width, (const char *)src + width, 2 * width, width, (size_t)K, kind, stream));
+            if (K > 16 && width <= ((size_t)1 << 28)) {   // many small blocks: one strided copy per half
+                GK(cudaMemcpy2DAsync(h.lo, width, src, 2 * width, width, (size_t)K, kind, stream));
+                GK(cudaMemcpy2DAsync(h.hi, width, (const char *)src + width, 2 * width, width, (size_t)K, kind, stream));
+            } else {
+                for (int b = 0; b < K; b++) {
+                    GK(cudaMemcpyAsync((char *)h.lo + (size_t)b * width, (const char *)src + (size_t)2 * b * width, width, kind, stream));
+                    GK(cudaMemcpyAsync((char *)h.hi + (size_t)b * width, (const char *)src + (size_t)(2 * b + 1) * width, width, kind, stream));
+                }
+            }
             GK(launch_reduce_words(h.lo, half * D, stream));   // COERCE-EXT reduces its input (src/field.lisp:115-117)
             GK(launch_reduce_words(h.hi, half * D, stream));
         }
@@ -346,7 +369,9 @@ extern "C" int sc_gkr_prove_upper(sc_ctx *const *ctxs, int lookups, sc_transcrip
         for (int b = K; b < KP; b++) mass = F.add(mass, e[b]);
         for (int l = 0; l < L; l++) cq[l] = F.sub(cq[l], mass);
     }
+    const bool trace = getenv("SABLE_B200_TRACE") != nullptr;   // per-layer host times on stderr
     for (int layer = 0; layer + 1 < n; layer++) {   // the in-block layers
+        const auto t_layer = std::chrono::steady_clock::now();
         if ((rc = layer_parts(parts, false))) return rc;
         std::vector<E> bw;                       // BLOCK-WEIGHTS (:73-77)
         if (rb.empty()) bw.push_back(F.one());
@@ -394,6 +419,7 @@ extern "C" int sc_gkr_prove_upper(sc_ctx *const *ctxs, int lookups, sc_transcrip
         if ((rc = finish_layer(finals, &tt))) return rc;
         ri = rho; ri.push_back(tt);
         rb = rbn;
+        if (trace) fprintf(stderr, "gkr layer %d: %.1f us\n", layer, std::chrono::duration<double, std::micro>(std::chrono::steady_clock::now() - t_layer).count());
     }
     if (ri_out) for (size_t i = 0; i < ri.size(); i++) memcpy(ri_out + i * D, ri[i].data(), 4 * (size_t)D);
     if (rb_out) for (size_t i = 0; i < rb.size(); i++) memcpy(rb_out + i * D, rb[i].data(), 4 * (size_t)D);

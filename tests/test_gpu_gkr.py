@@ -39,7 +39,7 @@ def test_device_proof_is_the_oracles(n, k, lookups, d):
     leaves, ta, got, tb, want = both(n, k, lookups, d, n + k + lookups + d)
     assert got == tuple(want)
     assert ta.proof() == tb.proof()
-    roots, ri, rb, cp, cq = gkr.verify_upper("gkr-test", d, ta.messages(), n, k, lookups)
+    roots, ri, rb, cp, cq = gkr.verify_upper("gkr-test", d, ta.messages, n, k, lookups)
     assert (ri, rb, cp, cq) == got
 
 
@@ -58,3 +58,44 @@ def test_words_above_p_are_reduced():
     ta, tb = sb.Transcript("gkr-test", d), sb.Transcript("gkr-test", d)
     assert sb.gkr_prove_upper(ta, n, k, leaves) == sb.gkr_prove_upper(tb, n, k, raised)
     assert ta.proof() == tb.proof()
+
+
+def test_leaves_on_the_device_give_the_same_proof():
+    import torch
+    n, k, lookups, d = 10, 3, 2, 4
+    leaves = random_leaves(lookups, n, k, d, 11)
+    dev = [(torch.from_numpy(p.view(np.int32)).cuda(), torch.from_numpy(q.view(np.int32)).cuda()) for p, q in leaves]
+    ta, tb = sb.Transcript("gkr-test", d), sb.Transcript("gkr-test", d)
+    assert sb.gkr_prove_upper(ta, n, k, leaves) == sb.gkr_prove_upper(tb, n, k, dev)
+    assert ta.proof() == tb.proof()
+    for (p, q), (dp, dq) in zip(leaves, dev):      # the caller's leaves are only read
+        assert (dp.cpu().numpy().view(np.uint32) == p).all() and (dq.cpu().numpy().view(np.uint32) == q).all()
+
+
+def test_borrowed_tables_prove_like_uploaded_ones():
+    # sc_borrow_table: round 0 reads the caller's device memory where it lies; the proof is the uploaded tables' proof
+    import torch
+    d, n = 4, 13
+    rng = np.random.default_rng(8)
+    tables = [("t%d" % i, rng.integers(0, P, size=(1 << n, d), dtype=np.uint32)) for i in range(4)]
+    eq = rng.integers(0, P, size=(n, d), dtype=np.uint32)
+    statement = "(+ (* t0 t3) (* t1 t2) (* 7 t2 t3))"
+    prover = sb.Prover(0)
+    try:
+        ta = sb.Transcript("borrow", d)
+        want = sb.prove(ta, n, statement, tables, eq=eq, prover=prover)
+        dev = [torch.from_numpy(t.view(np.int32)).cuda() for _, t in tables]
+        torch.cuda.synchronize()
+        for rep in range(2):                         # twice: the borrowed tables are left as they were
+            for slot, t in enumerate(dev):
+                prover.borrow_table(slot, t.data_ptr(), 1 << n, d)
+            tb = sb.Transcript("borrow", d)
+            got = sb.prove(tb, n, statement, [(nm, sb.DeviceTable(d)) for nm, _ in tables], eq=eq, prover=prover)
+            assert got == want and tb.proof() == ta.proof()
+        for (_, t), dt in zip(tables, dev):
+            assert (dt.cpu().numpy().view(np.uint32) == t).all()
+        prover.upload_table(0, tables[0][1])         # a slot goes back to memory of the context's own
+        tb = sb.Transcript("borrow", d)
+        assert sb.prove(tb, n, statement, [(nm, sb.DeviceTable(d)) for nm, _ in tables], eq=eq, prover=prover) == want
+    finally:
+        prover.close()
