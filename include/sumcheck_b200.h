@@ -39,7 +39,8 @@ extern "C" {
 #define SC_ECOMM (-6)       /* the collective layer failed or timed out */
 #define SC_ESTATEMENT (-7)  /* malformed statement, or a variable that is neither a table nor a constant */
 
-#define SC_MAX_TABLES 8
+#define SC_MAX_TABLES 8        /* table slots of one context */
+#define SC_MAX_WIDE_TABLES 64  /* tables of one sc_prove: a wider statement is cut into parts on child contexts */
 #define SC_MAX_TERMS 16
 #define SC_MAX_FACTORS 8
 #define SC_MAX_POINTS 8
@@ -99,6 +100,10 @@ int sc_borrow_table(sc_ctx *ctx, int slot, const uint32_t *table_dev, uint64_t e
    over K blocks and NTABLES tables, so that no proof of the run frees and allocates again.
    Optional; counted in the memory budget.  No reference counterpart. */
 int sc_reserve(sc_ctx *ctx, int D, int n, int K, int ntables);
+/* Child INDEX (0..63) of the context at *OUT: a context of its own on the same device, made on
+   first use, destroyed with its parent.  sc_prove runs the parts of a statement wider than one
+   kernel on them.  No reference counterpart. */
+int sc_child(sc_ctx *ctx, int index, sc_ctx **out);
 /* BYTES of device memory of the context's own for the caller's scratch, at *OUT: grow-only (a
    larger request frees and allocates, the contents are lost), freed with the context, counted in
    the memory budget.  No reference counterpart. */
@@ -217,7 +222,11 @@ int sc_lower_statement(const char *statement, int D, int ntables, const char *co
    memory of K * 2^N entries of STRIDES[t] words (with a communicator: this rank's slice, 2^N / world
    entries), or NULL for a table already on the device in slot t (sc_upload_table, sc_generate_table).  DEGREE < 0 takes the statement's degree.
    Outputs (any may be NULL): CHALLENGES n * D, FINALS ntables * D, FOLDED ntables * max(K,1) * D.
-   TR ends in the state, and with the recorded messages, the reference leaves it in. */
+   TR ends in the state, and with the recorded messages, the reference leaves it in.
+   A statement with more than SC_MAX_TABLES tables or SC_MAX_TERMS terms (or, above degree four,
+   more than four tables) is cut into groups of terms, each proved on a context of its own (CTX
+   and its children, sc_child) with the groups' sums added per round: up to SC_MAX_WIDE_TABLES
+   tables, all passed from host memory, one GPU. */
 int sc_prove(sc_ctx *ctx, sc_transcript *tr, int n, const char *statement, int ntables,
              const char *const *table_names, const uint32_t *const *tables, const int *strides, const uint32_t *eq,
              int nconstants, const char *const *constant_names, const uint32_t *constant_values, const char *label,

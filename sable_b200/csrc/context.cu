@@ -123,6 +123,7 @@ struct sc_ctx {
     u32 *d_out = nullptr, *h_out = nullptr, *h_out_dev = nullptr;   // h_out: mapped pinned; h_out_dev its device alias
     u32 *d_export = nullptr, *h_export = nullptr;
     u64 export_cap = 0;
+    std::vector<sc_ctx *> children;  // contexts of this one's own on the same device (sc_child), destroyed with it
     void *d_work = nullptr;          // a caller's scratch (sc_workspace), grow-only
     u64 work_cap = 0;
     u32 *d_gather = nullptr;         // world * SV_MAX_WORDS words: the ranks' sums side by side
@@ -302,6 +303,8 @@ extern "C" int sc_create(int device, sc_ctx **out) {
 
 extern "C" int sc_destroy(sc_ctx *ctx) {
     if (!ctx) return SC_OK;
+    for (sc_ctx *c : ctx->children) sc_destroy(c);
+    ctx->children.clear();
     cudaSetDevice(ctx->device);
     tail_stop(ctx);
     if (ctx->stream) cudaStreamSynchronize(ctx->stream);
@@ -676,6 +679,20 @@ static int split_bits(int D, int v) {
     if (v < 20) return 0;
     int a = v - 12;
     return a < low_bits_cap(D) ? a : low_bits_cap(D);
+}
+
+// Child INDEX of the context: a context of its own on the same device, made on first use and destroyed
+// with its parent (the parts of a statement wider than one kernel run on them).
+extern "C" int sc_child(sc_ctx *ctx, int index, sc_ctx **out) {
+    if (!ctx || !out || index < 0 || index >= 64) return SC_EINVAL;
+    while ((int)ctx->children.size() <= index) {
+        sc_ctx *c = nullptr;
+        int rc = sc_create(ctx->device, &c);
+        if (rc) return fail(ctx, rc, "sc_child: cannot make context %d", (int)ctx->children.size());
+        ctx->children.push_back(c);
+    }
+    *out = ctx->children[index];
+    return SC_OK;
 }
 
 // Device memory of the context's own for a caller's scratch: grow-only, freed with the context, counted in

@@ -10,6 +10,7 @@
 #include <cstdlib>
 #include <cstring>
 #include <map>
+#include <set>
 #include <memory>
 #include <string>
 #include <vector>
@@ -334,9 +335,14 @@ extern "C" uint64_t sc_transcript_encode(const sc_transcript *tr, const char mag
 
 // ------------------------------------------------------------------ the statement as a term table
 
-extern "C" int sc_lower_statement(const char *statement, int D, int ntables, const char *const *table_names, int nconstants,
-                                  const char *const *constant_names, const uint32_t *constant_values, int *degree, int *nterms,
-                                  uint32_t *coeffs, int32_t *term_ptr, int32_t *term_tables) {
+struct LoweredTerm {
+    std::vector<u32> coeff;     // D canonical words
+    std::vector<int> tables;    // sorted, with multiplicity
+};
+
+// EXPAND and the lowering, without a limit on the number of terms
+static int lower_terms(const char *statement, int D, int ntables, const char *const *table_names, int nconstants,
+                       const char *const *constant_names, const uint32_t *constant_values, int *degree, std::vector<LoweredTerm> *out) {
     if (!statement || (D != 4 && D != 8) || ntables < 0 || nconstants < 0) return SC_EINVAL;
     Parser ps{statement};
     std::unique_ptr<Form> form = ps.form();
@@ -370,17 +376,158 @@ extern "C" int sc_lower_statement(const char *statement, int D, int ntables, con
         for (int k = 0; k < D; k++) slot[k] = scf::fadd(slot[k], c[k]);
     }
     if (degree) *degree = deg;
-    int count = 0, used = 0;
+    out->clear();
     for (auto &t : terms) {
         if (std::all_of(t.second.begin(), t.second.end(), [](u32 x) { return x == 0; })) continue;
-        if (count >= SC_MAX_TERMS || (int)t.first.size() > SC_MAX_FACTORS) return SC_EUNSUPPORTED;
-        if (coeffs) memcpy(coeffs + (size_t)count * D, t.second.data(), 4 * (size_t)D);
+        out->push_back(LoweredTerm{t.second, t.first});
+    }
+    return SC_OK;
+}
+
+// the terms as the flat arrays sc_set_statement takes; SC_EUNSUPPORTED beyond its capacities
+static int flatten_terms(const std::vector<LoweredTerm> &terms, int D, int *nterms, uint32_t *coeffs, int32_t *term_ptr, int32_t *term_tables) {
+    int count = 0, used = 0;
+    for (auto &t : terms) {
+        if (count >= SC_MAX_TERMS || (int)t.tables.size() > SC_MAX_FACTORS) return SC_EUNSUPPORTED;
+        if (coeffs) memcpy(coeffs + (size_t)count * D, t.coeff.data(), 4 * (size_t)D);
         if (term_ptr) term_ptr[count] = used;
-        for (int idx : t.first) { if (term_tables) term_tables[used] = idx; used++; }
+        for (int idx : t.tables) { if (term_tables) term_tables[used] = idx; used++; }
         count++;
     }
     if (term_ptr) term_ptr[count] = used;
     if (nterms) *nterms = count;
+    return SC_OK;
+}
+
+extern "C" int sc_lower_statement(const char *statement, int D, int ntables, const char *const *table_names, int nconstants,
+                                  const char *const *constant_names, const uint32_t *constant_values, int *degree, int *nterms,
+                                  uint32_t *coeffs, int32_t *term_ptr, int32_t *term_tables) {
+    std::vector<LoweredTerm> terms;
+    int rc = lower_terms(statement, D, ntables, table_names, nconstants, constant_names, constant_values, degree, &terms);
+    if (rc) return rc;
+    return flatten_terms(terms, D, nterms, coeffs, term_ptr, term_tables);
+}
+
+// ------------------------------------------------------------------ statements wider than one kernel
+//
+// A round's sums are linear in the statement, so a statement with more tables or terms than one
+// kernel takes is cut into parts -- groups of terms over at most four tables where that works --
+// and part k runs on a context of its own (the caller's, then children of it) holding the part's
+// tables; the host adds the parts' sums before it sends them.  A table that several parts use is
+// uploaded to, and folded on, each of them.
+
+static bool needs_parts(const std::vector<LoweredTerm> &terms, int ntables, int points) {
+    if (ntables > SC_MAX_TABLES || (int)terms.size() > SC_MAX_TERMS) return true;
+    std::set<int> used;
+    for (auto &t : terms) used.insert(t.tables.begin(), t.tables.end());
+    return points > 4 && used.size() > 4;   // above degree four the kernels take four tables
+}
+
+struct StatementPart {
+    std::vector<int> tables;            // the part's tables (indices of the caller's), slot by slot
+    std::vector<LoweredTerm> terms;     // over the part's slots
+};
+
+static int cut_into_parts(const std::vector<LoweredTerm> &terms, int ntables, std::vector<StatementPart> *parts) {
+    parts->clear();
+    std::set<int> current;
+    std::vector<std::set<int>> sets;
+    std::vector<std::vector<const LoweredTerm *>> members;
+    for (auto &t : terms) {
+        std::set<int> mine(t.tables.begin(), t.tables.end());
+        if ((int)t.tables.size() > SC_MAX_FACTORS || mine.size() > (size_t)SC_MAX_TABLES) return SC_EUNSUPPORTED;
+        // the first part this term fits: its tables joined with the part's stay within four (or within the term's own count)
+        size_t at = sets.size();
+        const size_t cap = std::max<size_t>(4, mine.size());
+        for (size_t k = 0; k < sets.size(); k++) {
+            std::set<int> joined = sets[k];
+            joined.insert(mine.begin(), mine.end());
+            if (joined.size() <= cap && members[k].size() < (size_t)SC_MAX_TERMS) { at = k; sets[k] = joined; break; }
+        }
+        if (at == sets.size()) { sets.push_back(mine); members.emplace_back(); }
+        members[at].push_back(&t);
+    }
+    if (sets.empty()) { sets.emplace_back(); members.emplace_back(); }
+    // tables outside the statement are only folded: they go where there is room
+    std::set<int> placed;
+    for (auto &st : sets) placed.insert(st.begin(), st.end());
+    for (int t = 0; t < ntables; t++) {
+        if (placed.count(t)) continue;
+        size_t at = 0;
+        while (at < sets.size() && sets[at].size() >= (size_t)SC_MAX_TABLES) at++;
+        if (at == sets.size()) { sets.emplace_back(); members.emplace_back(); }
+        sets[at].insert(t);
+    }
+    for (size_t k = 0; k < sets.size(); k++) {
+        StatementPart pt;
+        pt.tables.assign(sets[k].begin(), sets[k].end());
+        std::map<int, int> slot;
+        for (size_t i = 0; i < pt.tables.size(); i++) slot[pt.tables[i]] = (int)i;
+        for (const LoweredTerm *t : members[k]) {
+            LoweredTerm local{t->coeff, {}};
+            for (int g : t->tables) local.tables.push_back(slot[g]);
+            pt.terms.push_back(local);
+        }
+        parts->push_back(pt);
+    }
+    return SC_OK;
+}
+
+static int prove_in_parts(sc_ctx *ctx, sc_transcript *tr, int n, const std::vector<LoweredTerm> &lowered, int ntables,
+                          const uint32_t *const *tables, const int *strides, const uint32_t *eq, const char *label, int blocks,
+                          const uint32_t *block_weights, int degree, uint32_t *challenges, uint32_t *finals, uint32_t *folded) {
+    const int D = tr->degree, points = std::max(degree, 1);
+    int world = 1, rc;
+    sc_comm_info(ctx, nullptr, &world);
+    if (world > 1 || points > SC_MAX_POINTS) return SC_EUNSUPPORTED;   // parts run on one GPU
+    if (!tables) return SC_EUNSUPPORTED;
+    for (int t = 0; t < ntables; t++) if (!tables[t]) return SC_EUNSUPPORTED;   // a part may sit on another context: host tables only
+    std::vector<StatementPart> parts;
+    if ((rc = cut_into_parts(lowered, ntables, &parts))) return rc;
+    std::vector<sc_ctx *> on(parts.size());
+    for (size_t k = 0; k < parts.size(); k++) {
+        on[k] = ctx;
+        if (k && (rc = sc_child(ctx, (int)k - 1, &on[k]))) return rc;
+        const StatementPart &pt = parts[k];
+        int nterms = 0;
+        std::vector<u32> coeffs((size_t)SC_MAX_TERMS * D);
+        std::vector<int32_t> ptr(SC_MAX_TERMS + 1), idx((size_t)SC_MAX_TERMS * SC_MAX_FACTORS);
+        if ((rc = flatten_terms(pt.terms, D, &nterms, coeffs.data(), ptr.data(), idx.data()))) return rc;
+        if ((rc = sc_set_statement(on[k], D, points, (int)pt.tables.size(), nterms, coeffs.data(), ptr.data(), idx.data()))) return rc;
+        for (size_t i = 0; i < pt.tables.size(); i++)
+            if ((rc = sc_upload_table(on[k], (int)i, tables[pt.tables[i]], (u64)blocks << n, strides[pt.tables[i]]))) return rc;
+        if ((rc = sc_begin(on[k], n, eq, blocks, block_weights))) return rc;
+    }
+    std::vector<u8> header(label, label + strlen(label));   // :24-27, :534
+    header.push_back('|');
+    header.push_back((u8)n); header.push_back((u8)(n >> 8));
+    header.push_back((u8)degree); header.push_back((u8)(degree >> 8));
+    for (int b = 0; b < 4; b++) header.push_back((u8)((u32)blocks >> (8 * b)));
+    tr->absorb(header.data(), header.size());
+    u32 sums[SC_MAX_POINTS * 8], part[SC_MAX_POINTS * 8], r[8];
+    for (int j = 0; j < n; j++) {
+        for (size_t k = 0; k < parts.size(); k++) {
+            if ((rc = sc_round(on[k], k ? part : sums))) return rc;
+            if (k) for (int w = 0; w < points * D; w++) sums[w] = scf::fadd(sums[w], part[w]);
+        }
+        tr->send(sums, points, D);
+        tr->challenge_base(D, r);
+        if (challenges) memcpy(challenges + (size_t)j * D, r, 4 * (size_t)D);
+        for (size_t k = 0; k < parts.size(); k++) if ((rc = sc_challenge(on[k], r))) return rc;
+    }
+    std::vector<bool> have((size_t)ntables, false);
+    for (size_t k = 0; k < parts.size(); k++) {
+        const StatementPart &pt = parts[k];
+        std::vector<u32> out(pt.tables.size() * (size_t)blocks * D);
+        if ((rc = sc_finish(on[k], out.data()))) return rc;
+        for (size_t i = 0; i < pt.tables.size(); i++) {
+            const int g = pt.tables[i];
+            if (have[g]) continue;
+            have[g] = true;
+            if (folded) memcpy(folded + (size_t)g * blocks * D, out.data() + i * (size_t)blocks * D, 4 * (size_t)blocks * D);
+            if (finals) memcpy(finals + (size_t)g * D, out.data() + i * (size_t)blocks * D, 4 * (size_t)D);
+        }
+    }
     return SC_OK;
 }
 
@@ -391,20 +538,23 @@ extern "C" int sc_prove(sc_ctx *ctx, sc_transcript *tr, int n, const char *state
                         int nconstants, const char *const *constant_names, const uint32_t *constant_values, const char *label,
                         int K, const uint32_t *block_weights, int degree, uint32_t *challenges, uint32_t *finals,
                         uint32_t *folded) {
-    if (!ctx || !tr || !statement || n < 0 || ntables < 1 || ntables > SC_MAX_TABLES) return SC_EINVAL;
+    if (!ctx || !tr || !statement || n < 0 || ntables < 1 || ntables > SC_MAX_WIDE_TABLES) return SC_EINVAL;
     const int D = tr->degree;
     if (!label) label = "sc";
     const int blocks = block_weights ? K : 1;
     if (blocks < 1) return SC_EINVAL;
 
     int deg = 0, nterms = 0;
-    std::vector<u32> coeffs((size_t)SC_MAX_TERMS * D);
-    std::vector<int32_t> ptr(SC_MAX_TERMS + 1), idx((size_t)SC_MAX_TERMS * SC_MAX_FACTORS);
-    int rc = sc_lower_statement(statement, D, ntables, table_names, nconstants, constant_names, constant_values, &deg, &nterms,
-                                coeffs.data(), ptr.data(), idx.data());
+    std::vector<LoweredTerm> lowered;
+    int rc = lower_terms(statement, D, ntables, table_names, nconstants, constant_names, constant_values, &deg, &lowered);
     if (rc) return rc;
     if (degree < 0) degree = deg;                       // :513
     const int points = std::max(degree, 1);             // :527
+    if (needs_parts(lowered, ntables, points))
+        return prove_in_parts(ctx, tr, n, lowered, ntables, tables, strides, eq, label, blocks, block_weights, degree, challenges, finals, folded);
+    std::vector<u32> coeffs((size_t)SC_MAX_TERMS * D);
+    std::vector<int32_t> ptr(SC_MAX_TERMS + 1), idx((size_t)SC_MAX_TERMS * SC_MAX_FACTORS);
+    if ((rc = flatten_terms(lowered, D, &nterms, coeffs.data(), ptr.data(), idx.data()))) return rc;
     if ((rc = sc_set_statement(ctx, D, points, ntables, nterms, coeffs.data(), ptr.data(), idx.data()))) return rc;
     // with a communicator each rank passes its slice: entries [rank 2^n / world, (rank + 1) 2^n / world)
     int world = 1;
