@@ -141,4 +141,34 @@ template <int D> SCF_HD Ext<D> emul(const Ext<D> &a, const ExtM<D> &b) {
 }
 template <int D> SCF_HD Ext<D> emul(const Ext<D> &a, const Ext<D> &b) { return emul<D>(a, eprep<D>(b)); }
 
+// a b + s c for a base element s: the product s c_k joins the first four products of coordinate k
+// before their reduction (the sum of four loses one p 2^32 first, so five products fit 64 bits and
+// stay below 2 p 2^32), which saves a reduction and an addition per coordinate.
+template <int D> SCF_HD Ext<D> emul_plus_scaled(const Ext<D> &a, const ExtM<D> &b, const Ext<D> &c, u32 s) {
+    Ext<D> o;
+#pragma unroll
+    for (int e = 0; e < D; e++) {
+        u32 res = 0;
+#pragma unroll
+        for (int g = 0; g < D; g += 4) {
+            u64 acc = 0;
+#pragma unroll
+            for (int i = g; i < g + 4 && i < D; i++) {
+                const int j = (e - i + D) % D;
+                const u32 bj = (i > e) ? b.t[brev<D>(j)] : b.v[brev<D>(j)];
+                acc += (u64)a.v[brev<D>(i)] * bj;
+            }
+            if (g == 0) {
+                u32 hi = (u32)(acc >> 32);
+                hi = umin32(hi, hi - P);
+                acc = (((u64)hi << 32) | (u32)acc) + (u64)c.v[brev<D>(e)] * s;
+            }
+            const u32 part = redc4(acc);
+            res = (g == 0) ? part : fadd(res, part);
+        }
+        o.v[brev<D>(e)] = res;
+    }
+    return o;
+}
+
 }  // namespace scf
