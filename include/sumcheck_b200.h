@@ -210,6 +210,20 @@ uint64_t sc_transcript_sent_bytes(const sc_transcript *tr);
 /* ENCODE-PROOF (src/proofio.lisp:44-49) of the recorded messages: returns the size; writes when CAP allows. */
 uint64_t sc_transcript_encode(const sc_transcript *tr, const char magic[8], uint8_t *out, uint64_t cap);
 
+/* The hash state of the transcript (B3S: chaining value, pending block as little-endian words,
+   bytes pending, blocks compressed), for a device that carries the transcript on. */
+int sc_transcript_state(const sc_transcript *tr, uint32_t cv[8], uint32_t pending[16], int *fill, uint64_t *blocks);
+/* TR (or NULL) is the host transcript of the proof that follows on CTX.  With it the resident kernel
+   of the last rounds copies the transcript's hash state when it starts and derives each challenge
+   itself (SEND of its sums, CHALLENGE-BASE) instead of waiting for the host.  The caller keeps
+   sending the sums sc_round returns and drawing the challenges as before; sc_challenge then checks
+   that the caller's challenge is the device's and returns SC_ESTATE if not (the transcript was
+   used for something else in between).  sc_prove attaches its transcript for the length of the
+   call.  Only with SABLE_B200_DEVICE_TRANSCRIPT=1 in the environment: one GPU thread hashes a
+   round in about 5 us, the host answers in about 4.5.  No reference counterpart: the reference's
+   transcript is host code throughout. */
+int sc_attach_transcript(sc_ctx *ctx, const sc_transcript *tr);
+
 /* EXPAND + the lowering to a term table (src/forms.lisp:57-78; STATEMENT-DEGREE,
    src/sumcheck.lisp:33-35).  STATEMENT is the form as text, e.g. "(+ (* alpha t0 t1) (* 3 t1))".
    Outputs as for sc_set_statement; *DEGREE gets the degree in the tables.  Capacities:

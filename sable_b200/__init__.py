@@ -31,7 +31,7 @@ SYMBOLS = [
     "sc_transcript_new", "sc_transcript_free", "sc_transcript_absorb", "sc_transcript_send",
     "sc_transcript_challenge_base", "sc_transcript_challenge_bits", "sc_transcript_digest",
     "sc_transcript_message_count", "sc_transcript_message", "sc_transcript_sent_bytes", "sc_transcript_encode",
-    "sc_lower_statement", "sc_prove", "sc_borrow_table", "sc_transcript_degree", "sc_gkr_prove_upper", "sc_reserve", "sc_workspace", "sc_child",
+    "sc_lower_statement", "sc_prove", "sc_borrow_table", "sc_transcript_degree", "sc_gkr_prove_upper", "sc_reserve", "sc_workspace", "sc_child", "sc_attach_transcript", "sc_transcript_state",
 ]
 
 

@@ -140,6 +140,8 @@ struct sc_ctx {
     unsigned tail_polls = TAIL_POLL_LIMIT;
     u64 tail_entries = 0;            // entries of the tables the first round of the launch read
     int tail_buf0[SC_MAX_TABLES];    // per slot: which of the table's two buffers the first round wrote
+    const sc_transcript *attached = nullptr;   // the host transcript the resident kernel may copy its hash state from
+    bool tail_own = false;           // the running resident kernel derives its challenges itself
 
     // the first two rounds from one pass over base tables (see SvArgs)
     bool sv_ok = false;
@@ -291,6 +293,7 @@ extern "C" int sc_create(int device, sc_ctx **out) {
          cudaHostGetDevicePointer(&ctx->h_tail_dev, ctx->h_tail, 0) == cudaSuccess;
     if (!ok) { cudaGetLastError(); sc_destroy(ctx); return SC_ECUDA; }
     memset(ctx->h_tail, 0, TAIL_WORDS * 4);
+    memset(ctx->h_out, 0, (MAX_PARTIAL_WORDS + 32) * 4);   // pinned memory comes back as an earlier context left it: its posted words must not be taken for ours
     if (cudaHostAlloc(&ctx->h_sv, (SV_MAX_WORDS + 32) * 4, cudaHostAllocMapped) != cudaSuccess ||
         cudaHostGetDevicePointer(&ctx->h_sv_dev, ctx->h_sv, 0) != cudaSuccess) { cudaGetLastError(); sc_destroy(ctx); return SC_ECUDA; }
     memset(ctx->h_sv, 0, (SV_MAX_WORDS + 32) * 4);
@@ -681,6 +684,16 @@ static int split_bits(int D, int v) {
     return a < low_bits_cap(D) ? a : low_bits_cap(D);
 }
 
+// The host transcript of the proof that follows (or NULL): with it the resident kernel of the last rounds
+// copies the transcript's hash state when it starts and derives every challenge itself instead of waiting
+// for the host; the caller goes on sending the sums and drawing the challenges as before, and sc_challenge
+// checks that they are the device's.  The transcript must not be used for anything else between those calls.
+extern "C" int sc_attach_transcript(sc_ctx *ctx, const sc_transcript *tr) {
+    if (!ctx) return SC_EINVAL;
+    ctx->attached = tr;
+    return SC_OK;
+}
+
 // Child INDEX of the context: a context of its own on the same device, made on first use and destroyed
 // with its parent (the parts of a statement wider than one kernel run on them).
 extern "C" int sc_child(sc_ctx *ctx, int index, sc_ctx **out) {
@@ -1058,6 +1071,23 @@ static int tail_start(sc_ctx *ctx) {
     a.seq = ctx->tail_seq;
     a.host = ctx->h_tail_dev;
     a.poll_limit = ctx->tail_polls;
+    {   // with a transcript attached the block derives the challenges itself: it starts from the host's hash state
+        // of this moment, which is the state before this round's sums are sent
+        const char *env = getenv("SABLE_B200_DEVICE_TRANSCRIPT");   // off unless asked for: measured slower than the host's answer
+        const bool on = env && env[0] == '1';
+        ctx->tail_own = false;
+        if (ctx->attached && on) {
+            uint32_t cv[8], pending[16];
+            int fill = 0;
+            uint64_t blocks = 0;
+            if (sc_transcript_state(ctx->attached, cv, pending, &fill, &blocks) == SC_OK && sc_transcript_degree(ctx->attached) == D) {
+                a.own_transcript = 1;
+                memcpy(a.b3_cv, cv, sizeof cv); memcpy(a.b3_pending, pending, sizeof pending);
+                a.b3_fill = fill; a.b3_blocks = blocks;
+                ctx->tail_own = true;
+            }
+        }
+    }
     ((volatile u32 *)ctx->h_tail)[TAIL_STATUS] = 0;
     std::atomic_thread_fence(std::memory_order_seq_cst);
     CU(launch_tail(D, ctx->shape, ctx->points, ctx->nt_used, a, ctx->stream));
@@ -1263,6 +1293,19 @@ extern "C" int sc_challenge(sc_ctx *ctx, const uint32_t *r) {
     if (ctx->have_r) return fail(ctx, SC_ESTATE, "round %d already has its challenge", ctx->j - 1);
     for (int c = 0; c < ctx->D; c++) ctx->r[c] = r[c] % P;
     ctx->have_r = true;
+    if (ctx->tail_active && ctx->tail_own) {
+        // the resident kernel derived this challenge itself from its copy of the transcript: it must be the caller's
+        const u32 k = (u32)(ctx->j - 1 - ctx->tail_first);
+        const u32 *slot = ctx->h_tail + (size_t)k * TAIL_SLOT_WORDS;
+        if (!wait_word(ctx, slot + 50, ctx->tail_seq + k)) return fail(ctx, SC_ECUDA, "the device did not post its challenge of round %d", ctx->j - 1);
+        for (int c = 0; c < ctx->D; c++)
+            if (((volatile const u32 *)slot)[52 + c] != ctx->r[c]) {
+                tail_stop(ctx);
+                ctx->begun = false;
+                return fail(ctx, SC_ESTATE, "round %d: the challenge differs from the attached transcript's (was the transcript used for something else during the proof?)", ctx->j - 1);
+            }
+        return SC_OK;
+    }
     if (ctx->tail_active) {   // hand the challenge to the resident kernel: the words first, then the word it polls
         u32 *slot = ctx->h_tail + (size_t)(ctx->j - 1 - ctx->tail_first) * TAIL_SLOT_WORDS;
         for (int c = 0; c < ctx->D; c++) ((volatile u32 *)slot)[40 + c] = ctx->r[c];
@@ -1283,6 +1326,11 @@ extern "C" int sc_finish(sc_ctx *ctx, uint32_t *folded) {
     if (ctx->tail_active) {   // the resident kernel folds by the last challenge and posts the final entries
         const bool ok = wait_word(ctx, ctx->h_tail + TAIL_FINALS - 1, ctx->tail_seq);
         CU(cudaStreamSynchronize(ctx->stream));
+        if (ok && ctx->tail_own && getenv("SABLE_B200_TRACE"))
+            for (int k = 0; k < ctx->tail_rounds; k++) {
+                const u32 *slot = ctx->h_tail + (size_t)k * TAIL_SLOT_WORDS;
+                fprintf(stderr, "  resident round %d: compute %u ns, post %u ns, absorb %u ns, challenge %u ns\n", ctx->tail_first + k, slot[60], slot[61], slot[62], slot[63]);
+            }
         if (ok) {
             ctx->tail_active = false;
             ctx->begun = false;

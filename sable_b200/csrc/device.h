@@ -162,6 +162,13 @@ struct TailArgs {
     u32 seq;
     u32 *host;                         // the mapped buffer (device address)
     unsigned poll_limit;               // polls before the block gives up on a challenge
+    // own_transcript: the block derives each challenge itself, from a copy of the host transcript's hash state
+    // as it stood before this launch's first round (the host replays the same messages and checks)
+    int own_transcript;
+    int b3_fill;                       // bytes in the pending block
+    u32 b3_cv[8];                      // chaining value
+    u32 b3_pending[16];                // pending block, little-endian words
+    u64 b3_blocks;                     // blocks compressed so far
 };
 cudaError_t launch_tail(int D, int shape, int points, int nt_used, const TailArgs &args, cudaStream_t stream);
 

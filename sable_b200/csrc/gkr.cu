@@ -164,6 +164,9 @@ static int prove_parts(sc_ctx *const *ctxs, std::vector<Part> &parts, sc_transcr
     header.push_back((uint8_t)degree); header.push_back((uint8_t)(degree >> 8));
     for (int b = 0; b < 4; b++) header.push_back((uint8_t)((u32)blocks >> (8 * b)));
     if ((rc = sc_transcript_absorb(tr, header.data(), header.size()))) return rc;
+    // one part: its sums are the message, so the device may carry the transcript through the last rounds itself
+    struct Attach { sc_ctx *c; ~Attach() { if (c) sc_attach_transcript(c, nullptr); } } attach{L == 1 ? ctxs[0] : nullptr};
+    if (L == 1 && (rc = sc_attach_transcript(ctxs[0], tr))) return rc;
     u32 sums[SC_MAX_POINTS * 8], part[SC_MAX_POINTS * 8];
     for (int j = 0; j < n; j++) {
         for (int l = 0; l < L; l++) {

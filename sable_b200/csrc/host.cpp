@@ -272,6 +272,14 @@ extern "C" sc_transcript *sc_transcript_new(const uint8_t *label, size_t label_l
 }
 extern "C" void sc_transcript_free(sc_transcript *tr) { delete tr; }
 extern "C" int sc_transcript_degree(const sc_transcript *tr) { return tr ? tr->degree : 0; }
+extern "C" int sc_transcript_state(const sc_transcript *tr, uint32_t cv[8], uint32_t pending[16], int *fill, uint64_t *blocks) {
+    if (!tr || !cv || !pending || !fill || !blocks) return SC_EINVAL;
+    memcpy(cv, tr->state.cv, sizeof tr->state.cv);
+    B3S::words(tr->state.pending, pending);
+    *fill = tr->state.fill;
+    *blocks = tr->state.blocks;
+    return SC_OK;
+}
 extern "C" int sc_transcript_absorb(sc_transcript *tr, const uint8_t *data, uint64_t len) {
     if (!tr || (len && !data)) return SC_EINVAL;
     tr->absorb(data, len);
@@ -563,6 +571,9 @@ extern "C" int sc_prove(sc_ctx *ctx, sc_transcript *tr, int n, const char *state
     for (int t = 0; t < ntables; t++)
         if (tables && tables[t] && (rc = sc_upload_table(ctx, t, tables[t], ((u64)blocks << n) / (u64)world, strides[t]))) return rc;
     if ((rc = sc_begin(ctx, n, eq, blocks, block_weights))) return rc;
+    // the last rounds may derive their challenges on the device from a copy of this transcript's state
+    struct Attach { sc_ctx *c; ~Attach() { sc_attach_transcript(c, nullptr); } } attach{ctx};
+    if ((rc = sc_attach_transcript(ctx, tr))) return rc;
 
     // header: label | "|" | n u16 | degree u16 | blocks u32 (:24-27, :534)
     std::vector<u8> header(label, label + strlen(label));

@@ -7,7 +7,12 @@
 // each challenge from the host through mapped memory, so a round costs a few microseconds
 // instead of a launch and a completion.  Every wait is bounded: a block that hears nothing for
 // its limit of polls, or is told to stop, records why and returns.
+//
+// With own_transcript the block does not wait at all: it carries a copy of the transcript's hash
+// state and derives every challenge itself (SEND of its sums, CHALLENGE), posting sums and challenges
+// for the host, which replays the same steps on its transcript and checks that they agree.
 #include "round_kernel.cuh"
+#include "b3s.cuh"
 
 namespace sc {
 
@@ -16,12 +21,19 @@ __device__ __forceinline__ u32 ld_sys(const u32 *p) {
     asm volatile("ld.volatile.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
     return v;
 }
+__device__ __forceinline__ u32 timer_ns() {
+    unsigned long long t;
+    asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+    return (u32)t;
+}
 __device__ __forceinline__ void st_sys(u32 *p, u32 v) { asm volatile("st.volatile.global.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory"); }
 
 template <int D, int PTS, int NT, int SHAPE>
 __global__ void __launch_bounds__(ROUND_THREADS) tail_kernel(const __grid_constant__ TailArgs a) {
     __shared__ u32 red[ROUND_THREADS / 32][PTS * D];
     __shared__ u32 chal[8];
+    __shared__ u32 msg[PTS * D];
+    __shared__ B3State hash;
     __shared__ int go;
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     constexpr int W = PTS * D, ROWS = ROUND_THREADS / 32;
@@ -38,7 +50,13 @@ __global__ void __launch_bounds__(ROUND_THREADS) tail_kernel(const __grid_consta
     for (int c = 0; c < D; c++) r.v[c] = a.r[c];
     ExtM<D> rm = eprep<D>(r);
 
+    if (a.own_transcript && tid == 0) {
+        for (int i = 0; i < 8; i++) hash.cv[i] = a.b3_cv[i];
+        for (int i = 0; i < 16; i++) hash.pending[i] = a.b3_pending[i];
+        hash.fill = a.b3_fill; hash.blocks = a.b3_blocks;
+    }
     for (int k = 0; k < a.nrounds; k++) {
+        const u32 t_round = timer_ns();
         const TailRound rd = a.rd[k];
         const int out = k & 1;
         Ext<D> total[PTS];
@@ -151,10 +169,26 @@ __global__ void __launch_bounds__(ROUND_THREADS) tail_kernel(const __grid_consta
                 s = emul<D>(s, pf);
             }
 #pragma unroll
-            for (int c = 0; c < D; c++) slot[tid * D + c] = s.v[c];
+            for (int c = 0; c < D; c++) { slot[tid * D + c] = s.v[c]; msg[tid * D + c] = s.v[c]; }
         }
         __syncthreads();   // also: every store of the folded tables is done before the next round reads them
-        if (tid == 0) {
+        if (tid == 0 && a.own_transcript) {
+            const u32 s0 = timer_ns();
+            __threadfence_system();
+            st_sys(slot + 32, a.seq + (u32)k);
+            const u32 s1 = timer_ns();
+            // the transcript's next steps, here: SEND of the sums, then the challenge; the host replays both and compares
+            b3_absorb_words(&hash, msg, W);
+            const u32 s2 = timer_ns();
+            b3_challenge(&hash, D, chal);
+            const u32 s3 = timer_ns();
+#pragma unroll
+            for (int c = 0; c < D; c++) slot[52 + c] = chal[c];
+            slot[60] = s0 - t_round; slot[61] = s1 - s0; slot[62] = s2 - s1; slot[63] = s3 - s2;   // nanoseconds: compute, post, absorb, challenge
+            __threadfence_system();
+            st_sys(slot + 50, a.seq + (u32)k);
+            go = 1;
+        } else if (tid == 0) {
             __threadfence_system();   // cumulative: the sums written before the barrier are visible before the word below
             st_sys(slot + 32, a.seq + (u32)k);
             // wait for the challenge, a bounded number of polls

@@ -344,6 +344,46 @@ def test_download_gives_the_table_back_and_refuses_in_the_small_value_rounds(pro
     assert e.value.code == -5
 
 
+@pytest.mark.parametrize("d,n,statement,names", [
+    (4, 13, "(+ (* t0 t3) (* t1 t2) (* alpha t2 t3))", ["t0", "t1", "t2", "t3"]),
+    (8, 10, "(* t0 t1 t2)", ["t0", "t1", "t2"]),
+    (4, 9, "(+ (* 7 t0 t1) t1 -3)", ["t0", "t1"]),
+])
+def test_device_transcript_gives_the_same_proof(prover, d, n, statement, names, monkeypatch):
+    # SABLE_B200_DEVICE_TRANSCRIPT=1: the resident kernel of the last rounds hashes its own sums (BLAKE3 on the
+    # device) and derives the challenges itself; the host replays and checks.  Same bytes as the oracle.
+    monkeypatch.setenv("SABLE_B200_DEVICE_TRANSCRIPT", "1")
+    rng = np.random.default_rng(n)
+    tables = [(nm, rand_ext(rng, d, 1 << n)) for nm in names]
+    constants = [("alpha", rand_ext(rng, d).tolist())] if "alpha" in statement else []
+    for eq in (rand_ext(rng, d, n), None):
+        got, want, ta, tb = both(prover, d, n, statement, tables, eq=eq, constants=constants)
+        assert_same(got, want, ta, tb)
+
+
+def test_device_transcript_notices_a_foreign_challenge(monkeypatch):
+    monkeypatch.setenv("SABLE_B200_DEVICE_TRANSCRIPT", "1")
+    import ctypes as C
+    p = sb.Prover(0)
+    try:
+        d, n = 4, 8
+        rng = np.random.default_rng(2)
+        degree, terms = sb.lower_statement("(* a b)", d, ["a", "b"])
+        p.set_statement(d, 2, 2, terms)
+        for s in range(2):
+            p.upload_table(s, rand_ext(rng, d, 1 << n))
+        tr = sb.Transcript("own", d)
+        p._call("sc_attach_transcript", C.c_void_p(tr._h))
+        p.begin(n)
+        tr.send(p.round())
+        p.challenge(tr.challenge())
+        tr.send(p.round())                           # the resident kernel starts here, with a copy of tr's state
+        with pytest.raises(sb.SumcheckError):        # not the challenge the device derived from that state
+            p.challenge([1, 2, 3, 4])
+    finally:
+        p.close()
+
+
 def test_slow_host_falls_back_to_a_launch_per_round(monkeypatch):
     # the resident kernel of the last rounds waits a bounded time for each challenge; when the host is
     # slower than that (here: a short limit and a pause) it returns and the proof goes on, launch by launch
