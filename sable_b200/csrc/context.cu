@@ -118,6 +118,8 @@ struct sc_ctx {
     u64 eq_cap = 0, bw_cap = 0, chunks_cap = 0, weights_cap = 0;
     WeightDesc *d_descs = nullptr;
     u64 descs_cap = 0;
+    std::vector<u32> stage_eq, stage_bw;          // what sc_begin copies to the device, kept alive past the call
+    std::vector<WeightDesc> stage_descs;
     u32 *d_partials = nullptr;
     unsigned int *d_counter = nullptr;
     u32 *d_out = nullptr, *h_out = nullptr, *h_out_dev = nullptr;   // h_out: mapped pinned; h_out_dev its device alias
@@ -780,7 +782,9 @@ extern "C" int sc_begin(sc_ctx *ctx, int n, const uint32_t *eq, int K, const uin
     ctx->plan.assign(n, RoundPlan());
 
     // eq and block weights in Montgomery form
-    std::vector<u32> eqm((size_t)(n > 0 ? n : 1) * D, 0), bwm((size_t)K * D, 0);
+    // staged in the context, so that the copies below need no wait: the vectors live until the next sc_begin
+    std::vector<u32> &eqm = ctx->stage_eq, &bwm = ctx->stage_bw;
+    eqm.assign((size_t)(n > 0 ? n : 1) * D, 0); bwm.assign((size_t)K * D, 0);
     if (eq) for (size_t i = 0; i < (size_t)n * D; i++) eqm[i] = to_mont(eq[i] % P);
     if (block_weights) for (size_t i = 0; i < (size_t)K * D; i++) bwm[i] = to_mont(block_weights[i] % P);
 
@@ -806,7 +810,8 @@ extern "C" int sc_begin(sc_ctx *ctx, int n, const uint32_t *eq, int K, const uin
     }
 
     // one LOW and one HIGH table per round
-    std::vector<WeightDesc> descs;
+    std::vector<WeightDesc> &descs = ctx->stage_descs;
+    descs.clear();
     u64 words = 0, total_entries = 0;
     for (int j = 0; j < n; j++) {
         RoundPlan &pl = ctx->plan[j];
@@ -844,8 +849,6 @@ extern "C" int sc_begin(sc_ctx *ctx, int n, const uint32_t *eq, int K, const uin
         CU(launch_weight_tables(D, ctx->d_chunks, ctx->d_descs, (int)descs.size(), ctx->d_bw, ctx->d_weights, total_entries, ctx->stream));
         ctx->launches++;
     }
-    // the host vectors above must outlive the copies
-    CU(cudaStreamSynchronize(ctx->stream));
     // rounds 0 and 1 from one pass, tables bound to both challenges on the way into round 2: a product of
     // base tables, large enough for split weights, on one GPU, one block
     {

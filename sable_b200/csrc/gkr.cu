@@ -129,6 +129,7 @@ struct Part {   // one lookup's share of a sumcheck
     std::vector<std::string> names, cnames;
     std::vector<const u32 *> host, dev;   // per table: one of them is set
     std::vector<u32> cvals;
+    bool layer = false;                   // the statement is the layer statement (constants a, al): no need to parse it
 };
 
 // PROVE (src/sumcheck.lisp:512-571) of the sum of the parts' statements, part l on context l: one header,
@@ -147,8 +148,21 @@ static int prove_parts(sc_ctx *const *ctxs, std::vector<Part> &parts, sc_transcr
         int deg = 0, nterms = 0;
         std::vector<u32> coeffs((size_t)SC_MAX_TERMS * D);
         std::vector<int32_t> ptr(SC_MAX_TERMS + 1), idx((size_t)SC_MAX_TERMS * SC_MAX_FACTORS);
-        if ((rc = sc_lower_statement(pt.statement.c_str(), D, nt, tn.data(), nc, cn.data(), pt.cvals.data(), &deg, &nterms, coeffs.data(),
-                                     ptr.data(), idx.data())))
+        if (pt.layer) {
+            // the layer statement's term table written down directly (what sc_lower_statement gives for it: the terms in
+            // the order of their table lists), a p0 q1 + a p1 q0 + al q0 q1, each times bw when that is table 0
+            const int o = pt.names[0] == "bw" ? 1 : 0;
+            const int lists[3][2] = {{o + 0, o + 3}, {o + 1, o + 2}, {o + 2, o + 3}};
+            int used = 0;
+            for (int t = 0; t < 3; t++) {
+                memcpy(coeffs.data() + (size_t)t * D, pt.cvals.data() + (size_t)(t == 2 ? D : 0), 4 * (size_t)D);
+                ptr[t] = used;
+                if (o) idx[used++] = 0;
+                idx[used++] = lists[t][0]; idx[used++] = lists[t][1];
+            }
+            ptr[3] = used; nterms = 3; deg = 2 + o;
+        } else if ((rc = sc_lower_statement(pt.statement.c_str(), D, nt, tn.data(), nc, cn.data(), pt.cvals.data(), &deg, &nterms, coeffs.data(),
+                                            ptr.data(), idx.data())))
             return rc;
         if (l == 0) { if (degree < 0) degree = deg; points = degree > 1 ? degree : 1; }
         if ((rc = sc_set_statement(ctxs[l], D, points, nt, nterms, coeffs.data(), ptr.data(), idx.data()))) return rc;
@@ -322,6 +336,7 @@ extern "C" int sc_gkr_prove_upper(sc_ctx *const *ctxs, int lookups, sc_transcrip
             if (with_bw) pt.names.push_back("bw");
             for (const char *nm : tnames) pt.names.push_back(nm);
             pt.cnames = {"a", "al"};
+            pt.layer = true;
             const E a(as.begin() + (size_t)l * D, as.begin() + (size_t)(l + 1) * D), al = F.mul(a, lam);
             pt.cvals.insert(pt.cvals.end(), a.begin(), a.end());
             pt.cvals.insert(pt.cvals.end(), al.begin(), al.end());
