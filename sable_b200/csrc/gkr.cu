@@ -26,6 +26,7 @@
 #include "../../include/sumcheck_b200.h"
 #include "device.h"
 #include "field.cuh"
+#include "part_workers.h"
 
 namespace sc {
 using namespace scf;
@@ -136,7 +137,7 @@ struct Part {   // one lookup's share of a sumcheck
 // per round the sum of the parts' sums.  FINALS and FOLDED are per part, per table (blocks entries).
 static int prove_parts(sc_ctx *const *ctxs, std::vector<Part> &parts, sc_transcript *tr, int n, const u32 *eq, const char *label,
                        int blocks, const u32 *bw, int degree, std::vector<HostField::E> *challenges,
-                       std::vector<std::vector<u32>> *folded) {
+                       std::vector<std::vector<u32>> *folded, PartWorkers *workers) {
     const int D = sc_transcript_degree(tr), L = (int)parts.size();
     int points = 1, rc;
     for (int l = 0; l < L; l++) {
@@ -183,9 +184,14 @@ static int prove_parts(sc_ctx *const *ctxs, std::vector<Part> &parts, sc_transcr
     if (L == 1 && (rc = sc_attach_transcript(ctxs[0], tr))) return rc;
     u32 sums[SC_MAX_POINTS * 8], part[SC_MAX_POINTS * 8];
     for (int j = 0; j < n; j++) {
-        for (int l = 0; l < L; l++) {
-            if ((rc = sc_round(ctxs[l], l ? part : sums))) return rc;
-            if (l) for (int k = 0; k < points * D; k++) sums[k] = fadd(sums[k], part[k]);
+        if (workers) {   // every lookup's round at the same time
+            if ((rc = workers->round(sums))) return rc;
+            for (int l = 1; l < L; l++) for (int k = 0; k < points * D; k++) sums[k] = fadd(sums[k], workers->part(l)[k]);
+        } else {
+            for (int l = 0; l < L; l++) {
+                if ((rc = sc_round(ctxs[l], l ? part : sums))) return rc;
+                if (l) for (int k = 0; k < points * D; k++) sums[k] = fadd(sums[k], part[k]);
+            }
         }
         if ((rc = sc_transcript_send(tr, sums, points, D))) return rc;
         HostField::E r((size_t)D);
@@ -360,6 +366,8 @@ extern "C" int sc_gkr_prove_upper(sc_ctx *const *ctxs, int lookups, sc_transcrip
     std::vector<E> r;
     std::vector<Part> parts;
     std::vector<std::vector<u32>> folded;
+    std::unique_ptr<PartWorkers> workers;    // several lookups: their rounds run side by side
+    if (L > 1) workers.reset(new PartWorkers(std::vector<sc_ctx *>(ctxs, ctxs + L)));
     for (int j = 0; j < lk; j++) {              // the top tree
         if ((rc = layer_parts(parts, false))) return rc;
         const int h = 1 << j;
@@ -373,7 +381,7 @@ extern "C" int sc_gkr_prove_upper(sc_ctx *const *ctxs, int lookups, sc_transcrip
         const std::vector<u32> eq = flat(r);
         const std::string lab = std::string(label) + "-top";
         std::vector<E> rho;
-        if ((rc = prove_parts(ctxs, parts, tr, j, j > 0 ? eq.data() : nullptr, lab.c_str(), 1, nullptr, j > 0 ? 2 : 0, &rho, &folded))) return rc;
+        if ((rc = prove_parts(ctxs, parts, tr, j, j > 0 ? eq.data() : nullptr, lab.c_str(), 1, nullptr, j > 0 ? 2 : 0, &rho, &folded, workers.get()))) return rc;
         std::vector<std::vector<E>> finals(L, std::vector<E>(4));
         for (int l = 0; l < L; l++) for (int t = 0; t < 4; t++) finals[l][t].assign(folded[l].begin() + (size_t)t * D, folded[l].begin() + (size_t)(t + 1) * D);
         E tt;
@@ -402,7 +410,7 @@ extern "C" int sc_gkr_prove_upper(sc_ctx *const *ctxs, int lookups, sc_transcrip
         const std::vector<u32> eq = flat(ri), bwf = flat(bw);
         std::vector<E> rho;
         std::vector<Part> saved = parts;
-        if ((rc = prove_parts(ctxs, parts, tr, layer, layer > 0 ? eq.data() : nullptr, label, K, bwf.data(), layer > 0 ? 2 : 0, &rho, &folded))) return rc;
+        if ((rc = prove_parts(ctxs, parts, tr, layer, layer > 0 ? eq.data() : nullptr, label, K, bwf.data(), layer > 0 ? 2 : 0, &rho, &folded, workers.get()))) return rc;
         std::vector<std::vector<E>> finals(L, std::vector<E>(4));
         std::vector<E> rbn;
         if (lk > 0) {
@@ -428,7 +436,7 @@ extern "C" int sc_gkr_prove_upper(sc_ctx *const *ctxs, int lookups, sc_transcrip
             }
             const std::string lab = std::string(label) + "-blk";
             std::vector<std::vector<u32>> fblk;
-            if ((rc = prove_parts(ctxs, blk, tr, lk, nullptr, lab.c_str(), 1, nullptr, -1, &rbn, &fblk))) return rc;
+            if ((rc = prove_parts(ctxs, blk, tr, lk, nullptr, lab.c_str(), 1, nullptr, -1, &rbn, &fblk, workers.get()))) return rc;
             for (int l = 0; l < L; l++) for (int t = 0; t < 4; t++) finals[l][t].assign(fblk[l].begin() + (size_t)(t + 1) * D, fblk[l].begin() + (size_t)(t + 2) * D);
         } else {
             for (int l = 0; l < L; l++) for (int t = 0; t < 4; t++) finals[l][t].assign(folded[l].begin() + (size_t)t * K * D, folded[l].begin() + (size_t)t * K * D + D);

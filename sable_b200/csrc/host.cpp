@@ -17,6 +17,7 @@
 
 #include "../../include/sumcheck_b200.h"
 #include "field.cuh"
+#include "part_workers.h"
 
 using scf::u32;
 using scf::u64;
@@ -512,12 +513,12 @@ static int prove_in_parts(sc_ctx *ctx, sc_transcript *tr, int n, const std::vect
     header.push_back((u8)degree); header.push_back((u8)(degree >> 8));
     for (int b = 0; b < 4; b++) header.push_back((u8)((u32)blocks >> (8 * b)));
     tr->absorb(header.data(), header.size());
-    u32 sums[SC_MAX_POINTS * 8], part[SC_MAX_POINTS * 8], r[8];
+    u32 sums[SC_MAX_POINTS * 8], r[8];
+    sc::PartWorkers workers(on);   // the parts' rounds run side by side
     for (int j = 0; j < n; j++) {
-        for (size_t k = 0; k < parts.size(); k++) {
-            if ((rc = sc_round(on[k], k ? part : sums))) return rc;
-            if (k) for (int w = 0; w < points * D; w++) sums[w] = scf::fadd(sums[w], part[w]);
-        }
+        if ((rc = workers.round(sums))) return rc;
+        for (size_t k = 1; k < parts.size(); k++)
+            for (int w = 0; w < points * D; w++) sums[w] = scf::fadd(sums[w], workers.part(k)[w]);
         tr->send(sums, points, D);
         tr->challenge_base(D, r);
         if (challenges) memcpy(challenges + (size_t)j * D, r, 4 * (size_t)D);
