@@ -606,7 +606,12 @@ extern "C" int sc_upload_table(sc_ctx *ctx, int slot, const uint32_t *host, uint
     CU(cudaMemcpyAsync(t.t0, host, entries * (u64)stride * 4, cudaMemcpyHostToDevice, ctx->stream));
     CU(launch_reduce_words(t.t0, entries * (u64)stride, ctx->stream));   // COERCE-EXT reduces its input
     ctx->launches++;
-    CU(cudaStreamSynchronize(ctx->stream));
+    // from pinned memory the copy reads the caller's buffer until it is done; from pageable memory the copy call
+    // returns once the data has left it, and the rest is ordered on the stream
+    cudaPointerAttributes at;
+    const bool pageable = cudaPointerGetAttributes(&at, host) != cudaSuccess || at.type == cudaMemoryTypeUnregistered;
+    cudaGetLastError();
+    if (!pageable) CU(cudaStreamSynchronize(ctx->stream));
     return SC_OK;
 }
 
