@@ -78,7 +78,9 @@ int sc_set_statement(sc_ctx *ctx, int D, int points, int ntables, int nterms, co
                      const int32_t *term_ptr, const int32_t *term_tables);
 
 /* Table SLOT from host memory: ENTRIES entries of STRIDE words, stride 1 (base field) or D.
-   Stands in for MAKE-TABLE (src/sumcheck.lisp:61-70).  The host array is only read. */
+   Stands in for MAKE-TABLE (src/sumcheck.lisp:61-70).  The host array is only read, and is free
+   again when the call returns (from pinned memory the call waits for the copy; from pageable
+   memory the data has left the array by then and the rest is ordered on the context's stream). */
 int sc_upload_table(sc_ctx *ctx, int slot, const uint32_t *host, uint64_t entries, int stride);
 
 /* Table SLOT filled on the device by the seeded generator of the benchmarks:
