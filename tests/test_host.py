@@ -151,3 +151,27 @@ def test_no_device_means_an_error_not_a_fallback():
         pytest.skip("a CUDA device is present")
     with pytest.raises(sb.SumcheckError):
         sb.Prover(0)
+
+
+def test_gkr_and_helpers_reject_bad_arguments_without_a_device():
+    # argument checks come before any CUDA call: no context, no lookups, no leaves, n < 1
+    lib = sb.library()
+    tr = sb.Transcript("x", 4)
+    h = ctypes.c_void_p(tr._h)
+    assert lib.sc_gkr_prove_upper(None, 1, h, 3, 1, None, None, 0, b"gkr", None, None, None, None) == -1
+    ctxs = (ctypes.c_void_p * 1)(None)
+    ptrs = (ctypes.POINTER(ctypes.c_uint32) * 1)()
+    assert lib.sc_gkr_prove_upper(ctxs, 0, h, 3, 1, ptrs, ptrs, 0, b"gkr", None, None, None, None) == -1
+    assert lib.sc_gkr_prove_upper(ctxs, 1, h, 0, 1, ptrs, ptrs, 0, b"gkr", None, None, None, None) == -1
+    assert lib.sc_gkr_prove_upper(ctxs, 1, h, 3, 1, ptrs, ptrs, 0, b"gkr", None, None, None, None) == -1   # null context
+    out = ctypes.c_void_p()
+    assert lib.sc_borrow_table(None, 0, None, ctypes.c_uint64(4), 4) == -1
+    assert lib.sc_reserve(None, 4, 3, 1, 4) == -1
+    assert lib.sc_workspace(None, ctypes.c_uint64(16), ctypes.byref(out)) == -1
+    assert lib.sc_child(None, 0, ctypes.byref(out)) == -1
+    assert lib.sc_attach_transcript(None, h) == -1
+    assert lib.sc_transcript_degree(h) == 4
+    cv = (ctypes.c_uint32 * 8)(); pend = (ctypes.c_uint32 * 16)(); fill = ctypes.c_int(); blocks = ctypes.c_uint64()
+    assert lib.sc_transcript_state(h, cv, pend, ctypes.byref(fill), ctypes.byref(blocks)) == 0
+    assert 0 < fill.value <= 64 and blocks.value == 0          # "LLM-SUMCHECK-v6-O|x": 19 bytes pending, nothing compressed yet
+    assert bytes(pend)[:fill.value] == b"LLM-SUMCHECK-v6-O|x"
