@@ -115,27 +115,50 @@ template <int D> SCF_HD ExtM<D> eprep(const Ext<D> &b) { ExtM<D> m;
     for (int i = 0; i < D; i++) { m.v[i] = b.v[i]; m.t[i] = ftriple(b.v[i]); }
     return m; }
 
+// A running sum of products below p^2 in 64 bits: four fit from zero; then the high word loses one
+// p (the sum drops below p 2^32) and two more fit, and so on; the sum stays below 2 p 2^32, which is
+// what redc4 takes.  So a coordinate with many products needs one reduction, not one per four.
+SCF_HD u64 presub(u64 t) {
+    u32 hi = (u32)(t >> 32);
+    hi = umin32(hi, hi - P);
+    return ((u64)hi << 32) | (u32)t;
+}
 // a b in F_p[w]/(w^D - 3): c_e = sum_{i+j=e} a_i b_j + 3 sum_{i+j=e+D} a_i b_j on the power-ordered
-// coefficients, four products per reduction (mul*, src/field.lisp:220-234).  Montgomery REDC on
-// each sum: with both factors in Montgomery form so is the product.
+// coefficients (mul*, src/field.lisp:220-234, reduces once per four products; here once per
+// coordinate).  Montgomery REDC on each sum: with both factors in Montgomery form so is the product.
 template <int D> SCF_HD Ext<D> emul(const Ext<D> &a, const ExtM<D> &b) {
     Ext<D> o;
 #pragma unroll
     for (int e = 0; e < D; e++) {
-        u32 res = 0;
+        u64 acc = 0;
 #pragma unroll
-        for (int g = 0; g < D; g += 4) {
-            u64 acc = 0;
-#pragma unroll
-            for (int i = g; i < g + 4 && i < D; i++) {
-                const int j = (e - i + D) % D;
-                const u32 bj = (i > e) ? b.t[brev<D>(j)] : b.v[brev<D>(j)];
-                acc += (u64)a.v[brev<D>(i)] * bj;
-            }
-            const u32 part = (D >= 4) ? redc4(acc) : redc(acc);
-            res = (g == 0) ? part : fadd(res, part);
+        for (int i = 0; i < D; i++) {
+            if (i >= 4 && (i & 1) == 0) acc = presub(acc);
+            const int j = (e - i + D) % D;
+            const u32 bj = (i > e) ? b.t[brev<D>(j)] : b.v[brev<D>(j)];
+            acc += (u64)a.v[brev<D>(i)] * bj;
         }
-        o.v[brev<D>(e)] = res;
+        o.v[brev<D>(e)] = (D >= 4) ? redc4(acc) : redc(acc);
+    }
+    return o;
+}
+// a1 b1 + a2 b2 with one reduction per coordinate
+template <int D> SCF_HD Ext<D> emul2(const Ext<D> &a1, const ExtM<D> &b1, const Ext<D> &a2, const ExtM<D> &b2) {
+    Ext<D> o;
+#pragma unroll
+    for (int e = 0; e < D; e++) {
+        u64 acc = 0;
+#pragma unroll
+        for (int k = 0; k < 2 * D; k++) {
+            if (k >= 4 && (k & 1) == 0) acc = presub(acc);
+            const int i = k % D;
+            const int j = (e - i + D) % D;
+            const Ext<D> &a = k < D ? a1 : a2;
+            const ExtM<D> &b = k < D ? b1 : b2;
+            const u32 bj = (i > e) ? b.t[brev<D>(j)] : b.v[brev<D>(j)];
+            acc += (u64)a.v[brev<D>(i)] * bj;
+        }
+        o.v[brev<D>(e)] = redc4(acc);
     }
     return o;
 }
@@ -148,25 +171,16 @@ template <int D> SCF_HD Ext<D> emul_plus_scaled(const Ext<D> &a, const ExtM<D> &
     Ext<D> o;
 #pragma unroll
     for (int e = 0; e < D; e++) {
-        u32 res = 0;
+        u64 acc = 0;
 #pragma unroll
-        for (int g = 0; g < D; g += 4) {
-            u64 acc = 0;
-#pragma unroll
-            for (int i = g; i < g + 4 && i < D; i++) {
-                const int j = (e - i + D) % D;
-                const u32 bj = (i > e) ? b.t[brev<D>(j)] : b.v[brev<D>(j)];
-                acc += (u64)a.v[brev<D>(i)] * bj;
-            }
-            if (g == 0) {
-                u32 hi = (u32)(acc >> 32);
-                hi = umin32(hi, hi - P);
-                acc = (((u64)hi << 32) | (u32)acc) + (u64)c.v[brev<D>(e)] * s;
-            }
-            const u32 part = redc4(acc);
-            res = (g == 0) ? part : fadd(res, part);
+        for (int i = 0; i < D; i++) {
+            if (i >= 4 && (i & 1) == 0) acc = presub(acc);
+            const int j = (e - i + D) % D;
+            const u32 bj = (i > e) ? b.t[brev<D>(j)] : b.v[brev<D>(j)];
+            acc += (u64)a.v[brev<D>(i)] * bj;
         }
-        o.v[brev<D>(e)] = res;
+        acc = presub(acc) + (u64)c.v[brev<D>(e)] * s;   // after four or after two products: room for at least one more
+        o.v[brev<D>(e)] = redc4(acc);
     }
     return o;
 }

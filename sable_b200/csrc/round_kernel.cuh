@@ -144,6 +144,7 @@ __device__ __forceinline__ Ext<D> eval_gkr(const Ext<D> (&val)[4], const ExtM<D>
     }
     if (ab) u.v[0] = fadd(u.v[0], val[0].v[0]); else u = eadd<D>(u, val[0]);
     if (bb && !cb && !db) return emul_plus_scaled<D>(u, eprep<D>(val[3]), val[2], val[1].v[0]);   // u d + b c, one reduction per coordinate
+    if (!bb && !cb && !db) return emul2<D>(u, eprep<D>(val[3]), val[1], eprep<D>(val[2]));   // u d + b c, one reduction per coordinate
     Ext<D> f = db ? escale<D>(u, val[3].v[0]) : emul<D>(u, val[3]);
     Ext<D> g;
     if (bb && cb) g = lift<D>(mmul(val[1].v[0], val[2].v[0]));
