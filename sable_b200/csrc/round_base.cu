@@ -57,7 +57,8 @@ __global__ void __launch_bounds__(ROUND_THREADS, 2) round_base_kernel(const __gr
         for (int x = 0; x < PTS; x++)
 #pragma unroll
             for (int c = 0; c < D; c++) { total[g][x][c] = 0; acc[g][x][c] = 0; }
-    int pending = 0;            // products in each 64-bit sum
+    int pending = 0;            // products added to each 64-bit sum since its high word last lost a p (see presub)
+    bool dirty = false;         // the 64-bit sums hold something
     u64 cur_h = ~0ull;
     u32 inner[NG][PTS][D];      // reduced sums of the current run
     bool have_inner = false;
@@ -75,9 +76,19 @@ __global__ void __launch_bounds__(ROUND_THREADS, 2) round_base_kernel(const __gr
                 }
         have_inner = true;
         pending = 0;
+        dirty = false;
+    };
+    auto settle = [&]() {       // two more products fit after this (four fit from zero)
+#pragma unroll
+        for (int g = 0; g < NG; g++)
+#pragma unroll
+            for (int x = 0; x < PTS; x++)
+#pragma unroll
+                for (int c = 0; c < D; c++) acc[g][x][c] = presub(acc[g][x][c]);
+        pending = 0;
     };
     auto flush = [&]() {        // total += high[h] * inner  (src/sumcheck.lisp:256-257)
-        if (pending) reduce();
+        if (dirty) reduce();
         if (!have_inner) return;
         if (a.use_high) {
             Ext<D> hw = *reinterpret_cast<const Ext<D> *>(a.high + cur_h * D);
@@ -192,7 +203,8 @@ __global__ void __launch_bounds__(ROUND_THREADS, 2) round_base_kernel(const __gr
 #pragma unroll
                     for (int c = 0; c < D; c++) acc[g][x][c] += (u64)lw[c] * m[g];
             }
-            if (++pending == 4) reduce();
+            dirty = true;
+            if (++pending == 2) settle();
             }
         }
     }
