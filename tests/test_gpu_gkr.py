@@ -99,3 +99,12 @@ def test_borrowed_tables_prove_like_uploaded_ones():
         assert sb.prove(tb, n, statement, [(nm, sb.DeviceTable(d)) for nm, _ in tables], eq=eq, prover=prover) == want
     finally:
         prover.close()
+
+
+def test_one_lookup_with_the_device_transcript(monkeypatch):
+    # with one lookup the resident last rounds of every layer may derive their challenges on the device
+    monkeypatch.setenv("SABLE_B200_DEVICE_TRANSCRIPT", "1")
+    for n, k, d in ((9, 1, 4), (6, 3, 8)):
+        leaves, ta, got, tb, want = both(n, k, 1, d, 21 + n)
+        assert got == tuple(want)
+        assert ta.proof() == tb.proof()
