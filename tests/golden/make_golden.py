@@ -60,7 +60,9 @@ def unstring(x):
 
 
 def main():
-    src = sys.argv[1] if len(sys.argv) > 1 else "/root/reference/tests/vectors.sexp"
+    if len(sys.argv) != 2:
+        sys.exit("usage: make_golden.py <reference tree>/tests/vectors.sexp")
+    src = sys.argv[1]
     text = "\n".join(line for line in open(src).read().split("\n") if not line.startswith(";"))
     out = {}
     for vector in parse(text):
