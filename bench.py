@@ -42,10 +42,14 @@ CONFIGS = {
 }
 SEED = 1
 EQ_ID, CONST_ID = 255, 254
-# DRAM bytes moved per algorithmic byte by the fused round kernel, from an ncu capture of rounds 1 and 2 at
-# n = 24 (profiles/round_kernel_c4_n24_ncu.md: 1914.6 MB read + written against 2013.3 MB); traffic grows
-# in proportion to the pairs processed, so a launch's traffic is its algorithmic bytes times this.
-NCU_TRAFFIC_PER_ALGORITHMIC_BYTE = 0.951
+# DRAM bytes per algorithmic byte of the fused round kernel, from an ncu capture of the C4 workload at n = 24
+# (rounds 1 and 2: dram__bytes_read.sum equal to the tables read to 0.1 %, dram__bytes_write.sum 0.91 and 0.81 of
+# the folded tables written, the rest still in L2 when the kernel ended).  `roofline.traffic` is SCALED from
+# that capture, not measured in this run: the read ratio times the bytes read plus the round-1 write ratio
+# times the bytes written, over the launches that move more than twice the L2 (the others are left out of both
+# `traffic` and `traffic_basis`).
+NCU_READ_RATIO, NCU_WRITE_RATIO = 1.0, 0.91
+L2_BYTES = 126 << 20
 
 
 def splitmix64(x):
@@ -118,13 +122,21 @@ def measured_peak():
     return 6650.0, "fallback"
 
 
+def host_cores():
+    """The host cores this process may run on (not OMP_NUM_THREADS, which a launcher may have set to 1)."""
+    try:
+        return max(1, len(os.sched_getaffinity(0)))
+    except AttributeError:
+        return max(1, os.cpu_count() or 1)
+
+
 def cpu_port(cfg, D, n_sample, steps, warmup, threads=0):
     """The CPU oracle (a port of the reference prover) on a bounded sample of the workload: Mentries/s."""
     from oracle import pyoracle as orc
     tables = [(name, orc.generate(SEED, t, 0, 1 << n_sample, 1 if stride == 1 else D, nonzero=nz)) for t, (name, stride, nz) in enumerate(cfg["tables"])]
     eq = [seeded_ext(EQ_ID, i, D) for i in range(n_sample)]
     constants = [(c, seeded_ext(CONST_ID, i, D)) for i, c in enumerate(cfg["constants"])]
-    cores = orc.max_threads() if threads == 0 else threads
+    cores = host_cores() if threads == 0 else threads
     times = []
     for step in range(warmup + steps):
         tr = orc.Transcript("bench", D)
@@ -227,6 +239,7 @@ def main():
     ap.add_argument("--n", type=int, default=None, help="override the config's n (smaller runs)")
     ap.add_argument("--impl", default="sable", choices=("sable", "reference"))
     ap.add_argument("--cpu-n", type=int, default=24, help="n of the CPU sample")
+    ap.add_argument("--verify", action="store_true", help="one proof at the config's own n on the device and on the CPU port (all host threads): the proof bytes must be equal")
     ap.add_argument("--no-e2e", action="store_true")
     ap.add_argument("--no-cpu", action="store_true")
     ap.add_argument("--gkr", type=int, default=0, metavar="LOOKUPS", help="time LogUp-GKR PROVE-UPPER of this many lookups instead (one GPU; --n leaf bits, default 22)")
@@ -250,13 +263,18 @@ def main():
             return
         n_sample = min(n, args.cpu_n)
         value, mean, cores, _ = cpu_port(cfg, D, n_sample, max(args.steps, 1), args.warmup)
-        sample = "the same statement at n=%d (one whole proof per step), all host threads" % n_sample
+        sample = "the same statement at n=%d (one whole proof per step), %d host threads" % (n_sample, cores)
+        # the reference itself is single-threaded: one proof on one thread beside it, on a smaller sample
+        n_one = min(n_sample, 20)
+        one_value, one_mean, _, _ = cpu_port(cfg, D, n_one, 1, 0, threads=1)
         print(json.dumps({
             "impl": "reference", "metric": metric, "value": value, "unit": "Mentries/s", "n_gpus": args.gpus, "steps": args.steps,
             "warmup": args.warmup, "ms_per_step": mean * 1e3, "higher_is_better": True, "scaling": "strong", "vs_baseline": None,
             "dtype": "u32", "data": "synthetic",
             "config": {"workload": workload, "sample": sample},
-            "cpu_baseline": {"value": value, "unit": "Mentries/s", "cores": cores, "kind": "port", "sample": sample},
+            "cpu_baseline": {"value": value, "unit": "Mentries/s", "cores": cores, "kind": "port", "sample": sample,
+                             "one_thread": {"value": one_value, "unit": "Mentries/s", "cores": 1,
+                                            "sample": "one proof of the same statement at n=%d on one thread (%.2f s)" % (n_one, one_mean)}},
             "e2e": {"value": value, "unit": "Mentries/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
             "note": "the reference is Common Lisp (SBCL) and no Lisp is installed; this is the C port of its prover, pinned by the reference's own vectors",
         }))
@@ -317,6 +335,32 @@ def main():
             ms, wall = t.tolist()
         return ms, wall, prover.launches - launches0, tr, out
 
+    if args.verify:
+        # the device against the CPU port at full size, once: same seeded tables (generated on the device here, by the
+        # identical generator on the host there), same transcript, the proof bytes and the finals compared
+        t0 = time.perf_counter()
+        tr, out = one_proof(resident)
+        torch.cuda.synchronize()
+        gpu_s = time.perf_counter() - t0
+        record = {"verify": args.config, "n": n, "D": D, "n_gpus": world, "device_s": round(gpu_s, 4), "proof_bytes": len(tr.proof()),
+                  "proof_sha256": hashlib.sha256(tr.proof()).hexdigest()}
+        if rank == 0:
+            from oracle import pyoracle as orc
+            t0 = time.perf_counter()
+            tables = [(name, orc.generate(SEED, t, 0, 1 << n, 1 if stride == 1 else D, nonzero=nz)) for t, (name, stride, nz) in enumerate(cfg["tables"])]
+            gen_s = time.perf_counter() - t0
+            otr = orc.Transcript("bench", D)
+            t0 = time.perf_counter()
+            want = orc.prove(otr, n, cfg["statement"], tables, eq=eq, constants=constants, threads=host_cores())
+            record.update({"cpu_s": round(time.perf_counter() - t0, 2), "cpu_generate_s": round(gen_s, 2), "cpu_threads": host_cores(),
+                           "cpu_proof_sha256": hashlib.sha256(otr.proof()).hexdigest(),
+                           "equal": otr.proof() == tr.proof() and want[0] == out[0] and want[1] == out[1]})
+            print(json.dumps(record))
+            assert record["equal"], "the device proof differs from the CPU port's"
+        if world > 1:
+            dist.destroy_process_group()
+        return
+
     for _ in range(args.warmup):
         one_proof(resident)
     sampler = ClockSampler(local_rank)
@@ -338,9 +382,20 @@ def main():
     fused_ms = sum(s[0] for s in fused)
     achieved = fused_bytes / (fused_ms * 1e-3) / 1e9 if fused_ms > 0 else 0.0
     rounds = [{"round": j, "ms": round(s[0], 4), "GB/s": round(s[1] / (s[0] * 1e-3) / 1e9, 1)} for j, s in enumerate(stats) if s[1] >= (128 << 20) and s[0] > 0]
+    traffic = traffic_basis = None
+    if args.config == "C4" and D == 4:      # the workload the ncu capture was taken on
+        traffic = traffic_basis = 0
+        for j, st in enumerate(stats):
+            if j == 0 or st[1] < 2 * L2_BYTES:
+                continue
+            read = sum(4 * (1 if (stride == 1 and j == 1) else D) << (n_loc - j + 1) for _, stride, _ in cfg["tables"])
+            write = st[1] - read
+            traffic += int(read * NCU_READ_RATIO + write * NCU_WRITE_RATIO)
+            traffic_basis += st[1]
     roofline = {"bound": "hbm", "kernel": "round_kernel<D=%d,points,tables,fold> (rounds 1..n-1: fold by the previous challenge + round sums)" % D,
                 "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak, "peak_kind": peak_kind,
-                "traffic": int(fused_bytes * NCU_TRAFFIC_PER_ALGORITHMIC_BYTE) if args.config == "C4" and D == 4 else None,
+                "traffic": traffic, "traffic_basis": traffic_basis,
+                "traffic_note": "scaled from an ncu capture of the same kernel at n=24 (per-launch DRAM bytes over algorithmic bytes), launches above twice the L2 only; not measured in this run",
                 "launches": len(fused), "bytes_per_step": fused_bytes, "ms_per_step": fused_ms, "rounds": rounds,
                 "whole_proof_frac": algorithmic_bytes(cfg, n_loc, D) / (ms_per_step * 1e-3) / 1e9 / peak}
 
@@ -369,10 +424,15 @@ def main():
     if rank == 0 and world == 1 and not args.no_cpu:
         n_sample = min(n, args.cpu_n)
         v, mean, cores, cpu_proof = cpu_port(cfg, D, n_sample, 1, 0)
+        n_one = min(n_sample, 20)
+        v1, mean1, _, _ = cpu_port(cfg, D, n_one, 1, 0, threads=1)
         cpu = {"value": v, "unit": "Mentries/s", "cores": cores, "kind": "port",
-               "sample": "one proof of the same statement at n=%d on all host threads (%.2f s)" % (n_sample, mean)}
+               "sample": "one proof of the same statement at n=%d on %d host threads (%.2f s)" % (n_sample, cores, mean),
+               "one_thread": {"value": v1, "unit": "Mentries/s", "cores": 1,
+                              "sample": "one proof of the same statement at n=%d on one thread (%.2f s)" % (n_one, mean1)}}
         if n_sample == n:
             assert cpu_proof == proof_bytes, "the device proof differs from the CPU port's"
+            cpu["verified"] = "the device's proof bytes equal the CPU port's at n=%d" % n
 
     if rank == 0:
         print(json.dumps({

@@ -173,17 +173,22 @@ int sc_comm_info(const sc_ctx *ctx, int *rank, int *world);
    no counterpart in the reference (which allocates freely); it computes what sc_round returns
    for round 0 of a proof without eq weights: the sums of the statement (given as for
    sc_set_statement) at X = 0, 2, .., POINTS over the pairs of the caller's device-resident
-   tables (TABLES_DEV[t]: ENTRIES entries of STRIDES[t] words, canonical, below p), written as
-   POINTS * D canonical words to the device buffer SUMS_DEV.  The launch is asynchronous on STREAM
-   (a cudaStream_t, or NULL).
-   Scratch: the per-block partial sums and a block counter live in one fixed array in the
-   library's device image (256.25 KiB, held by every GPU that loads the library until exit),
-   one row of 32 words per 65 536 pairs and at most 2 048 rows, so ENTRIES may be at most 2^28
-   and POINTS * D at most 32; more is refused with an error code and a message naming the limit.  The first call on a device looks up
+   tables (TABLES_DEV[t]: ENTRIES entries of STRIDES[t] words, canonical, below p, each table
+   starting on a 16-byte boundary, as cudaMalloc and torch give them; an offset into a larger buffer
+   must keep that), written as POINTS * D canonical words to the device buffer SUMS_DEV (4-byte
+   aligned).  The launch is asynchronous on STREAM (a cudaStream_t, or NULL); the device that is
+   current when the call is made must be the stream's and the tables' device.
+   Scratch: the blocks' partial sums and a block counter live in one fixed array in the library's
+   device image (256.25 KiB: 2 048 rows of 32 words and the counter, held by every GPU that loads
+   the library until exit).  The limits that follow from it: ENTRIES at most 2^28 per table and
+   POINTS * D at most 32; more is refused with an error code and a message naming the limit,
+   and so are misaligned or null pointers -- nothing is launched then.  The first call on a device looks up
    the array's device address (cudaGetSymbolAddress), so make that first call before any stream
-   capture begins.  All calls share the array: the counter is cleared at the start of each call,
-   the rows are overwritten, and two calls that run on the GPU at the same time race -- order
-   them on one stream or with events.  Nothing is allocated or freed, on the device or by any
+   capture begins.  All calls on one device share the array: the counter is cleared at the start of
+   each call, the rows are overwritten, and two calls that run on the GPU at the same time race --
+   order them on one stream or with events.  On the host nothing is shared between calls but the
+   looked-up addresses, so calls may come from several host threads (ordering their work on the
+   GPU stays the caller's job).  Nothing is allocated or freed, on the device or by any
    library, and no context is needed.  On failure the text of the error is copied to MESSAGE
    (MESSAGE_CAP bytes, may be NULL). */
 int sc_round_sums_static(int D, int points, int ntables, const uint32_t *const *tables_dev, const int *strides,

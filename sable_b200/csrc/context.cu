@@ -81,6 +81,7 @@ struct sc_ctx {
     int device = 0;
     int sms = 148;
     int blocks_per_sm = 2;           // round-kernel blocks launched per SM (SABLE_B200_BLOCKS_PER_SM overrides)
+    bool force_generic = false;      // SABLE_B200_GENERIC at sc_create: every statement runs the term-table kernel
     cudaStream_t stream = nullptr;
     std::string last_error;
     u64 budget = 0, used = 0;
@@ -165,6 +166,7 @@ struct sc_ctx {
     bool p2p = false;
     u32 xseq = 0;
     int comm_timeout_s = 30;         // a round whose exchange has not finished after this long aborts the communicator
+    unsigned mail_polls = MAIL_POLL_LIMIT;   // polls a round kernel's last block waits for the other ranks' sums (SABLE_B200_MAIL_POLLS)
 };
 
 static int fail(sc_ctx *c, int code, const char *fmt, ...) {
@@ -285,6 +287,7 @@ extern "C" int sc_create(int device, sc_ctx **out) {
     if (e != cudaSuccess) { delete ctx; return SC_ECUDA; }
     ctx->sms = prop.multiProcessorCount;
     if (const char *env = getenv("SABLE_B200_BLOCKS_PER_SM")) { int v = atoi(env); if (v >= 1 && v <= 8) ctx->blocks_per_sm = v; }
+    ctx->force_generic = getenv("SABLE_B200_GENERIC") != nullptr;
     ctx->grid_cap = ctx->sms * 8;
     bool ok = cudaMalloc(&ctx->d_partials, (size_t)ctx->grid_cap * PARTIAL_ROW_WORDS * 4) == cudaSuccess &&
               cudaMalloc(&ctx->d_counter, 64) == cudaSuccess && cudaMemset(ctx->d_counter, 0, 64) == cudaSuccess &&
@@ -301,6 +304,7 @@ extern "C" int sc_create(int device, sc_ctx **out) {
     memset(ctx->h_sv, 0, (SV_MAX_WORDS + 32) * 4);
     if (const char *env = getenv("SABLE_B200_TAIL_BITS")) ctx->tail_bits = std::max(0, std::min(14, atoi(env)));
     if (const char *env = getenv("SABLE_B200_COMM_TIMEOUT_S")) ctx->comm_timeout_s = std::max(1, atoi(env));
+    if (const char *env = getenv("SABLE_B200_MAIL_POLLS")) ctx->mail_polls = (unsigned)std::max(1000, std::min((int)MAIL_POLL_LIMIT, atoi(env)));
     if (const char *env = getenv("SABLE_B200_TAIL_POLLS")) ctx->tail_polls = (unsigned)std::max(1000, std::min((int)TAIL_POLL_LIMIT, atoi(env)));
     *out = ctx;
     return SC_OK;
@@ -487,7 +491,7 @@ extern "C" int sc_set_statement(sc_ctx *ctx, int D, int points, int ntables, int
     for (int s = 0; s < ntables; s++) if (!placed[s]) { ctx->order[npos] = s; pos_of[s] = npos++; }
     if (!round_supported(D, points, nt_used > 0 ? nt_used : 1))
         return fail(ctx, SC_EUNSUPPORTED, "no kernel for degree %d over %d tables (degree above 4: at most 4 tables)", points, nt_used);
-    if (getenv("SABLE_B200_GENERIC")) shape = SHAPE_GENERIC;   // run every statement through the term-table kernel (for cross-checks)
+    if (ctx->force_generic) shape = SHAPE_GENERIC;   // run every statement through the term-table kernel (for cross-checks)
     ctx->shape = shape;
     ctx->D = D; ctx->points = points; ctx->ntables = ntables; ctx->nt_used = nt_used > 0 ? nt_used : 1;
     memset(&ctx->st, 0, sizeof ctx->st);
@@ -1211,7 +1215,7 @@ extern "C" int sc_round(sc_ctx *ctx, uint32_t *sums) {
     a.partials = ctx->d_partials; a.counter = ctx->d_counter;
     a.out_dev = ctx->d_out;
     a.out_host = local ? nullptr : ctx->h_out_dev;
-    bool all_base = !fold && ctx->base_groups > 0 && !getenv("SABLE_B200_GENERIC");
+    bool all_base = !fold && ctx->base_groups > 0 && !ctx->force_generic;
     for (int k = 0; k < ctx->nt_used && all_base; k++) all_base = a.src_base[k];
     // sharded rounds: the last block exchanges the sums with the other ranks itself (peer stores), unless the
     // ranks could not open each other's memory or the round runs the base-table kernel: then NCCL carries them
@@ -1219,6 +1223,7 @@ extern "C" int sc_round(sc_ctx *ctx, uint32_t *sums) {
     if (fused_exchange) {
         for (int r = 0; r < ctx->world; r++) a.mail[r] = ctx->mail[r];
         a.world = ctx->world; a.rank = ctx->rank; a.xseq = ++ctx->xseq;
+        a.mail_polls = ctx->mail_polls;
         a.out_host = ctx->h_out_dev;
     }
 
@@ -1444,7 +1449,8 @@ constexpr int STATIC_ROW_WORDS = 32;              // points * D words per row: d
 constexpr int STATIC_WORDS = STATIC_HEAD_WORDS + STATIC_ROWS * STATIC_ROW_WORDS;   // 64 + 2048 * 32 words = 256.25 KiB
 static __device__ __align__(256) u32 g_static_scratch[STATIC_WORDS];
 constexpr int STATIC_MAX_DEVICES = 64;
-u32 *g_static_ptr[STATIC_MAX_DEVICES];            // the array's device address, per device ordinal (0 = not asked yet)
+std::atomic<u32 *> g_static_ptr[STATIC_MAX_DEVICES];   // the array's device address, per device ordinal (null = not asked yet)
+std::atomic<int> g_static_sms[STATIC_MAX_DEVICES];     // the device's SM count, asked at the same time
 }  // namespace
 
 static int round_sums_static(sc_ctx *ctx, int D, int points, int ntables, const uint32_t *const *tables_dev, const int *strides,
@@ -1455,7 +1461,9 @@ extern "C" int sc_round_sums_static(int D, int points, int ntables, const uint32
                                     uint64_t entries, int nterms, const uint32_t *coeffs, const int32_t *term_ptr,
                                     const int32_t *term_tables, uint32_t *sums_dev, void *stream, char *message,
                                     size_t message_cap) {
-    static sc_ctx lowering;   // holds only the lowered statement; it never owns device memory
+    // the statement is lowered into a context of this call's own (it never owns device memory), so calls
+    // from different host threads share nothing on the host but the table of scratch addresses below
+    sc_ctx lowering;
     sc_ctx *ctx = &lowering;
     if (message && message_cap) message[0] = 0;
     const int rc = round_sums_static(ctx, D, points, ntables, tables_dev, strides, entries, nterms, coeffs, term_ptr, term_tables,
@@ -1479,19 +1487,25 @@ static int round_sums_static(sc_ctx *ctx, int D, int points, int ntables, const 
     int rc = sc_set_statement(ctx, D, points, ntables, nterms, coeffs, term_ptr, term_tables);
     if (rc) return rc;
     if (!round_supported(D, ctx->points, ctx->nt_used)) return fail(ctx, SC_EUNSUPPORTED, "no kernel for D=%d points=%d tables=%d", D, points, ctx->nt_used);
-    for (int t = 0; t < ntables; t++)
+    for (int t = 0; t < ntables; t++) {
         if (!tables_dev[t] || (strides[t] != 1 && strides[t] != D)) return fail(ctx, SC_EINVAL, "table %d: null, or stride %d not 1 or %d", t, strides[t], D);
+        // the kernel reads pairs of base entries as 8-byte words and extension entries as 16-byte words
+        if ((uintptr_t)tables_dev[t] % 16) return fail(ctx, SC_EINVAL, "table %d does not start on a 16-byte boundary", t);
+    }
+    if ((uintptr_t)sums_dev % 4) return fail(ctx, SC_EINVAL, "the sums do not start on a 4-byte boundary");
 
     // set-up, once per device: the array's name is a host-side stand-in, the kernel needs its device address
     int device = -1;
     CU(cudaGetDevice(&device));
     if (device < 0 || device >= STATIC_MAX_DEVICES) return fail(ctx, SC_EUNSUPPORTED, "device ordinal %d", device);
-    if (!g_static_ptr[device]) {
-        u32 *p = nullptr;
-        CU(cudaGetSymbolAddress((void **)&p, g_static_scratch));
-        g_static_ptr[device] = p;
+    u32 *scratch = g_static_ptr[device].load(std::memory_order_acquire);
+    int sms = g_static_sms[device].load(std::memory_order_acquire);
+    if (!scratch) {   // two threads that both find it unset both ask, and store the same answer
+        CU(cudaGetSymbolAddress((void **)&scratch, g_static_scratch));
+        CU(cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, device));
+        g_static_sms[device].store(sms, std::memory_order_release);
+        g_static_ptr[device].store(scratch, std::memory_order_release);
     }
-    u32 *scratch = g_static_ptr[device];
     cudaStream_t s = (cudaStream_t)stream;
     // the array keeps what the last call left: the counter must start at zero
     CU(cudaMemsetAsync(scratch, 0, STATIC_HEAD_WORDS * 4, s));
@@ -1503,6 +1517,8 @@ static int round_sums_static(sc_ctx *ctx, int D, int points, int ntables, const 
         a.src[k] = tables_dev[ctx->order[k]];
         a.src_base[k] = strides[ctx->order[k]] == 1;
     }
+    // a statement over five or seven tables runs the kernel for six or eight: the spare position repeats position 0
+    for (int k = ctx->nt_used; k < SC_MAX_TABLES; k++) { a.src[k] = a.src[0]; a.src_base[k] = a.src_base[0]; }
     a.npairs = npairs;
     a.st = ctx->st;
     a.use_post = ctx->st_e > 0 || ctx->use_factor;
@@ -1511,6 +1527,10 @@ static int round_sums_static(sc_ctx *ctx, int D, int points, int ntables, const 
     a.counter = scratch;
     a.partials = scratch + STATIC_HEAD_WORDS;
     a.out_dev = sums_dev;
-    CU(launch_round(D, ctx->shape, ctx->points, ctx->nt_used, false, a, (int)rows, 0, s));
+    // blocks: one per chunk of 256 pairs up to two per SM, and never more than the array has rows
+    const u64 chunks = (npairs + ROUND_THREADS - 1) / ROUND_THREADS;
+    u64 grid = std::min<u64>(chunks, (u64)2 * (u64)(sms > 0 ? sms : 148));
+    grid = std::max<u64>(1, std::min<u64>(grid, (u64)STATIC_ROWS));
+    CU(launch_round(D, ctx->shape, ctx->points, ctx->nt_used, false, a, (int)grid, 0, s));
     return SC_OK;
 }

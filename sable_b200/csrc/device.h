@@ -76,6 +76,7 @@ struct RoundArgs {
     u32 *mail[8];         // the ranks' mailboxes, mail[rank] this rank's own
     int world, rank;
     u32 xseq;
+    unsigned mail_polls;  // polls (with a short sleep each) the last block waits for the other ranks' sums
     u32 bind[4][8];       // FOLD = 2: eq(rho0 rho1, b), b < 4, Montgomery form: entry y of the bound table is sum_b bind[b] T[4y + b]
     int ngroups;
     int product;          // 1: the statement is the product of the tables (no term table needed)

@@ -3,8 +3,9 @@
 // The reference's base variant (ROUND-KERNEL-CODE with BASE, src/sumcheck.lisp:194-195,237-246):
 // line values and the statement are base-field integers and a term costs one base-times-extension
 // product by its weight.  Here that product is four (or eight) 32x32 -> 64-bit multiply-adds into
-// 64-bit sums that are reduced once per four pairs (four products below p^2 fit a 64-bit word,
-// as in REDUCED-SUM, src/field.lisp:213-218); the high weight multiplies once per run of pairs.
+// 64-bit sums that are reduced once per run of pairs under one high weight: four products below
+// p^2 fit a 64-bit word (REDUCED-SUM, src/field.lisp:213-218), and after every second pair the
+// sums' high words lose one p, which makes room for two more; the high weight multiplies once per run.
 // Terms with an extension-field coefficient keep a sum of their own and meet their coefficient
 // in the last block, so the pairs never see an extension-by-extension product.
 #include "round_kernel.cuh"

@@ -450,7 +450,7 @@ __global__ void __launch_bounds__(ROUND_THREADS, NT > 4 ? 1 : (D == 8 ? SC_MINBL
             if (tid < a.world) {
                 const volatile u32 *flag = a.mail[a.rank] + ((size_t)(a.xseq & 1) * a.world + tid) * MAIL_WORDS + MAIL_FLAG;
                 unsigned poll = 0;
-                while (*flag != a.xseq && ++poll < MAIL_POLL_LIMIT) __nanosleep(64);
+                while (*flag != a.xseq && ++poll < a.mail_polls) __nanosleep(64);
                 if (*flag != a.xseq) atomicAdd(&missing, 1);
             }
             __syncthreads();

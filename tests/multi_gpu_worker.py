@@ -27,8 +27,9 @@ CASES = [
 ]
 
 
-def lost_rank(prover, rank, out_file):
-    """Rank 1 leaves between two rounds; rank 0's next exchange must end with SC_ECOMM, not hang."""
+def lost_rank(prover, rank, out_file, withheld=False):
+    """Rank 1 leaves between two rounds (or, WITHHELD, stays but never runs its next round); rank 0's next
+    exchange must end with SC_ECOMM, not hang."""
     d, n = 4, 20
     rng = np.random.default_rng(3)
     size = (1 << n) // 2
@@ -42,6 +43,15 @@ def lost_rank(prover, rank, out_file):
     for _ in range(2):
         tr.send(prover.round())
         prover.challenge(tr.challenge())
+    if rank == 1 and withheld:
+        # alive, its mailbox still there, but no round: rank 0's kernel runs out of polls.  Leave only once rank 0
+        # has reported (it has closed its view of this rank's memory by then)
+        other = out_file.replace("out1", "out0")
+        deadline = time.time() + 90
+        while not os.path.exists(other) and time.time() < deadline:
+            time.sleep(0.05)
+        json.dump({"withheld": True}, open(out_file, "w"))
+        os._exit(0)
     if rank == 1:
         json.dump({"left": True}, open(out_file, "w"))
         os._exit(0)      # between rounds, nothing of this rank in flight
@@ -56,8 +66,10 @@ def lost_rank(prover, rank, out_file):
     tr2 = sb.Transcript("after", d)
     sb.prove(tr2, 4, "(* a b)", [("a", small[0]), ("b", small[1])], prover=prover)
     result["after"] = len(tr2.messages)
-    json.dump(result, open(out_file, "w"))
     prover.close()
+    with open(out_file + ".tmp", "w") as f:
+        json.dump(result, f)
+    os.rename(out_file + ".tmp", out_file)
 
 
 def main():
@@ -74,8 +86,8 @@ def main():
             raise SystemExit("no communicator id after 60 s")
         time.sleep(0.05)
     prover.comm_init(open(id_file, "rb").read(), rank, world)
-    if len(sys.argv) > 5 and sys.argv[5] == "lost-rank":
-        return lost_rank(prover, rank, out_file)
+    if len(sys.argv) > 5 and sys.argv[5] in ("lost-rank", "withheld-round"):
+        return lost_rank(prover, rank, out_file, withheld=sys.argv[5] == "withheld-round")
     results = []
     for d, n, statement, strides, consts, with_eq in CASES + [(4, logw, "(* t0 t1)", [1, 0], [], True)]:
         rng = np.random.default_rng(1000 + n)     # the same stream on every rank

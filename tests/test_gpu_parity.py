@@ -474,3 +474,122 @@ def test_degrees_five_to_eight(prover, d):
             got, want, ta, tb = both(prover, d, n, statement, tables, eq=rand_ext(rng, d, n), constants=constants)
             assert_same(got, want, ta, tb)
             assert ta.messages[0].shape[0] >= 5
+
+
+# ------------------------------------------------------------------ the kernels of the benchmark configs, at sizes where
+# the eq weights are split and every block sums several runs of pairs (one high weight per run)
+
+@pytest.mark.parametrize("d", [4, 8])
+@pytest.mark.parametrize("statement,names", [
+    ("(+ (* alpha t0 t1) (* 3 t1))", ["t0", "t1"]),        # base tables and an extension constant: two sums per point
+    ("(+ (* t0 t1 t2) (* 7 t1))", ["t0", "t1", "t2"]),     # the reference's own base-table statement (tests/tests.lisp:333, 377)
+])
+def test_base_table_statements_at_size(prover, d, statement, names):
+    n = 22
+    rng = np.random.default_rng(d + len(names))
+    tables = [(nm, rng.integers(0, P, size=1 << n, dtype=np.uint32)) for nm in names]
+    constants = [("alpha", rand_ext(rng, d).tolist())] if "alpha" in statement else []
+    for eq in (rand_ext(rng, d, n), None):
+        got, want, ta, tb = both(prover, d, n, statement, tables, eq=eq, constants=constants, threads=0)
+        assert_same(got, want, ta, tb)
+
+
+@pytest.mark.parametrize("d", [4, 8])
+def test_built_in_statements_through_the_term_table_kernel(d, monkeypatch):
+    # reference tests/tests.lisp:348-372 (compiled kernel = generic loop): with SABLE_B200_GENERIC every statement
+    # runs the term-table interpreter instead of its built-in kernel, and the proof is still the oracle's
+    monkeypatch.setenv("SABLE_B200_GENERIC", "1")
+    p = sb.Prover(0)
+    try:
+        n = 21
+        rng = np.random.default_rng(210 + d)
+        base = lambda: rng.integers(0, P, size=1 << n, dtype=np.uint32)
+        cases = [("(* t0 t1 t2)", [("t0", base()), ("t1", base()), ("t2", base())], []),
+                 ("(* t0 t1)", [("t0", rand_ext(rng, d, 1 << n)), ("t1", base())], []),
+                 ("(+ (* t0 t3) (* t1 t2) (* lam t2 t3))", [("t0", base()), ("t1", base()), ("t2", rand_ext(rng, d, 1 << n)), ("t3", rand_ext(rng, d, 1 << n))],
+                  [("lam", rand_ext(rng, d).tolist())])]
+        for statement, tables, constants in cases:
+            got, want, ta, tb = both(p, d, n, statement, tables, eq=rand_ext(rng, d, n), constants=constants, threads=0)
+            assert_same(got, want, ta, tb)
+    finally:
+        p.close()
+
+
+# ------------------------------------------------------------------ boundary values
+#
+# The kernels add products in 64-bit words and reduce late: four products below p^2 fit, then the high word
+# loses one p and two more fit, and so on.  Random inputs never put p - 1 into every operand at once; these do.
+
+def fill(pattern, shape):
+    a = np.zeros(shape, dtype=np.uint32)
+    if pattern == "max":
+        a[...] = P - 1
+    elif pattern == "alt":          # 0, p-1, 0, p-1 ... along the entries
+        a[1::2] = P - 1
+    elif pattern == "alt2":         # p-1, 0, p-1, 0 ...
+        a[0::2] = P - 1
+    return a
+
+
+BOUNDARY_STATEMENTS = [
+    # statement, table kinds (1 base, 0 extension), constants: one case per kernel family
+    ("(* t0 t1 t2)", [1, 1, 1], []),                                    # base-table kernel / small-value pass / two-challenge bind
+    ("(+ (* alpha t0 t1) (* 3 t1))", [1, 1], ["alpha"]),                # base-table kernel with an extension coefficient
+    ("(+ (* t0 t3) (* t1 t2) (* lam t2 t3))", [1, 1, 0, 0], ["lam"]),   # the layer statement's kernel
+    ("(* t0 t1 t2)", [0, 0, 0], []),                                    # product kernel on extension tables
+    ("(+ (* t0 t1 t2) (* 7 t1) -1)", [0, 1, 0], []),                    # term-table kernel
+    ("(* t0 t1 t2 t3)", [1, 0, 1, 0], []),                              # four points, mixed
+]
+
+
+@pytest.mark.parametrize("d", [4, 8])
+@pytest.mark.parametrize("pattern", ["max", "zero", "alt", "alt2"])
+def test_boundary_values_small(prover, d, pattern):
+    n = 13
+    for statement, kinds, cnames in BOUNDARY_STATEMENTS:
+        tables = [("t%d" % t, fill(pattern, (1 << n,) if k else (1 << n, d))) for t, k in enumerate(kinds)]
+        constants = [(c, fill("max", d).tolist()) for c in cnames]
+        for eq in (fill("max", (n, d)), fill(pattern, (n, d)), None):
+            got, want, ta, tb = both(prover, d, n, statement, tables, eq=eq, constants=constants)
+            try:
+                assert_same(got, want, ta, tb)
+            except AssertionError as e:
+                raise AssertionError("%s D=%d %s: %s" % (statement, d, pattern, e))
+
+
+@pytest.mark.parametrize("d", [4, 8])
+def test_boundary_values_at_size(prover, d):
+    # every operand p - 1 (and the alternating pattern) where the weights are split and the runs are long
+    n = 22
+    for statement, kinds, cnames in BOUNDARY_STATEMENTS[:4]:
+        for pattern in ("max", "alt"):
+            tables = [("t%d" % t, fill(pattern, (1 << n,) if k else (1 << n, d))) for t, k in enumerate(kinds)]
+            constants = [(c, fill("max", d).tolist()) for c in cnames]
+            got, want, ta, tb = both(prover, d, n, statement, tables, eq=fill("max", (n, d)), constants=constants, threads=0)
+            try:
+                assert_same(got, want, ta, tb)
+            except AssertionError as e:
+                raise AssertionError("%s D=%d %s: %s" % (statement, d, pattern, e))
+
+
+@pytest.mark.parametrize("d", [4, 8])
+def test_boundary_values_with_block_weights(prover, d):
+    K, n = 3, 6
+    tables = [("a", fill("max", (K << n, d))), ("b", fill("max", K << n)), ("c", fill("alt", (K << n, d)))]
+    got, want, ta, tb = both(prover, d, n, "(+ (* a b) (* lam b c))", tables, eq=fill("max", (n, d)),
+                             constants=[("lam", fill("max", d).tolist())], block_weights=fill("max", (K, d)), label="gkr")
+    assert_same(got, want, ta, tb)
+
+
+# ------------------------------------------------------------------ the seeded generator of the benchmarks
+
+@pytest.mark.parametrize("stride,nonzero,first", [(1, False, 0), (4, True, 0), (8, False, 12345), (1, True, (1 << 40) + 7), (4, False, 1 << 33)])
+def test_generated_tables_are_the_oracle_generator_s(prover, stride, nonzero, first):
+    import torch
+    entries = 1 << 16
+    prover.generate_table(0, 1, 3, entries, stride, first=first, nonzero=nonzero)
+    back = torch.empty(entries * stride, dtype=torch.int32)
+    prover.fetch_pointer(0, back.data_ptr(), entries * stride)
+    want = orc.generate(1, 3, first, entries, stride, nonzero=nonzero)
+    assert (back.numpy().view(np.uint32) == want.reshape(-1)).all()
+    assert (want < P).all()
