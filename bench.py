@@ -165,6 +165,8 @@ def gkr_bench(args):
         q[:, 0] |= 1
         leaves.append((p.contiguous(), q.contiguous()))
     provers = [sb.Prover(0) for _ in range(L)]
+    for p in provers:
+        p.set_device_transcript(args.transcript == "device")
 
     def run(lv):
         tr = sb.Transcript("bench", D)
@@ -240,8 +242,11 @@ def main():
     ap.add_argument("--impl", default="sable", choices=("sable", "reference"))
     ap.add_argument("--cpu-n", type=int, default=24, help="n of the CPU sample")
     ap.add_argument("--verify", action="store_true", help="one proof at the config's own n on the device and on the CPU port (all host threads): the proof bytes must be equal")
+    ap.add_argument("--transcript", default="host", choices=("host", "device"),
+                    help="device: the round kernels carry the BLAKE3 transcript on themselves and every round is enqueued at once (an option of the library; the default is the reference's host transcript)")
     ap.add_argument("--no-e2e", action="store_true")
     ap.add_argument("--no-cpu", action="store_true")
+    ap.add_argument("--no-device-transcript", action="store_true", help="skip the second figure with the transcript on the device")
     ap.add_argument("--gkr", type=int, default=0, metavar="LOOKUPS", help="time LogUp-GKR PROVE-UPPER of this many lookups instead (one GPU; --n leaf bits, default 22)")
     ap.add_argument("--blocks", type=int, default=1, help="K of --gkr")
     args = ap.parse_args()
@@ -292,6 +297,7 @@ def main():
     logw = world.bit_length() - 1
     n_loc = n - logw
     prover = sb.Prover(local_rank)
+    prover.set_device_transcript(args.transcript == "device")
     if world > 1:
         ids = [sb.comm_unique_id() if rank == 0 else None]
         dist.broadcast_object_list(ids, src=0)
@@ -371,6 +377,18 @@ def main():
     value = (1 << n) / (ms_per_step * 1e-3) / 1e6
     proof_bytes = tr.proof()
 
+    # the same proofs with the transcript carried on the device (the library's option), as a second figure
+    other = None
+    if args.transcript == "host" and not args.no_device_transcript:
+        prover.set_device_transcript(True)
+        for _ in range(min(args.warmup, 3)):
+            one_proof(resident)
+        oms, _, olaunches, otr, oout = timed(resident, args.steps)
+        prover.set_device_transcript(False)
+        other = {"transcript": "device (the last block of each round kernel hashes and draws the challenge; all rounds enqueued at once)",
+                 "value": (1 << n) / (oms / args.steps * 1e-3) / 1e6, "unit": "Mentries/s", "ms_per_step": oms / args.steps,
+                 "gpu_launches": olaunches, "same_proof": otr.proof() == proof_bytes and oout == out}
+
     # the round kernels, one by one (a separate pass: the events cost a little)
     prover.enable_timing(True)
     one_proof(resident)
@@ -439,9 +457,11 @@ def main():
             "metric": metric, "value": value, "unit": "Mentries/s", "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
             "ms_per_step": ms_per_step, "wall_ms_per_step": wall / args.steps, "higher_is_better": True, "scaling": "strong",
             "vs_baseline": None, "dtype": "u32", "data": "synthetic",
-            "config": {"workload": workload, "sharding": "top %d variables over %d GPUs" % (logw, world), "transcript": "host (BLAKE3)",
+            "config": {"workload": workload, "sharding": "top %d variables over %d GPUs" % (logw, world),
+                       "transcript": "host (BLAKE3)" if args.transcript == "host" else "device (BLAKE3 in the round kernels' last block)",
                        "l2": "inputs larger than L2 (%.1f GiB per rank per proof)" % (sum(4 * (strides[s] << n_loc) for s in range(len(strides))) / 2 ** 30)},
             "e2e": e2e, "gpu_launches": launches, "clocks": clocks, "roofline": roofline, "cpu_baseline": cpu,
+            "transcript_on_device": other,
             "proof_bytes": len(proof_bytes), "proof_sha256": hashlib.sha256(proof_bytes).hexdigest(),
         }))
     if world > 1:

@@ -220,16 +220,31 @@ uint64_t sc_transcript_encode(const sc_transcript *tr, const char magic[8], uint
 /* The hash state of the transcript (B3S: chaining value, pending block as little-endian words,
    bytes pending, blocks compressed), for a device that carries the transcript on. */
 int sc_transcript_state(const sc_transcript *tr, uint32_t cv[8], uint32_t pending[16], int *fill, uint64_t *blocks);
-/* TR (or NULL) is the host transcript of the proof that follows on CTX.  With it the resident kernel
-   of the last rounds copies the transcript's hash state when it starts and derives each challenge
-   itself (SEND of its sums, CHALLENGE-BASE) instead of waiting for the host.  The caller keeps
-   sending the sums sc_round returns and drawing the challenges as before; sc_challenge then checks
-   that the caller's challenge is the device's and returns SC_ESTATE if not (the transcript was
-   used for something else in between).  sc_prove attaches its transcript for the length of the
-   call.  Only with SABLE_B200_DEVICE_TRANSCRIPT=1 in the environment: one GPU thread hashes a
-   round in about 5 us, the host answers in about 4.5.  No reference counterpart: the reference's
-   transcript is host code throughout. */
+/* For tests: the transcript code the device runs (one round: SEND of ROWS x COLS values, then CHALLENGE of TR's
+   degree), executed on the host from TR's present state without changing TR.  STATE_OUT gets 32 words: chaining
+   value, pending block, bytes pending, blocks compressed (low, high); CHALLENGE gets the degree's words. */
+int sc_transcript_device_round(const sc_transcript *tr, const uint32_t *values, int rows, int cols, uint32_t *state_out,
+                               uint32_t *challenge);
+/* The transcript on the device (an option; the default keeps it on the host, as the reference does).  Per round
+   the host's part is SEND of the sums and CHALLENGE (src/transcript.lisp:116-176): a launch, a wait and a hash
+   per round, which is all a small round costs.  With sc_set_device_transcript(CTX, 1) -- or
+   SABLE_B200_DEVICE_TRANSCRIPT=1 in the environment when the context is made -- and the proof's transcript
+   attached, the first sc_round of a proof enqueues EVERY round at once: the last block of each round kernel
+   sends its sums and draws the challenge itself (sequential BLAKE3 on the device, from a copy of the
+   transcript's hash state), and the next launch folds by the challenge it finds in device memory.  The caller's
+   loop stays as it is: sc_round returns each round's sums as they are posted, the caller sends them and draws
+   the challenge on its own transcript, and sc_challenge checks that it is the device's (SC_ESTATE if not: the
+   transcript was used for something else in between).  The proof bytes are the same.  With several GPUs every
+   rank hashes the same summed words, so nothing more crosses NVLink.  The small-value first rounds of a product
+   of base tables stay with the host; the chain starts after them.
+   sc_attach_transcript: TR (or NULL) is the host transcript of the proofs that follow on CTX; sc_prove attaches
+   its own for the length of the call.  sc_attach_transcript_state: the same for a transcript that is not the
+   library's own, such as the Lisp one: its B3S state -- chaining value, pending block as little-endian words, bytes
+   pending, blocks compressed -- as it stands when the next sc_round is called; used by that call if it starts
+   a chain, forgotten otherwise.  No reference counterpart: the reference's transcript is host code throughout. */
 int sc_attach_transcript(sc_ctx *ctx, const sc_transcript *tr);
+int sc_attach_transcript_state(sc_ctx *ctx, const uint32_t cv[8], const uint32_t pending[16], int fill, uint64_t blocks);
+int sc_set_device_transcript(sc_ctx *ctx, int on);
 
 /* EXPAND + the lowering to a term table (src/forms.lisp:57-78; STATEMENT-DEGREE,
    src/sumcheck.lisp:33-35).  STATEMENT is the form as text, e.g. "(+ (* alpha t0 t1) (* 3 t1))".

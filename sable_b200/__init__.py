@@ -32,6 +32,7 @@ SYMBOLS = [
     "sc_transcript_challenge_base", "sc_transcript_challenge_bits", "sc_transcript_digest",
     "sc_transcript_message_count", "sc_transcript_message", "sc_transcript_sent_bytes", "sc_transcript_encode",
     "sc_lower_statement", "sc_prove", "sc_borrow_table", "sc_transcript_degree", "sc_gkr_prove_upper", "sc_reserve", "sc_workspace", "sc_child", "sc_attach_transcript", "sc_transcript_state",
+    "sc_transcript_device_round", "sc_attach_transcript_state", "sc_set_device_transcript",
 ]
 
 
@@ -296,6 +297,14 @@ class Prover:
     @property
     def launches(self):
         return int(library().sc_launch_count(self._h))
+
+    def set_device_transcript(self, on=True):
+        """Carry the transcript on the device: every round of a proof is enqueued at once (sc_set_device_transcript)."""
+        self._call("sc_set_device_transcript", 1 if on else 0)
+
+    def attach_transcript(self, tr):
+        """The host transcript of the proofs that follow (or None); needed by the device transcript."""
+        self._call("sc_attach_transcript", C.c_void_p(tr._h) if tr is not None else None)
 
     def comm_init(self, unique_id, rank, world):
         self._call("sc_comm_init", unique_id, rank, world)

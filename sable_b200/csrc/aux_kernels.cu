@@ -119,7 +119,7 @@ cudaError_t launch_weight_tables(int D, const u32 *chunks, const WeightDesc *des
 template <int D> __global__ void fold_kernel(const __grid_constant__ FoldArgs a) {
     Ext<D> r;
 #pragma unroll
-    for (int c = 0; c < D; c++) r.v[c] = a.r[c];
+    for (int c = 0; c < D; c++) r.v[c] = a.r_dev ? a.r_dev[c] : a.r[c];
     const ExtM<D> rm = eprep<D>(r);
     for (u64 i = (u64)blockIdx.x * blockDim.x + threadIdx.x; i < a.nout; i += (u64)gridDim.x * blockDim.x) {
         for (int t = 0; t < a.ntables; t++) {

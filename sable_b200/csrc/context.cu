@@ -143,8 +143,21 @@ struct sc_ctx {
     unsigned tail_polls = TAIL_POLL_LIMIT;
     u64 tail_entries = 0;            // entries of the tables the first round of the launch read
     int tail_buf0[SC_MAX_TABLES];    // per slot: which of the table's two buffers the first round wrote
-    const sc_transcript *attached = nullptr;   // the host transcript the resident kernel may copy its hash state from
+    const sc_transcript *attached = nullptr;   // the host transcript a chain copies its hash state from
     bool tail_own = false;           // the running resident kernel derives its challenges itself
+
+    // the transcript on the device: every round of a proof enqueued at once, each launch's last block sending its
+    // sums and drawing the challenge the next launch folds by (see RoundArgs::tstate)
+    bool device_transcript = false;  // SABLE_B200_DEVICE_TRANSCRIPT=1 at sc_create, or sc_set_device_transcript
+    u32 *d_tstate = nullptr;         // the hash state between launches, B3_STATE_WORDS words
+    u32 *d_chal = nullptr;           // per round 16 words: the challenge in Montgomery form, then canonical
+    u32 *h_chain = nullptr, *h_chain_dev = nullptr;   // mapped host memory: per round CHAIN_SLOT_WORDS words
+    bool chain_active = false;
+    int chain_first = 0;             // the first round of the chain
+    int chain_end = 0;               // the first round not run by a round kernel of the chain: the resident kernel's first, or n
+    u32 chain_seq = 0;               // round j of the chain posts chain_seq + j
+    bool have_state = false;         // a hash state handed over by sc_attach_transcript_state, not used yet
+    u32 state0[B3_STATE_WORDS];
 
     // the first two rounds from one pass over base tables (see SvArgs)
     bool sv_ok = false;
@@ -168,6 +181,8 @@ struct sc_ctx {
     int comm_timeout_s = 30;         // a round whose exchange has not finished after this long aborts the communicator
     unsigned mail_polls = MAIL_POLL_LIMIT;   // polls a round kernel's last block waits for the other ranks' sums (SABLE_B200_MAIL_POLLS)
 };
+
+constexpr int CHAIN_MAX_ROUNDS = 64;
 
 static int fail(sc_ctx *c, int code, const char *fmt, ...) {
     char buf[512];
@@ -211,6 +226,7 @@ template <class T> static int ensure(sc_ctx *ctx, T **p, u64 *cap, u64 bytes) {
 
 // Make the resident kernel of the last rounds return (it polls this word), and wait for it.
 static void tail_stop(sc_ctx *ctx) {
+    ctx->chain_active = false;   // a chain's launches wait for nobody: whatever follows on the stream comes after them
     if (!ctx->tail_active) return;
     *(volatile u32 *)(ctx->h_tail + TAIL_STOP) = ctx->tail_seq;
     std::atomic_thread_fence(std::memory_order_seq_cst);
@@ -302,6 +318,12 @@ extern "C" int sc_create(int device, sc_ctx **out) {
     if (cudaHostAlloc(&ctx->h_sv, (SV_MAX_WORDS + 32) * 4, cudaHostAllocMapped) != cudaSuccess ||
         cudaHostGetDevicePointer(&ctx->h_sv_dev, ctx->h_sv, 0) != cudaSuccess) { cudaGetLastError(); sc_destroy(ctx); return SC_ECUDA; }
     memset(ctx->h_sv, 0, (SV_MAX_WORDS + 32) * 4);
+    if (cudaMalloc(&ctx->d_tstate, B3_STATE_WORDS * 4) != cudaSuccess || cudaMemset(ctx->d_tstate, 0, B3_STATE_WORDS * 4) != cudaSuccess ||
+        cudaMalloc(&ctx->d_chal, (size_t)CHAIN_MAX_ROUNDS * 16 * 4) != cudaSuccess ||
+        cudaHostAlloc(&ctx->h_chain, (size_t)CHAIN_MAX_ROUNDS * CHAIN_SLOT_WORDS * 4, cudaHostAllocMapped) != cudaSuccess ||
+        cudaHostGetDevicePointer(&ctx->h_chain_dev, ctx->h_chain, 0) != cudaSuccess) { cudaGetLastError(); sc_destroy(ctx); return SC_ECUDA; }
+    memset(ctx->h_chain, 0, (size_t)CHAIN_MAX_ROUNDS * CHAIN_SLOT_WORDS * 4);
+    if (const char *env = getenv("SABLE_B200_DEVICE_TRANSCRIPT")) ctx->device_transcript = env[0] == '1';
     if (const char *env = getenv("SABLE_B200_TAIL_BITS")) ctx->tail_bits = std::max(0, std::min(14, atoi(env)));
     if (const char *env = getenv("SABLE_B200_COMM_TIMEOUT_S")) ctx->comm_timeout_s = std::max(1, atoi(env));
     if (const char *env = getenv("SABLE_B200_MAIL_POLLS")) ctx->mail_polls = (unsigned)std::max(1000, std::min((int)MAIL_POLL_LIMIT, atoi(env)));
@@ -319,6 +341,8 @@ extern "C" int sc_destroy(sc_ctx *ctx) {
     if (ctx->stream) cudaStreamSynchronize(ctx->stream);
     if (ctx->h_tail) cudaFreeHost(ctx->h_tail);
     if (ctx->h_sv) cudaFreeHost(ctx->h_sv);
+    if (ctx->h_chain) cudaFreeHost(ctx->h_chain);
+    cudaFree(ctx->d_tstate); cudaFree(ctx->d_chal);
     for (int r = 0; r < 8; r++) {
         if (!ctx->mail[r]) continue;
         if (r == ctx->rank || ctx->world == 1) cudaFree(ctx->mail[r]); else cudaIpcCloseMemHandle(ctx->mail[r]);
@@ -671,7 +695,7 @@ extern "C" int sc_download_table(sc_ctx *ctx, int slot, uint32_t *host, uint64_t
     if (!ctx || slot < 0 || slot >= SC_MAX_TABLES || !ctx->D) return SC_EINVAL;
     TableState &t = ctx->tab[slot];
     if (!t.t0) return fail(ctx, SC_ESTATE, "table %d was never uploaded", slot);
-    if (ctx->tail_active) return fail(ctx, SC_ESTATE, "the last rounds are running on the device: the folded tables are not available");
+    if (ctx->tail_active || ctx->chain_active) return fail(ctx, SC_ESTATE, "the rounds are running on the device: the folded tables are not available");
     if (ctx->begun && ctx->sv_ok && (ctx->j == 1 || ctx->j == 2))
         return fail(ctx, SC_ESTATE, "the first two rounds ran from one pass over the tables: nothing is folded before round 2");
     cudaSetDevice(ctx->device);
@@ -703,6 +727,39 @@ extern "C" int sc_attach_transcript(sc_ctx *ctx, const sc_transcript *tr) {
     if (!ctx) return SC_EINVAL;
     ctx->attached = tr;
     return SC_OK;
+}
+// The same for a caller whose transcript is not an sc_transcript (a Lisp one): the hash state as it stands when the
+// next sc_round is called.  It is used by that call, if it starts a chain, and forgotten either way.
+extern "C" int sc_attach_transcript_state(sc_ctx *ctx, const uint32_t cv[8], const uint32_t pending[16], int fill, uint64_t blocks) {
+    if (!ctx || !cv || !pending || fill < 0 || fill > 64) return SC_EINVAL;
+    memset(ctx->state0, 0, sizeof ctx->state0);
+    memcpy(ctx->state0, cv, 32);
+    memcpy(ctx->state0 + 8, pending, 64);
+    for (int b = fill; b < 64; b++) reinterpret_cast<unsigned char *>(ctx->state0 + 8)[b] = 0;
+    ctx->state0[24] = (u32)fill; ctx->state0[25] = (u32)blocks; ctx->state0[26] = (u32)(blocks >> 32);
+    ctx->have_state = true;
+    return SC_OK;
+}
+extern "C" int sc_set_device_transcript(sc_ctx *ctx, int on) {
+    if (!ctx) return SC_EINVAL;
+    tail_stop(ctx);
+    ctx->device_transcript = on != 0;
+    return SC_OK;
+}
+// The transcript's hash state of this moment, for a chain that starts now; false without a transcript of the proof's degree.
+static bool transcript_state_now(sc_ctx *ctx, u32 *state) {
+    if (ctx->attached) {
+        uint32_t cv[8], pending[16];
+        int fill = 0;
+        uint64_t blocks = 0;
+        if (sc_transcript_state(ctx->attached, cv, pending, &fill, &blocks) != SC_OK || sc_transcript_degree(ctx->attached) != ctx->D) return false;
+        memset(state, 0, B3_STATE_WORDS * 4);
+        memcpy(state, cv, sizeof cv); memcpy(state + 8, pending, sizeof pending);
+        state[24] = (u32)fill; state[25] = (u32)blocks; state[26] = (u32)(blocks >> 32);
+        return true;
+    }
+    if (ctx->have_state) { memcpy(state, ctx->state0, B3_STATE_WORDS * 4); return true; }
+    return false;
 }
 
 // Child INDEX of the context: a context of its own on the same device, made on first use and destroyed
@@ -880,7 +937,7 @@ static void challenge_words(const sc_ctx *ctx, u32 *out) {
 
 // Fold every table by the pending challenge with the stand-alone kernel (the last fold, and the
 // fold before the gather).
-static int fold_all(sc_ctx *ctx) {
+static int fold_all(sc_ctx *ctx, const u32 *r_dev = nullptr) {
     const int D = ctx->D;
     FoldArgs a;
     memset(&a, 0, sizeof a);
@@ -888,7 +945,7 @@ static int fold_all(sc_ctx *ctx) {
     if (!a.ntables) return SC_OK;
     const TableState &t0 = ctx->tab[0];
     a.nout = t0.cur_entries / 2;
-    challenge_words(ctx, a.r);
+    if (r_dev) a.r_dev = r_dev; else challenge_words(ctx, a.r);
     for (int s = 0; s < ctx->ntables; s++) {
         TableState &t = ctx->tab[s];
         const int nb = t.cur_buf == 0 ? 1 : 0;
@@ -1039,15 +1096,17 @@ static int sv_round1(sc_ctx *ctx, uint32_t *sums) {
 }
 
 // The last rounds run in one resident launch when the tables are small, there is one block of
-// weights, and nobody asked for per-round timing.
-static bool tail_wanted(const sc_ctx *ctx) {
+// weights, and nobody asked for per-round timing.  J: the round that would be its first.
+static bool tail_wanted(const sc_ctx *ctx, int j) {
     if (ctx->tail_bits <= 0 || ctx->K != 1 || ctx->timing || ctx->ntables < 1 || ctx->nt_used > 4 || ctx->points > FAST_POINTS) return false;
-    if (ctx->n - ctx->j > TAIL_MAX_ROUNDS) return false;
+    if (ctx->n - j > TAIL_MAX_ROUNDS) return false;
     return ctx->tab[ctx->order[0]].cur_entries <= (1ull << ctx->tail_bits);
 }
 
-static int tail_start(sc_ctx *ctx) {
-    const int D = ctx->D, j = ctx->j;
+// Launch the resident kernel for the rounds J .. n-1.  CHAIN: it carries the transcript on itself, from STATE0 (the
+// host transcript's state, when it is the chain's first launch) or from the state the launch before it left.
+static int tail_start(sc_ctx *ctx, int j, bool chain, bool chain_first, const u32 *state0) {
+    const int D = ctx->D;
     TailArgs a;
     memset(&a, 0, sizeof a);
     a.ntables = ctx->ntables;
@@ -1073,7 +1132,8 @@ static int tail_start(sc_ctx *ctx) {
         a.rd[k].high_word = pl.high_word;
         a.rd[k].use_high = pl.use_high;
     }
-    challenge_words(ctx, a.r);
+    if (chain && !chain_first) a.r_dev = ctx->d_chal + (size_t)(j - 1) * 16;
+    else challenge_words(ctx, a.r);
     a.weights = ctx->d_weights;
     a.st = ctx->st;
     a.use_post = ctx->st_e > 0 || ctx->use_factor;
@@ -1083,22 +1143,11 @@ static int tail_start(sc_ctx *ctx) {
     a.seq = ctx->tail_seq;
     a.host = ctx->h_tail_dev;
     a.poll_limit = ctx->tail_polls;
-    {   // with a transcript attached the block derives the challenges itself: it starts from the host's hash state
-        // of this moment, which is the state before this round's sums are sent
-        const char *env = getenv("SABLE_B200_DEVICE_TRANSCRIPT");   // off unless asked for: measured slower than the host's answer
-        const bool on = env && env[0] == '1';
-        ctx->tail_own = false;
-        if (ctx->attached && on) {
-            uint32_t cv[8], pending[16];
-            int fill = 0;
-            uint64_t blocks = 0;
-            if (sc_transcript_state(ctx->attached, cv, pending, &fill, &blocks) == SC_OK && sc_transcript_degree(ctx->attached) == D) {
-                a.own_transcript = 1;
-                memcpy(a.b3_cv, cv, sizeof cv); memcpy(a.b3_pending, pending, sizeof pending);
-                a.b3_fill = fill; a.b3_blocks = blocks;
-                ctx->tail_own = true;
-            }
-        }
+    ctx->tail_own = chain;
+    if (chain) {
+        a.own_transcript = 1;
+        if (chain_first) memcpy(a.tstate0, state0, sizeof a.tstate0);
+        else a.tstate = ctx->d_tstate;
     }
     ((volatile u32 *)ctx->h_tail)[TAIL_STATUS] = 0;
     std::atomic_thread_fence(std::memory_order_seq_cst);
@@ -1107,7 +1156,6 @@ static int tail_start(sc_ctx *ctx) {
     ctx->tail_active = true;
     ctx->tail_first = j;
     ctx->tail_rounds = a.nrounds;
-    ctx->have_r = false;
     return SC_OK;
 }
 
@@ -1131,8 +1179,9 @@ static int tail_round(sc_ctx *ctx, uint32_t *sums) {
     const int k = ctx->j - ctx->tail_first;
     const u32 *slot = ctx->h_tail + (size_t)k * TAIL_SLOT_WORDS;
     if (!wait_word(ctx, slot + 32, ctx->tail_seq + (u32)k)) {
-        if (tail_recover(ctx, k)) return sc_round(ctx, sums);
+        if (!ctx->tail_own && tail_recover(ctx, k)) return sc_round(ctx, sums);
         ctx->tail_active = false;
+        ctx->chain_active = false;
         ctx->begun = false;
         return fail(ctx, SC_ESTATE, "the device stopped waiting for a challenge (status %u)", ctx->h_tail[TAIL_STATUS]);
     }
@@ -1142,33 +1191,24 @@ static int tail_round(sc_ctx *ctx, uint32_t *sums) {
     return SC_OK;
 }
 
-extern "C" int sc_round(sc_ctx *ctx, uint32_t *sums) {
-    if (!ctx || !sums) return SC_EINVAL;
-    if (!ctx->begun) return fail(ctx, SC_ESTATE, "sc_round before sc_begin");
-    if (ctx->j >= ctx->n) return fail(ctx, SC_ESTATE, "all %d rounds are done", ctx->n);
-    if (ctx->j > 0 && !ctx->have_r) return fail(ctx, SC_ESTATE, "round %d needs the challenge of round %d", ctx->j, ctx->j - 1);
-    static const bool trace = getenv("SABLE_B200_TRACE") != nullptr;
-    const auto tr0 = std::chrono::steady_clock::now();
-    cudaSetDevice(ctx->device);
-    const int D = ctx->D, j = ctx->j, W = ctx->points * D;
-    if (ctx->tail_active) return tail_round(ctx, sums);
-    if (ctx->sv_ok && j == 0) return sv_round0(ctx, sums);
-    if (ctx->sv_ok && j == 1) return sv_round1(ctx, sums);
+// What a launched round kernel leaves for the host to wait on and to account.
+struct RoundLaunch {
+    u32 seq = 0;
+    u64 bytes = 0, npairs = 0;
+    cudaEvent_t e0 = nullptr, e1 = nullptr;
+};
+
+// Launch the kernel of round J on the current tables (FOLD: folded by the previous challenge on the way in) and move
+// the tables' state on to what the kernel leaves.  CHAIN: the round is part of a chain (see RoundArgs::tstate): it
+// takes its challenge from device memory (unless it is the chain's first launch: then from the host, with STATE0 the
+// host transcript's hash state), does the transcript's part itself and posts to its slot of the chain's buffer.
+static int enqueue_round(sc_ctx *ctx, int j, bool fold, bool chain, bool chain_first, const u32 *state0, RoundLaunch *out) {
+    const int D = ctx->D, W = ctx->points * D;
     const bool bind2 = ctx->sv_ok && j == 2;   // round 2 reads the base tables and binds both challenges on the way in
-    if (!round_supported(D, ctx->points, ctx->nt_used)) return fail(ctx, SC_EUNSUPPORTED, "no kernel for D=%d points=%d tables=%d", D, ctx->points, ctx->nt_used);
-    int rc;
-    if (ctx->world > 1 && j == ctx->gather_round) {   // the slices are small: gather them, every rank goes on alike
-        if (ctx->have_r && (rc = fold_all(ctx))) return rc;
-        if ((rc = gather_tables(ctx))) return rc;
-    }
     const bool local = ctx->world > 1 && j < ctx->gather_round;
-    const bool fold = ctx->have_r;
     const int shrink = bind2 ? 4 : 2;   // entries in per entry out of the fold
     const RoundPlan &pl = ctx->plan[j];
-    if (fold && !local && tail_wanted(ctx)) {
-        if ((rc = tail_start(ctx))) return rc;
-        return tail_round(ctx, sums);
-    }
+    int rc;
 
     RoundArgs a;
     memset(&a, 0, sizeof a);
@@ -1190,7 +1230,10 @@ extern "C" int sc_round(sc_ctx *ctx, uint32_t *sums) {
     // a statement over five or seven tables runs the kernel for six or eight: the spare position repeats position 0
     for (int k = ctx->ntables; k < SC_MAX_TABLES; k++) { a.src[k] = a.src[0]; a.dst[k] = a.dst[0]; a.src_base[k] = a.src_base[0]; }
     a.npairs = fold ? in_entries / (2 * shrink) : in_entries / 2;
-    if (fold) challenge_words(ctx, a.r);
+    if (fold) {
+        if (chain && !chain_first) a.r_dev = ctx->d_chal + (size_t)(j - 1) * 16;
+        else challenge_words(ctx, a.r);
+    }
     if (bind2) {   // eq(rho0 rho1, b): bit 0 of b pairs with rho0 (EQ-TABLE, src/field.lisp:354-363)
         E4 r0, r1; memcpy(r0.v, ctx->sv_rho0, 16); memcpy(r1.v, ctx->r, 16);
         const E4 one = e4_base(1), n0 = e4_sub(one, r0), n1 = e4_sub(one, r1);
@@ -1211,21 +1254,31 @@ extern "C" int sc_round(sc_ctx *ctx, uint32_t *sums) {
         for (int c = 0; c < D; c++) a.post[c] = ctx->use_factor ? mmul(to_mont(ctx->st_factor[c]), re) : (c == 0 ? re : 0u);
         if (rankw) ext_mul_host(D, a.post, ctx->post, a.post);
     }
-    a.seq = ++ctx->seq;
     a.partials = ctx->d_partials; a.counter = ctx->d_counter;
     a.out_dev = ctx->d_out;
-    a.out_host = local ? nullptr : ctx->h_out_dev;
+    if (chain) {
+        a.seq = ctx->chain_seq + (u32)j;
+        a.out_host = ctx->h_chain_dev + (size_t)j * CHAIN_SLOT_WORDS;
+        a.tstate = ctx->d_tstate;
+        a.chal_dev = ctx->d_chal + (size_t)j * 16;
+        a.tinit = chain_first;
+        if (chain_first) memcpy(a.tstate0, state0, sizeof a.tstate0);
+    } else {
+        a.seq = ++ctx->seq;
+        a.out_host = local ? nullptr : ctx->h_out_dev;
+    }
     bool all_base = !fold && ctx->base_groups > 0 && !ctx->force_generic;
     for (int k = 0; k < ctx->nt_used && all_base; k++) all_base = a.src_base[k];
     // sharded rounds: the last block exchanges the sums with the other ranks itself (peer stores), unless the
-    // ranks could not open each other's memory or the round runs the base-table kernel: then NCCL carries them
-    const bool fused_exchange = local && ctx->p2p && !all_base;
+    // ranks could not open each other's memory: then NCCL carries them
+    const bool fused_exchange = local && ctx->p2p;
     if (fused_exchange) {
         for (int r = 0; r < ctx->world; r++) a.mail[r] = ctx->mail[r];
         a.world = ctx->world; a.rank = ctx->rank; a.xseq = ++ctx->xseq;
         a.mail_polls = ctx->mail_polls;
-        a.out_host = ctx->h_out_dev;
+        if (!chain) a.out_host = ctx->h_out_dev;
     }
+    if (chain && local && !fused_exchange) return fail(ctx, SC_ESTATE, "a chained round without peer access");
 
     const u64 chunk = (1ull << a.logL) > (u64)ROUND_THREADS ? (1ull << a.logL) : (u64)ROUND_THREADS;
     u64 chunks = (a.npairs + chunk - 1) / chunk;
@@ -1234,13 +1287,11 @@ extern "C" int sc_round(sc_ctx *ctx, uint32_t *sums) {
     if (grid < 1) grid = 1;
     const size_t smem = a.use_low ? ((size_t)1 << a.logL) * 2 * D * 4 : 0;
 
-    cudaEvent_t e0 = nullptr, e1 = nullptr;
     if (ctx->timing) {
         while (ctx->ev.size() < 2) { cudaEvent_t e; CU(cudaEventCreate(&e)); ctx->ev.push_back(e); }
-        e0 = ctx->ev[0]; e1 = ctx->ev[1];
-        CU(cudaEventRecord(e0, ctx->stream));
+        out->e0 = ctx->ev[0]; out->e1 = ctx->ev[1];
+        CU(cudaEventRecord(out->e0, ctx->stream));
     }
-    const auto tr1 = std::chrono::steady_clock::now();
     if (all_base) {
         a.ngroups = ctx->base_groups;
         a.product = ctx->shape == SHAPE_PRODUCT;
@@ -1250,7 +1301,7 @@ extern "C" int sc_round(sc_ctx *ctx, uint32_t *sums) {
         CU(launch_round(D, ctx->shape, ctx->points, ctx->nt_used, bind2 ? 2 : (fold ? 1 : 0), a, grid, smem, ctx->stream));
     }
     ctx->launches++;
-    if (ctx->timing) CU(cudaEventRecord(e1, ctx->stream));
+    if (ctx->timing) CU(cudaEventRecord(out->e1, ctx->stream));
     if (local && !fused_exchange) {   // the whole job's sums: all-gather of the ranks' words, then their sum mod p
         if (!ctx->d_gather) { if ((rc = dev_alloc(ctx, (void **)&ctx->d_gather, (u64)ctx->world * SV_MAX_WORDS * 4))) return rc; }
         ncclResult_t r = g_nccl.AllGather(ctx->d_out, ctx->d_gather, (size_t)W, NCCL_UINT32, ctx->comm, ctx->stream);
@@ -1258,24 +1309,137 @@ extern "C" int sc_round(sc_ctx *ctx, uint32_t *sums) {
         CU(launch_sum_ranks(ctx->d_gather, ctx->world, W, ctx->d_out, ctx->h_out_dev, MAX_PARTIAL_WORDS, a.seq, ctx->stream));
         ctx->launches++;
     }
+    if (fold) {   // the tables the next launch reads (everything is ordered on the stream)
+        for (int k = 0; k < ctx->ntables; k++) {
+            TableState &t = ctx->tab[ctx->order[k]];
+            const int nb = t.cur_buf == 0 ? 1 : 0;
+            t.cur = t.buf[nb]; t.cur_buf = nb; t.cur_base = false; t.cur_entries = in_entries / shrink;
+        }
+    }
+    out->seq = a.seq; out->bytes = bytes; out->npairs = a.npairs;
+    return SC_OK;
+}
+
+// Wait for the launch number WANT at WORD (the kernel posts it after its sums).  The wait is bounded; a failed or
+// unfinished exchange between the GPUs ends with the communicator aborted and SC_ECOMM.
+static int await_round(sc_ctx *ctx, int j, const u32 *word, u32 want) {
+    const bool had_comm = ctx->comm != nullptr;
+    const bool seen = wait_word(ctx, word, want);
+    if (!seen && had_comm && !ctx->comm) {
+        cudaStreamSynchronize(ctx->stream);
+        ctx->chain_active = false;
+        return fail(ctx, SC_ECOMM, "round %d: the exchange between the GPUs did not finish in %d s; the communicator was aborted", j, ctx->comm_timeout_s);
+    }
+    if (seen && (*(volatile const u32 *)word & EXCHANGE_FAILED)) {
+        CU(cudaStreamSynchronize(ctx->stream));
+        tail_stop(ctx);
+        comm_abort(ctx);
+        return fail(ctx, SC_ECOMM, "round %d: another rank's sums never arrived; the communicator was aborted", j);
+    }
+    if (!seen || ctx->timing) CU(cudaStreamSynchronize(ctx->stream));
+    if (!seen && (*(volatile const u32 *)word & ~EXCHANGE_FAILED) != want) return fail(ctx, SC_ECUDA, "round %d: the kernel did not post its sums", j);
+    return SC_OK;
+}
+
+// The transcript on the device is asked for and possible: a transcript (or its state) is at hand, nobody wants
+// per-round timing, and with several GPUs the ranks can exchange their sums inside the kernels.
+static bool chain_wanted(const sc_ctx *ctx) {
+    if (!ctx->device_transcript || ctx->timing || ctx->n > CHAIN_MAX_ROUNDS) return false;
+    if (!ctx->attached && !ctx->have_state) return false;
+    if (ctx->attached && sc_transcript_degree(ctx->attached) != ctx->D) return false;
+    return ctx->world == 1 || ctx->p2p;
+}
+
+// Enqueue every remaining round at once, from round ctx->j on: round kernels whose last block carries the transcript
+// on, then the resident kernel for the small rounds.  Nothing here waits for the device.
+static int chain_start(sc_ctx *ctx) {
+    u32 state[B3_STATE_WORDS];
+    if (!transcript_state_now(ctx, state)) return fail(ctx, SC_ESTATE, "no transcript state for the device to start from");
+    ctx->have_state = false;
+    const int j0 = ctx->j;
+    ctx->chain_first = j0;
+    ctx->chain_seq = ctx->seq + 1;
+    ctx->seq += CHAIN_MAX_ROUNDS + 2;
+    bool fold = ctx->have_r, first = true;
+    int j = j0, rc;
+    for (; j < ctx->n; j++) {
+        const u32 *r_dev = first ? nullptr : ctx->d_chal + (size_t)(j - 1) * 16;
+        if (ctx->world > 1 && j == ctx->gather_round) {   // the slices are small: gather them, every rank goes on alike
+            if (fold && (rc = fold_all(ctx, r_dev))) return rc;
+            if ((rc = gather_tables(ctx))) return rc;
+            if (fold) {   // the fold is done: the round itself reads the gathered tables as they are ...
+                // ... which the round kernels cannot know, so the tables go one more step: round j folds nothing
+                fold = false;
+            }
+        }
+        const bool local = ctx->world > 1 && j < ctx->gather_round;
+        if (fold && !local && tail_wanted(ctx, j)) {
+            if ((rc = tail_start(ctx, j, true, first, state))) return rc;
+            break;
+        }
+        RoundLaunch L;
+        if ((rc = enqueue_round(ctx, j, fold, true, first, state, &L))) return rc;
+        first = false;
+        fold = true;
+    }
+    ctx->chain_end = j;
+    ctx->chain_active = true;
+    ctx->have_r = false;
+    return SC_OK;
+}
+
+// A round of a chain: wait for its slot.
+static int chain_round(sc_ctx *ctx, uint32_t *sums) {
+    const int j = ctx->j;
+    if (j >= ctx->chain_end) return tail_round(ctx, sums);
+    const u32 *slot = ctx->h_chain + (size_t)j * CHAIN_SLOT_WORDS;
+    int rc = await_round(ctx, j, slot + MAX_PARTIAL_WORDS, ctx->chain_seq + (u32)j);
+    if (rc) { ctx->chain_active = false; ctx->begun = false; return rc; }
+    memcpy(sums, slot, (size_t)ctx->points * ctx->D * 4);
+    ctx->have_r = false;
+    ctx->j = j + 1;
+    return SC_OK;
+}
+
+extern "C" int sc_round(sc_ctx *ctx, uint32_t *sums) {
+    if (!ctx || !sums) return SC_EINVAL;
+    if (!ctx->begun) return fail(ctx, SC_ESTATE, "sc_round before sc_begin");
+    if (ctx->j >= ctx->n) return fail(ctx, SC_ESTATE, "all %d rounds are done", ctx->n);
+    if (ctx->j > 0 && !ctx->have_r) return fail(ctx, SC_ESTATE, "round %d needs the challenge of round %d", ctx->j, ctx->j - 1);
+    static const bool trace = getenv("SABLE_B200_TRACE") != nullptr;
+    const auto tr0 = std::chrono::steady_clock::now();
+    cudaSetDevice(ctx->device);
+    const int D = ctx->D, j = ctx->j, W = ctx->points * D;
+    if (ctx->chain_active) return chain_round(ctx, sums);
+    if (ctx->tail_active) return tail_round(ctx, sums);
+    if (ctx->sv_ok && j == 0) return sv_round0(ctx, sums);
+    if (ctx->sv_ok && j == 1) return sv_round1(ctx, sums);
+    if (!round_supported(D, ctx->points, ctx->nt_used)) return fail(ctx, SC_EUNSUPPORTED, "no kernel for D=%d points=%d tables=%d", D, ctx->points, ctx->nt_used);
+    int rc;
+    if (chain_wanted(ctx)) {
+        if ((rc = chain_start(ctx))) return rc;
+        return chain_round(ctx, sums);
+    }
+    ctx->have_state = false;   // a state handed over for this call and not used
+    bool fold = ctx->have_r;
+    if (ctx->world > 1 && j == ctx->gather_round) {   // the slices are small: gather them, every rank goes on alike
+        if (fold && (rc = fold_all(ctx))) return rc;
+        if ((rc = gather_tables(ctx))) return rc;
+        fold = false;   // folded already (fold_all cleared the pending challenge)
+    }
+    const bool local = ctx->world > 1 && j < ctx->gather_round;
+    if (fold && !local && tail_wanted(ctx, j)) {
+        if ((rc = tail_start(ctx, j, false, false, nullptr))) return rc;
+        ctx->have_r = false;
+        return tail_round(ctx, sums);
+    }
+    const auto tr1 = std::chrono::steady_clock::now();
+    RoundLaunch L;
+    if ((rc = enqueue_round(ctx, j, fold, false, false, nullptr, &L))) return rc;
     const auto tr2 = std::chrono::steady_clock::now();
     // wait for the sums: poll the word the kernel posts after them (a stream synchronize costs several
     // microseconds more per round); the wait is bounded
-    {
-        const bool had_comm = ctx->comm != nullptr;
-        const bool seen = wait_word(ctx, ctx->h_out + MAX_PARTIAL_WORDS, a.seq);
-        if (!seen && had_comm && !ctx->comm) {
-            cudaStreamSynchronize(ctx->stream);
-            return fail(ctx, SC_ECOMM, "round %d: the exchange between the GPUs did not finish in %d s; the communicator was aborted", j, ctx->comm_timeout_s);
-        }
-        if (seen && (*(volatile u32 *)(ctx->h_out + MAX_PARTIAL_WORDS) & EXCHANGE_FAILED)) {
-            CU(cudaStreamSynchronize(ctx->stream));
-            comm_abort(ctx);
-            return fail(ctx, SC_ECOMM, "round %d: another rank's sums never arrived; the communicator was aborted", j);
-        }
-        if (!seen || ctx->timing) CU(cudaStreamSynchronize(ctx->stream));
-        if (!seen && (*(volatile u32 *)(ctx->h_out + MAX_PARTIAL_WORDS) & ~EXCHANGE_FAILED) != a.seq) return fail(ctx, SC_ECUDA, "round %d: the kernel did not post its sums", j);
-    }
+    if ((rc = await_round(ctx, j, ctx->h_out + MAX_PARTIAL_WORDS, L.seq))) return rc;
     memcpy(sums, ctx->h_out, (size_t)W * 4);
     if (trace) {
         const auto tr3 = std::chrono::steady_clock::now();
@@ -1284,16 +1448,9 @@ extern "C" int sc_round(sc_ctx *ctx, uint32_t *sums) {
     }
     if (ctx->timing) {
         sc_round_stat s;
-        CU(cudaEventElapsedTime(&s.kernel_ms, e0, e1));
-        s.bytes = bytes; s.pairs = a.npairs;
+        CU(cudaEventElapsedTime(&s.kernel_ms, L.e0, L.e1));
+        s.bytes = L.bytes; s.pairs = L.npairs;
         ctx->stats.push_back(s);
-    }
-    if (fold) {
-        for (int k = 0; k < ctx->ntables; k++) {
-            TableState &t = ctx->tab[ctx->order[k]];
-            const int nb = t.cur_buf == 0 ? 1 : 0;
-            t.cur = t.buf[nb]; t.cur_buf = nb; t.cur_base = false; t.cur_entries = in_entries / shrink;
-        }
     }
     ctx->have_r = false;
     ctx->j = j + 1;
@@ -1306,24 +1463,36 @@ extern "C" int sc_challenge(sc_ctx *ctx, const uint32_t *r) {
     if (ctx->have_r) return fail(ctx, SC_ESTATE, "round %d already has its challenge", ctx->j - 1);
     for (int c = 0; c < ctx->D; c++) ctx->r[c] = r[c] % P;
     ctx->have_r = true;
+    const int done = ctx->j - 1;   // the round the challenge belongs to
+    if (ctx->chain_active && done >= ctx->chain_first && done < ctx->chain_end) {
+        // the round kernel derived this challenge itself and posted it with its sums: it must be the caller's
+        const volatile u32 *slot = ctx->h_chain + (size_t)done * CHAIN_SLOT_WORDS;
+        for (int c = 0; c < ctx->D; c++)
+            if (slot[CHAIN_CHAL_WORD + c] != ctx->r[c]) {
+                tail_stop(ctx);
+                ctx->begun = false;
+                return fail(ctx, SC_ESTATE, "round %d: the challenge differs from the one the device derived from the attached transcript (was the transcript used for something else during the proof?)", done);
+            }
+        return SC_OK;
+    }
     if (ctx->tail_active && ctx->tail_own) {
         // the resident kernel derived this challenge itself from its copy of the transcript: it must be the caller's
-        const u32 k = (u32)(ctx->j - 1 - ctx->tail_first);
+        const u32 k = (u32)(done - ctx->tail_first);
         const u32 *slot = ctx->h_tail + (size_t)k * TAIL_SLOT_WORDS;
-        if (!wait_word(ctx, slot + 50, ctx->tail_seq + k)) return fail(ctx, SC_ECUDA, "the device did not post its challenge of round %d", ctx->j - 1);
+        if (!wait_word(ctx, slot + 50, ctx->tail_seq + k)) return fail(ctx, SC_ECUDA, "the device did not post its challenge of round %d", done);
         for (int c = 0; c < ctx->D; c++)
             if (((volatile const u32 *)slot)[52 + c] != ctx->r[c]) {
                 tail_stop(ctx);
                 ctx->begun = false;
-                return fail(ctx, SC_ESTATE, "round %d: the challenge differs from the attached transcript's (was the transcript used for something else during the proof?)", ctx->j - 1);
+                return fail(ctx, SC_ESTATE, "round %d: the challenge differs from the attached transcript's (was the transcript used for something else during the proof?)", done);
             }
         return SC_OK;
     }
     if (ctx->tail_active) {   // hand the challenge to the resident kernel: the words first, then the word it polls
-        u32 *slot = ctx->h_tail + (size_t)(ctx->j - 1 - ctx->tail_first) * TAIL_SLOT_WORDS;
+        u32 *slot = ctx->h_tail + (size_t)(done - ctx->tail_first) * TAIL_SLOT_WORDS;
         for (int c = 0; c < ctx->D; c++) ((volatile u32 *)slot)[40 + c] = ctx->r[c];
         std::atomic_thread_fence(std::memory_order_seq_cst);
-        ((volatile u32 *)slot)[48] = ctx->tail_seq + (u32)(ctx->j - 1 - ctx->tail_first);
+        ((volatile u32 *)slot)[48] = ctx->tail_seq + (u32)(done - ctx->tail_first);
         std::atomic_thread_fence(std::memory_order_seq_cst);
     }
     return SC_OK;
@@ -1342,10 +1511,11 @@ extern "C" int sc_finish(sc_ctx *ctx, uint32_t *folded) {
         if (ok && ctx->tail_own && getenv("SABLE_B200_TRACE"))
             for (int k = 0; k < ctx->tail_rounds; k++) {
                 const u32 *slot = ctx->h_tail + (size_t)k * TAIL_SLOT_WORDS;
-                fprintf(stderr, "  resident round %d: compute %u ns, post %u ns, absorb %u ns, challenge %u ns\n", ctx->tail_first + k, slot[60], slot[61], slot[62], slot[63]);
+                fprintf(stderr, "  resident round %d: arithmetic %u ns, transcript %u ns\n", ctx->tail_first + k, slot[60], slot[61]);
             }
         if (ok) {
             ctx->tail_active = false;
+            ctx->chain_active = false;
             ctx->begun = false;
             if (folded)
                 for (int k = 0; k < ctx->ntables; k++)
@@ -1364,6 +1534,7 @@ extern "C" int sc_finish(sc_ctx *ctx, uint32_t *folded) {
         for (int s = 0; s < ctx->ntables; s++) slots[s] = s;
         if ((rc = export_tables(ctx, slots, ctx->ntables, (u64)ctx->K, folded))) return rc;
     }
+    ctx->chain_active = false;
     ctx->begun = false;
     return SC_OK;
 }

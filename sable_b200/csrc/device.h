@@ -5,6 +5,7 @@
 
 #include "../../include/sumcheck_b200.h"
 #include "field.cuh"
+#include "transcript.cuh"
 
 namespace sc {
 
@@ -77,11 +78,26 @@ struct RoundArgs {
     int world, rank;
     u32 xseq;
     unsigned mail_polls;  // polls (with a short sleep each) the last block waits for the other ranks' sums
+    // The transcript carried on by the device (transcript.cuh).  With TSTATE the last block does the transcript's part of
+    // the round itself: SEND of the sums and CHALLENGE, from the hash state in TSTATE (or, for the first launch of a
+    // chain, from TSTATE0, the host transcript's state), leaves the new state in TSTATE and the challenge in CHAL_DEV
+    // (D words in Montgomery form, then the D canonical words) and, canonical, at word CHAIN_CHAL_WORD of out_host.
+    // The next launch folds by the challenge it finds at its R_DEV, so the host can enqueue every round of a proof
+    // without waiting for any of them.  Word CHAIN_DEAD of TSTATE: a round of this chain failed (another rank's sums
+    // never came); the launches after it post the failure at once instead of waiting again.
+    const u32 *r_dev;
+    u32 *tstate;
+    u32 *chal_dev;
+    int tinit;
+    u32 tstate0[B3_STATE_WORDS - 4];
     u32 bind[4][8];       // FOLD = 2: eq(rho0 rho1, b), b < 4, Montgomery form: entry y of the bound table is sum_b bind[b] T[4y + b]
     int ngroups;
     int product;          // 1: the statement is the product of the tables (no term table needed)
     u32 gcoef[2][8];      // Montgomery form
 };
+constexpr int CHAIN_CHAL_WORD = 72;   // out_host: sums at [0, 64), the posted launch number at 64, the challenge at [72, 80)
+constexpr int CHAIN_SLOT_WORDS = 96;
+constexpr int CHAIN_DEAD = 31;
 constexpr int MAIL_WORDS = 128, MAIL_FLAG = 64;
 constexpr unsigned MAIL_POLL_LIMIT = 20000000u;   // polls (with a short sleep each) a rank waits for the others' sums
 constexpr u32 EXCHANGE_FAILED = 0x80000000u;      // or-ed into the posted launch number when a rank's sums never came
@@ -163,13 +179,14 @@ struct TailArgs {
     u32 seq;
     u32 *host;                         // the mapped buffer (device address)
     unsigned poll_limit;               // polls before the block gives up on a challenge
-    // own_transcript: the block derives each challenge itself, from a copy of the host transcript's hash state
-    // as it stood before this launch's first round (the host replays the same messages and checks)
+    // own_transcript: the block derives each challenge itself (transcript.cuh) instead of waiting for the host, which
+    // replays the same messages on its transcript and checks.  The hash state it starts from is TSTATE0 (a copy of
+    // the host transcript's state before this launch's first round) or, when TSTATE is set, the state the round
+    // kernels before it left in device memory; then the challenge of the round before the launch is at R_DEV.
     int own_transcript;
-    int b3_fill;                       // bytes in the pending block
-    u32 b3_cv[8];                      // chaining value
-    u32 b3_pending[16];                // pending block, little-endian words
-    u64 b3_blocks;                     // blocks compressed so far
+    u32 tstate0[B3_STATE_WORDS - 4];
+    u32 *tstate;
+    const u32 *r_dev;
 };
 cudaError_t launch_tail(int D, int shape, int points, int nt_used, const TailArgs &args, cudaStream_t stream);
 
@@ -179,6 +196,7 @@ struct FoldArgs {
     u32 *dst[SC_MAX_TABLES];
     uint8_t src_base[SC_MAX_TABLES];
     int ntables;
+    const u32 *r_dev;   // non-null: the challenge lies here, in device memory, instead of in r
     u32 r[8];     // Montgomery form
     u64 nout;     // entries written per table
 };

@@ -18,6 +18,7 @@
 #include "../../include/sumcheck_b200.h"
 #include "field.cuh"
 #include "part_workers.h"
+#include "transcript.cuh"
 
 using scf::u32;
 using scf::u64;
@@ -279,6 +280,24 @@ extern "C" int sc_transcript_state(const sc_transcript *tr, uint32_t cv[8], uint
     B3S::words(tr->state.pending, pending);
     *fill = tr->state.fill;
     *blocks = tr->state.blocks;
+    return SC_OK;
+}
+// The device's transcript code (transcript.cuh) run on the host from TR's present state: SEND of the ROWS x COLS
+// values and CHALLENGE of TR's degree.  TR itself is not changed, so a test can make the same two steps on TR
+// and compare the challenge and the state.
+extern "C" int sc_transcript_device_round(const sc_transcript *tr, const uint32_t *values, int rows, int cols, uint32_t *state_out,
+                                          uint32_t *challenge) {
+    if (!tr || !values || rows < 1 || cols < 1 || rows * cols > SC_MAX_POINTS * 8) return SC_EINVAL;
+    u32 state[sc::B3_STATE_WORDS] = {0}, pending[16];
+    int fill = 0;
+    uint64_t blocks = 0;
+    sc_transcript_state(tr, state, pending, &fill, &blocks);
+    memcpy(state + 8, pending, sizeof pending);
+    state[24] = (u32)fill; state[25] = (u32)blocks; state[26] = (u32)(blocks >> 32);
+    sc::TrWork work;
+    sc::transcript_round(&work, state, values, rows * cols, tr->degree, state);
+    if (state_out) memcpy(state_out, state, sizeof state);
+    if (challenge) memcpy(challenge, work.chal, 4 * (size_t)tr->degree);
     return SC_OK;
 }
 extern "C" int sc_transcript_absorb(sc_transcript *tr, const uint8_t *data, uint64_t len) {

@@ -25,6 +25,8 @@ __global__ void __launch_bounds__(ROUND_THREADS, 2) round_base_kernel(const __gr
     extern __shared__ __align__(16) u32 smem[];
     constexpr int W = NG * PTS * D;
     __shared__ u32 red[ROUND_THREADS / 32][W];
+    __shared__ u32 out[PTS * D];
+    __shared__ TrWork tw;
     __shared__ bool is_last;
     const int tid = threadIdx.x;
     const u32 L = 1u << a.logL;
@@ -268,20 +270,11 @@ __global__ void __launch_bounds__(ROUND_THREADS, 2) round_base_kernel(const __gr
                 s = emul<D>(s, pf);
             }
 #pragma unroll
-            for (int c = 0; c < D; c++) {
-                a.out_dev[tid * D + c] = s.v[c];
-                if (a.out_host) a.out_host[tid * D + c] = s.v[c];
-            }
-            __threadfence_system();
+            for (int c = 0; c < D; c++) out[tid * D + c] = s.v[c];
         }
         __syncthreads();
-        if (tid == 0) {
-            *a.counter = 0;
-            if (a.out_host) {
-                __threadfence_system();
-                *reinterpret_cast<volatile u32 *>(a.out_host + MAX_PARTIAL_WORDS) = a.seq;
-            }
-        }
+        if (tid == 0) *a.counter = 0;
+        publish_round(a, out, PTS * D, D, &tw);
     }
 }
 

@@ -55,6 +55,68 @@ template <int D, int NT> __device__ __forceinline__ Ext<D> pick(const Ext<D> (&v
     return o;
 }
 
+// The end of a round, run by every thread of the one block that holds the round's W sums (canonical words, in
+// shared memory).  Several GPUs: the sums go to every rank's mailbox and come back added up.  With the transcript
+// on the device (RoundArgs::tstate) the block then sends the sums and draws the challenge.  Last the sums (and the
+// challenge) are written for the host, and the launch number after them.
+static __device__ __noinline__ void publish_round(const RoundArgs &a, u32 *sums, int W, int D, TrWork *tw) {
+    const int tid = threadIdx.x;
+    __shared__ int missing;
+    u32 posted = a.seq;
+    const bool dead = a.tstate && !a.tinit && *reinterpret_cast<const volatile u32 *>(a.tstate + CHAIN_DEAD) != 0;
+    if (a.xseq) {
+        // hand the sums to every rank (this one included), the exchange number after them
+        const size_t box = ((size_t)(a.xseq & 1) * a.world + a.rank) * MAIL_WORDS;
+        if (tid < W)
+            for (int r = 0; r < a.world; r++) a.mail[r][box + tid] = sums[tid];
+        __threadfence_system();
+        __syncthreads();
+        if (tid < a.world) *reinterpret_cast<volatile u32 *>(a.mail[tid] + box + MAIL_FLAG) = a.xseq;
+        // wait for every rank's number in this rank's own mailbox: bounded
+        if (tid == 0) missing = dead ? 1 : 0;
+        __syncthreads();
+        if (tid < a.world && !dead) {
+            const volatile u32 *flag = a.mail[a.rank] + ((size_t)(a.xseq & 1) * a.world + tid) * MAIL_WORDS + MAIL_FLAG;
+            unsigned poll = 0;
+            while (*flag != a.xseq && ++poll < a.mail_polls) __nanosleep(64);
+            if (*flag != a.xseq) atomicAdd(&missing, 1);
+        }
+        __syncthreads();
+        if (missing) posted |= EXCHANGE_FAILED;
+        else if (tid < W) {
+            u32 v = 0;
+            for (int r = 0; r < a.world; r++)
+                v = fadd(v, *reinterpret_cast<const volatile u32 *>(a.mail[a.rank] + ((size_t)(a.xseq & 1) * a.world + r) * MAIL_WORDS + tid));
+            sums[tid] = v;
+        }
+        __syncthreads();
+    }
+    if (a.tstate) {
+        if (posted & EXCHANGE_FAILED) {
+            if (tid == 0) a.tstate[CHAIN_DEAD] = 1;
+        } else {
+            transcript_round(tw, a.tinit ? a.tstate0 : a.tstate, sums, W, D, a.tstate);
+            __syncthreads();
+            if (tid < D) {
+                const u32 c = tw->chal[tid];
+                a.chal_dev[tid] = to_mont(c);
+                a.chal_dev[D + tid] = c;
+                if (a.out_host) a.out_host[CHAIN_CHAL_WORD + tid] = c;
+            }
+            if (tid == 0 && a.tinit) a.tstate[CHAIN_DEAD] = 0;
+        }
+    }
+    if (tid < W) {
+        a.out_dev[tid] = sums[tid];
+        if (a.out_host) a.out_host[tid] = sums[tid];
+    }
+    __syncthreads();
+    if (tid == 0 && a.out_host) {   // the host polls this word: the words above are visible before it (the fence is cumulative)
+        __threadfence_system();
+        *reinterpret_cast<volatile u32 *>(a.out_host + MAX_PARTIAL_WORDS) = posted;
+    }
+}
+
 // The statement at one point: sum of coefficient * product of the tables' values.  Values are
 // canonical words; a product of two of them leaves REDC's factor 1/R behind, which the
 // coefficients and the final factor of the round make up for (see DevStatement).  With BASEAWARE
@@ -158,6 +220,7 @@ template <int D, int PTS, int NT, int FOLD, int SHAPE>
 __global__ void __launch_bounds__(ROUND_THREADS, NT > 4 ? 1 : (D == 8 ? SC_MINBLOCKS_D8 : (FOLD ? SC_MINBLOCKS : SC_MINBLOCKS_R0))) round_kernel(const __grid_constant__ RoundArgs a) {
     extern __shared__ __align__(16) u32 smem[];
     __shared__ u32 red[ROUND_THREADS / 32][PTS * D];
+    __shared__ TrWork tw;
     __shared__ bool is_last;
     const int tid = threadIdx.x;
     const u32 L = 1u << a.logL;
@@ -173,7 +236,7 @@ __global__ void __launch_bounds__(ROUND_THREADS, NT > 4 ? 1 : (D == 8 ? SC_MINBL
     if (FOLD == 1) {
         Ext<D> r;
 #pragma unroll
-        for (int c = 0; c < D; c++) r.v[c] = a.r[c];
+        for (int c = 0; c < D; c++) r.v[c] = a.r_dev ? a.r_dev[c] : a.r[c];
         rm = eprep<D>(r);
     }
     u32 bind[4][D];   // FOLD = 2: the weights of the four entries of a block
@@ -434,44 +497,7 @@ __global__ void __launch_bounds__(ROUND_THREADS, NT > 4 ? 1 : (D == 8 ? SC_MINBL
             for (int c = 0; c < D; c++) red[0][tid * D + c] = s.v[c];
         }
         __syncthreads();
-        u32 posted = a.seq;
-        if (a.xseq) {
-            // hand the sums to every rank (this one included), the exchange number after them
-            const size_t box = ((size_t)(a.xseq & 1) * a.world + a.rank) * MAIL_WORDS;
-            if (tid < W)
-                for (int r = 0; r < a.world; r++) a.mail[r][box + tid] = red[0][tid];
-            __threadfence_system();
-            __syncthreads();
-            if (tid < a.world) *reinterpret_cast<volatile u32 *>(a.mail[tid] + box + MAIL_FLAG) = a.xseq;
-            // wait for every rank's number in this rank's own mailbox: bounded
-            __shared__ int missing;
-            if (tid == 0) missing = 0;
-            __syncthreads();
-            if (tid < a.world) {
-                const volatile u32 *flag = a.mail[a.rank] + ((size_t)(a.xseq & 1) * a.world + tid) * MAIL_WORDS + MAIL_FLAG;
-                unsigned poll = 0;
-                while (*flag != a.xseq && ++poll < a.mail_polls) __nanosleep(64);
-                if (*flag != a.xseq) atomicAdd(&missing, 1);
-            }
-            __syncthreads();
-            if (missing) posted |= EXCHANGE_FAILED;
-            else if (tid < W) {
-                u32 v = 0;
-                for (int r = 0; r < a.world; r++)
-                    v = fadd(v, *reinterpret_cast<const volatile u32 *>(a.mail[a.rank] + ((size_t)(a.xseq & 1) * a.world + r) * MAIL_WORDS + tid));
-                red[0][tid] = v;
-            }
-            __syncthreads();
-        }
-        if (tid < W) {
-            a.out_dev[tid] = red[0][tid];
-            if (a.out_host) a.out_host[tid] = red[0][tid];
-        }
-        __syncthreads();
-        if (tid == 0 && a.out_host) {   // the host polls this word: the sums above are visible before it (the fence is cumulative)
-            __threadfence_system();
-            *reinterpret_cast<volatile u32 *>(a.out_host + MAX_PARTIAL_WORDS) = posted;
-        }
+        publish_round(a, &red[0][0], W, D, &tw);
     }
 }
 

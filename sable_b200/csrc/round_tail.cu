@@ -8,11 +8,10 @@
 // instead of a launch and a completion.  Every wait is bounded: a block that hears nothing for
 // its limit of polls, or is told to stop, records why and returns.
 //
-// With own_transcript the block does not wait at all: it carries a copy of the transcript's hash
-// state and derives every challenge itself (SEND of its sums, CHALLENGE), posting sums and challenges
-// for the host, which replays the same steps on its transcript and checks that they agree.
+// With own_transcript the block does not wait at all: it carries the transcript's hash state on
+// (transcript.cuh) and derives every challenge itself (SEND of its sums, CHALLENGE), posting sums and
+// challenges for the host, which replays the same steps on its transcript and checks that they agree.
 #include "round_kernel.cuh"
-#include "b3s.cuh"
 
 namespace sc {
 
@@ -33,7 +32,8 @@ __global__ void __launch_bounds__(ROUND_THREADS) tail_kernel(const __grid_consta
     __shared__ u32 red[ROUND_THREADS / 32][PTS * D];
     __shared__ u32 chal[8];
     __shared__ u32 msg[PTS * D];
-    __shared__ B3State hash;
+    __shared__ u32 hash[B3_STATE_WORDS];
+    __shared__ TrWork tw;
     __shared__ int go;
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     constexpr int W = PTS * D, ROWS = ROUND_THREADS / 32;
@@ -47,14 +47,10 @@ __global__ void __launch_bounds__(ROUND_THREADS) tail_kernel(const __grid_consta
     }
     Ext<D> r;
 #pragma unroll
-    for (int c = 0; c < D; c++) r.v[c] = a.r[c];
+    for (int c = 0; c < D; c++) r.v[c] = a.r_dev ? a.r_dev[c] : a.r[c];
     ExtM<D> rm = eprep<D>(r);
 
-    if (a.own_transcript && tid == 0) {
-        for (int i = 0; i < 8; i++) hash.cv[i] = a.b3_cv[i];
-        for (int i = 0; i < 16; i++) hash.pending[i] = a.b3_pending[i];
-        hash.fill = a.b3_fill; hash.blocks = a.b3_blocks;
-    }
+    if (a.own_transcript && tid < B3_STATE_WORDS - 4) hash[tid] = a.tstate ? a.tstate[tid] : a.tstate0[tid];
     for (int k = 0; k < a.nrounds; k++) {
         const u32 t_round = timer_ns();
         const TailRound rd = a.rd[k];
@@ -172,22 +168,19 @@ __global__ void __launch_bounds__(ROUND_THREADS) tail_kernel(const __grid_consta
             for (int c = 0; c < D; c++) { slot[tid * D + c] = s.v[c]; msg[tid * D + c] = s.v[c]; }
         }
         __syncthreads();   // also: every store of the folded tables is done before the next round reads them
-        if (tid == 0 && a.own_transcript) {
-            const u32 s0 = timer_ns();
-            __threadfence_system();
-            st_sys(slot + 32, a.seq + (u32)k);
-            const u32 s1 = timer_ns();
+        if (a.own_transcript) {
             // the transcript's next steps, here: SEND of the sums, then the challenge; the host replays both and compares
-            b3_absorb_words(&hash, msg, W);
-            const u32 s2 = timer_ns();
-            b3_challenge(&hash, D, chal);
-            const u32 s3 = timer_ns();
-#pragma unroll
-            for (int c = 0; c < D; c++) slot[52 + c] = chal[c];
-            slot[60] = s0 - t_round; slot[61] = s1 - s0; slot[62] = s2 - s1; slot[63] = s3 - s2;   // nanoseconds: compute, post, absorb, challenge
-            __threadfence_system();
-            st_sys(slot + 50, a.seq + (u32)k);
-            go = 1;
+            const u32 s0 = timer_ns();
+            transcript_round(&tw, hash, msg, W, D, hash);
+            __syncthreads();
+            if (tid < D) { chal[tid] = tw.chal[tid]; slot[52 + tid] = tw.chal[tid]; }
+            if (tid == 0) { slot[60] = s0 - t_round; slot[61] = timer_ns() - s0; go = 1; }   // nanoseconds: the round's arithmetic, its transcript steps
+            __syncthreads();
+            if (tid == 0) {
+                __threadfence_system();   // cumulative: the sums and the challenge written before the barrier are visible before the words below
+                st_sys(slot + 32, a.seq + (u32)k);
+                st_sys(slot + 50, a.seq + (u32)k);
+            }
         } else if (tid == 0) {
             __threadfence_system();   // cumulative: the sums written before the barrier are visible before the word below
             st_sys(slot + 32, a.seq + (u32)k);

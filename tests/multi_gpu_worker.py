@@ -105,6 +105,7 @@ def main():
         for slot, (_, a) in enumerate(mine):
             prover.upload_table(slot, a)
         prover.begin(n, eq=eq)
+        prover.attach_transcript(tr)      # used only when the device carries the transcript (SABLE_B200_DEVICE_TRANSCRIPT=1)
         tr.absorb(b"sc|" + n.to_bytes(2, "little") + degree.to_bytes(2, "little") + (1).to_bytes(4, "little"))
         rho = []
         for _ in range(n):
@@ -114,6 +115,7 @@ def main():
             rho.append(r)
             prover.challenge(r)
         finals = prover.finish(len(full))[:, 0, :].tolist()
+        prover.attach_transcript(None)
         if rank == 0:
             from oracle import pyoracle as orc
             tb = orc.Transcript("multi", d)

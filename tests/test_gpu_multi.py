@@ -18,13 +18,16 @@ def gpu_count():
     return torch.cuda.device_count()
 
 
-@pytest.mark.parametrize("world,gather_bits", [(2, None), (2, 0), (4, None), (8, 2)])
-def test_sharded_proof_equals_the_oracle(world, gather_bits):
+@pytest.mark.parametrize("world,gather_bits,device_transcript", [(2, None, False), (2, 0, False), (4, None, False), (8, 2, False),
+                                                                  (2, None, True), (4, None, True), (8, None, True)])
+def test_sharded_proof_equals_the_oracle(world, gather_bits, device_transcript):
     # gather_bits: the slice size (log2) at which the ranks gather their tables; 0 keeps every round but the last sharded
     if gpu_count() < world:
         pytest.skip("needs %d GPUs" % world)
     with tempfile.TemporaryDirectory() as tmp:
         env = dict(os.environ, NCCL_NVLS_ENABLE="0")
+        if device_transcript:                 # every rank's round kernels hash the summed words themselves
+            env["SABLE_B200_DEVICE_TRANSCRIPT"] = "1"
         if gather_bits is not None:
             env["SABLE_B200_GATHER_BITS"] = str(gather_bits)
             env["SABLE_B200_P2P"] = "0"       # these runs carry the sums with NCCL, the others with peer stores

@@ -344,25 +344,82 @@ def test_download_gives_the_table_back_and_refuses_in_the_small_value_rounds(pro
     assert e.value.code == -5
 
 
-@pytest.mark.parametrize("d,n,statement,names", [
-    (4, 13, "(+ (* t0 t3) (* t1 t2) (* alpha t2 t3))", ["t0", "t1", "t2", "t3"]),
-    (8, 10, "(* t0 t1 t2)", ["t0", "t1", "t2"]),
-    (4, 9, "(+ (* 7 t0 t1) t1 -3)", ["t0", "t1"]),
+@pytest.fixture(scope="module")
+def chained():
+    """A context that carries the transcript on the device: every round of a proof is enqueued at once."""
+    p = sb.Prover(0)
+    p.set_device_transcript(True)
+    yield p
+    p.close()
+
+
+@pytest.mark.parametrize("d,n,statement,kinds", [
+    (4, 13, "(+ (* t0 t3) (* t1 t2) (* alpha t2 t3))", [0, 0, 0, 0]),
+    (8, 10, "(* t0 t1 t2)", [0, 0, 0]),
+    (4, 9, "(+ (* 7 t0 t1) t1 -3)", [0, 0]),
+    (4, 3, "(* t0 t1)", [1, 0]),                                        # fewer rounds than the resident kernel's first
+    (4, 21, "(+ (* t0 t3) (* t1 t2) (* alpha t2 t3))", [1, 1, 0, 0]),   # many-block launches: round 0 on the caller's tables, split weights
+    (8, 20, "(+ (* alpha t0 t1) (* 3 t1))", [1, 1]),                    # round 0 by the base-table kernel
+    (4, 22, "(* t0 t1 t2)", [1, 1, 1]),                                 # rounds 0 and 1 from one pass (host), the chain from round 2
+    (4, 18, "(+ (* t0 t1) (* t1 t2) (* t2 t3) (* t3 t4) (* 3 t4 t0))", [1, 0, 0, 1, 0]),   # five tables: no resident kernel, the last fold alone
 ])
-def test_device_transcript_gives_the_same_proof(prover, d, n, statement, names, monkeypatch):
-    # SABLE_B200_DEVICE_TRANSCRIPT=1: the resident kernel of the last rounds hashes its own sums (BLAKE3 on the
-    # device) and derives the challenges itself; the host replays and checks.  Same bytes as the oracle.
-    monkeypatch.setenv("SABLE_B200_DEVICE_TRANSCRIPT", "1")
+def test_device_transcript_gives_the_same_proof(chained, d, n, statement, kinds):
+    # the last block of every round kernel hashes the round's sums (BLAKE3 on the device) and draws the challenge the
+    # next launch folds by; the host replays the transcript afterwards and checks.  Same bytes as the oracle.
     rng = np.random.default_rng(n)
-    tables = [(nm, rand_ext(rng, d, 1 << n)) for nm in names]
+    tables = [("t%d" % t, rng.integers(0, P, size=1 << n, dtype=np.uint32) if k else rand_ext(rng, d, 1 << n)) for t, k in enumerate(kinds)]
     constants = [("alpha", rand_ext(rng, d).tolist())] if "alpha" in statement else []
     for eq in (rand_ext(rng, d, n), None):
-        got, want, ta, tb = both(prover, d, n, statement, tables, eq=eq, constants=constants)
+        before = chained.launches
+        got, want, ta, tb = both(chained, d, n, statement, tables, eq=eq, constants=constants, threads=0)
         assert_same(got, want, ta, tb)
+        assert chained.launches > before
+
+
+def test_device_transcript_with_block_weights(chained):
+    d, K, n = 4, 3, 14
+    rng = np.random.default_rng(5)
+    tables = [("a", rand_ext(rng, d, K << n)), ("b", rng.integers(0, P, size=K << n, dtype=np.uint32)), ("c", rand_ext(rng, d, K << n))]
+    got, want, ta, tb = both(chained, d, n, "(+ (* a b) (* lam b c))", tables, eq=rand_ext(rng, d, n),
+                             constants=[("lam", rand_ext(rng, d).tolist())], block_weights=rand_ext(rng, d, K), label="gkr", threads=0)
+    assert_same(got, want, ta, tb)
+
+
+def test_device_transcript_from_a_bare_hash_state(chained):
+    # a caller whose transcript is not the library's (a Lisp one) hands over the hash state before the first round
+    import ctypes as C
+    d, n = 4, 15
+    rng = np.random.default_rng(15)
+    tabs = [rng.integers(0, P, size=1 << n, dtype=np.uint32), rand_ext(rng, d, 1 << n)]
+    eq = rand_ext(rng, d, n)
+    degree, terms = sb.lower_statement("(* a b)", d, ["a", "b"])
+    chained.attach_transcript(None)
+    chained.set_statement(d, 2, 2, terms)
+    for s, t in enumerate(tabs):
+        chained.upload_table(s, t)
+    chained.begin(n, eq=eq)
+    tr = orc.Transcript("bare", d)                # the oracle's transcript stands in for the foreign one
+    tr.absorb(b"sc|" + n.to_bytes(2, "little") + (2).to_bytes(2, "little") + (1).to_bytes(4, "little"))
+    mirror = sb.Transcript("bare", d)             # only to read the same state in the library's layout
+    mirror.absorb(b"sc|" + n.to_bytes(2, "little") + (2).to_bytes(2, "little") + (1).to_bytes(4, "little"))
+    cv = (C.c_uint32 * 8)(); pend = (C.c_uint32 * 16)(); fill = C.c_int(); blocks = C.c_uint64()
+    assert sb.library().sc_transcript_state(C.c_void_p(mirror._h), cv, pend, C.byref(fill), C.byref(blocks)) == 0
+    chained._call("sc_attach_transcript_state", cv, pend, fill, blocks)
+    before = chained.launches
+    rho = []
+    for j in range(n):
+        tr.send(chained.round())
+        rho.append(tr.challenge())
+        chained.challenge(rho[-1])
+    assert chained.launches - before <= n - 10    # one launch per large round and one for all the small ones, none per small round
+    finals = chained.finish(2)[:, 0, :].tolist()
+    tb = orc.Transcript("bare", d)
+    want = orc.prove(tb, n, "(* a b)", [("a", tabs[0]), ("b", tabs[1])], eq=eq)
+    assert rho == want[0] and finals == [want[1]["a"], want[1]["b"]] and tr.proof() == tb.proof()
 
 
 def test_device_transcript_notices_a_foreign_challenge(monkeypatch):
-    monkeypatch.setenv("SABLE_B200_DEVICE_TRANSCRIPT", "1")
+    monkeypatch.setenv("SABLE_B200_DEVICE_TRANSCRIPT", "1")      # read when the context is made
     import ctypes as C
     p = sb.Prover(0)
     try:
@@ -377,9 +434,13 @@ def test_device_transcript_notices_a_foreign_challenge(monkeypatch):
         p.begin(n)
         tr.send(p.round())
         p.challenge(tr.challenge())
-        tr.send(p.round())                           # the resident kernel starts here, with a copy of tr's state
-        with pytest.raises(sb.SumcheckError):        # not the challenge the device derived from that state
+        tr.send(p.round())
+        with pytest.raises(sb.SumcheckError):        # not the challenge the device derived from its copy of tr's state
             p.challenge([1, 2, 3, 4])
+        # and the context is usable again
+        tables = [("a", rand_ext(rng, d, 1 << n)), ("b", rand_ext(rng, d, 1 << n))]
+        got, want, ta, tb = both(p, d, n, "(* a b)", tables, eq=rand_ext(rng, d, n))
+        assert_same(got, want, ta, tb)
     finally:
         p.close()
 

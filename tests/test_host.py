@@ -175,3 +175,48 @@ def test_gkr_and_helpers_reject_bad_arguments_without_a_device():
     assert lib.sc_transcript_state(h, cv, pend, ctypes.byref(fill), ctypes.byref(blocks)) == 0
     assert 0 < fill.value <= 64 and blocks.value == 0          # "LLM-SUMCHECK-v6-O|x": 19 bytes pending, nothing compressed yet
     assert bytes(pend)[:fill.value] == b"LLM-SUMCHECK-v6-O|x"
+
+
+def device_state(tr):
+    """The transcript's hash state in the device's layout (32 words)."""
+    lib = sb.library()
+    cv = (ctypes.c_uint32 * 8)(); pend = (ctypes.c_uint32 * 16)(); fill = ctypes.c_int(); blocks = ctypes.c_uint64()
+    assert lib.sc_transcript_state(ctypes.c_void_p(tr._h), cv, pend, ctypes.byref(fill), ctypes.byref(blocks)) == 0
+    return list(cv) + list(pend) + [fill.value, blocks.value & 0xffffffff, blocks.value >> 32]
+
+
+@pytest.mark.parametrize("d", [4, 8])
+def test_device_transcript_code_follows_the_host_transcript(d):
+    # the code the round kernels' last block runs (transcript.cuh), executed on the host: after any prefix, SEND of a
+    # round message and CHALLENGE give the host transcript's challenge and leave the same hash state -- whatever
+    # the byte offset inside the pending block, for every message size, over chains of rounds
+    lib = sb.library()
+    rng = np.random.default_rng(d)
+    for trial in range(40):
+        tr = sb.Transcript("dev-%d" % trial, d)
+        tr.absorb(bytes(rng.integers(0, 256, size=int(rng.integers(0, 200)), dtype=np.uint8)))
+        for rnd in range(12):
+            rows = int(rng.integers(1, 9))
+            values = rng.integers(0, P, size=(rows, d), dtype=np.uint32)
+            state = (ctypes.c_uint32 * 32)()
+            chal = (ctypes.c_uint32 * 8)()
+            assert lib.sc_transcript_device_round(ctypes.c_void_p(tr._h), values.ctypes.data_as(ctypes.POINTER(ctypes.c_uint32)),
+                                                  rows, d, state, chal) == 0
+            tr.send(values)
+            assert list(chal)[:d] == tr.challenge(), (trial, rnd)
+            assert list(state)[:27] == device_state(tr), (trial, rnd)
+
+
+def test_device_transcript_code_against_the_oracle_transcript():
+    # the same through the oracle's transcript (pinned by the reference's :transcript and :b3s vectors)
+    lib = sb.library()
+    d = 4
+    ta, tb = sb.Transcript("sc-vec", d), orc.Transcript("sc-vec", d)
+    rng = np.random.default_rng(9)
+    for rnd in range(30):
+        values = rng.integers(0, P, size=(3, d), dtype=np.uint32)
+        chal = (ctypes.c_uint32 * 8)()
+        assert lib.sc_transcript_device_round(ctypes.c_void_p(ta._h), values.ctypes.data_as(ctypes.POINTER(ctypes.c_uint32)), 3, d, None, chal) == 0
+        ta.send(values); tb.send(values)
+        want = tb.challenge()
+        assert ta.challenge() == want and list(chal)[:d] == want
