@@ -31,6 +31,7 @@ constexpr int TR_BUF_WORDS = 96;     // 384 bytes: a pending block (64), a messa
 struct TrWork {          // a block's scratch for one round of the transcript (shared memory on the device)
     u32 cv[8];
     u32 buf[TR_BUF_WORDS];
+    u32 out[16];         // the last compression's output
     u32 chal[8];         // the challenge, canonical words
     u32 off, total;      // byte offsets into buf: the pending block starts at off, the stream ends at total
     u32 blocks[2];
@@ -97,10 +98,9 @@ TR_FN void tr_compress(const u32 *cv, const u32 *block, u32 counter_lo, u32 coun
 // so every block of the stream but the last one is compressed.
 TR_INL void tr_settle(TrWork *w) {
     while (w->total - w->off > 64) {
-        u32 o[16];
-        tr_compress(w->cv, w->buf + w->off / 4, w->blocks[0], w->blocks[1], 64, 0, o);
+        tr_compress(w->cv, w->buf + w->off / 4, w->blocks[0], w->blocks[1], 64, 0, w->out);
 #pragma unroll
-        for (int i = 0; i < 8; i++) w->cv[i] = o[i];
+        for (int i = 0; i < 8; i++) w->cv[i] = w->out[i];
         if (++w->blocks[0] == 0) ++w->blocks[1];
         w->off += 64;
     }
@@ -141,19 +141,18 @@ TR_FN void transcript_round(TrWork *w, const u32 *state_in, const u32 *sums, int
                 w->off = 0; w->total = fill;
             }
             const int nbytes = 4 * (D - have + 4);      // at most 48: one output block
-            u32 o[16];
-            tr_compress(w->cv, w->buf + w->off / 4, 0, 0, w->total - w->off, 2u | 8u, o);   // CHUNK_END | ROOT, counter 0 (:113-123)
-            // SQUEEZE (:152-157): after the output, "squeeze" and the first 32 output bytes are absorbed
-            const char *tag = "squeeze";
-            for (int k = 0; k < 7; k++) tr_put_byte(w, w->total + (u32)k, (u32)(unsigned char)tag[k]);
-            const int take = nbytes < 32 ? nbytes : 32;
-            for (int k = 0; k < take; k++) tr_put_byte(w, w->total + 7u + (u32)k, (o[k >> 2] >> (8 * (k & 3))) & 0xffu);
-            w->total += 7u + (u32)take;
-            tr_settle(w);
+            tr_compress(w->cv, w->buf + w->off / 4, 0, 0, w->total - w->off, 2u | 8u, w->out);   // CHUNK_END | ROOT, counter 0 (:113-123)
             for (int i = 0; i < nbytes / 4 && have < D; i++) {
-                const u32 v = o[i] & 0x7FFFFFFFu;
+                const u32 v = w->out[i] & 0x7FFFFFFFu;
                 if (v < scf::P) w->chal[have++] = v;
             }
+            // SQUEEZE (:152-157): after the output, "squeeze" and the first 32 output bytes are absorbed
+            const u32 tag[2] = {0x65757173u, 0x00657a65u};   // "sque", "eze"
+            for (int k = 0; k < 7; k++) tr_put_byte(w, w->total + (u32)k, (tag[k >> 2] >> (8 * (k & 3))) & 0xffu);
+            const int take = nbytes < 32 ? nbytes : 32;
+            for (int k = 0; k < take; k++) tr_put_byte(w, w->total + 7u + (u32)k, (w->out[k >> 2] >> (8 * (k & 3))) & 0xffu);
+            w->total += 7u + (u32)take;
+            tr_settle(w);     // overwrites w->out: the challenge and the absorbed bytes were taken from it above
         }
     }
     TR_SYNC();
