@@ -158,6 +158,7 @@ struct sc_ctx {
     u32 chain_seq = 0;               // round j of the chain posts chain_seq + j
     bool have_state = false;         // a hash state handed over by sc_attach_transcript_state, not used yet
     u32 state0[B3_STATE_WORDS];
+    std::chrono::steady_clock::time_point chain_t0;   // when the chain's last launch was enqueued (for SABLE_B200_TRACE)
 
     // the first two rounds from one pass over base tables (see SvArgs)
     bool sv_ok = false;
@@ -438,6 +439,43 @@ static u32 pow_r(int k) {
     return k >= 0 ? pw(R1, (u64)k) : pw(pw(R1, P - 2), (u64)(-k));
 }
 
+// The statements with kernels of their own (device.h): can the statement's tables be put into the entry's positions
+// so that the terms' table lists agree, with no coefficient beyond the kind the entry's term takes?
+static bool match_listed(const ListedInfo &L, int D, int ntables, int nterms, const uint32_t *coeffs, const int32_t *term_ptr,
+                         const int32_t *term_tables, const bool *used, int *slot_at, int *term_at) {
+    int slots[SC_MAX_TABLES], ns = 0;
+    for (int s = 0; s < ntables; s++) if (used[s]) slots[ns++] = s;
+    if (ns != L.nt || nterms != L.nterms || nterms > LISTED_MAX_TERMS) return false;
+    for (int t = 0; t < nterms; t++) if (term_ptr[t + 1] - term_ptr[t] > LISTED_MAX_FACTORS) return false;
+    int perm[SC_MAX_TABLES];
+    for (int k = 0; k < ns; k++) perm[k] = k;
+    do {   // position k holds slot slots[perm[k]]
+        int pos_of[SC_MAX_TABLES] = {0};
+        for (int k = 0; k < ns; k++) pos_of[slots[perm[k]]] = k;
+        int torder[LISTED_MAX_TERMS] = {0, 1, 2};
+        do {   // statement term t plays the entry's term torder[t]
+            bool ok = true;
+            for (int t = 0; t < nterms && ok; t++) {
+                const int e = torder[t], nf = term_ptr[t + 1] - term_ptr[t];
+                if (nf != L.nf[e]) { ok = false; break; }
+                int mine[LISTED_MAX_FACTORS], theirs[LISTED_MAX_FACTORS];
+                for (int k = 0; k < nf; k++) { mine[k] = pos_of[term_tables[term_ptr[t] + k]]; theirs[k] = L.f[e][k]; }
+                std::sort(mine, mine + nf); std::sort(theirs, theirs + nf);
+                for (int k = 0; k < nf; k++) ok = ok && mine[k] == theirs[k];
+                bool upper = false;
+                for (int c = 1; c < D; c++) upper = upper || coeffs[(size_t)t * D + c] % P != 0;
+                if (upper && L.ck[e] != CK_EXT) ok = false;
+            }
+            if (ok) {
+                for (int k = 0; k < ns; k++) slot_at[k] = slots[perm[k]];
+                for (int t = 0; t < nterms; t++) term_at[t] = torder[t];
+                return true;
+            }
+        } while (std::next_permutation(torder, torder + nterms));
+    } while (std::next_permutation(perm, perm + ns));
+    return false;
+}
+
 extern "C" int sc_set_statement(sc_ctx *ctx, int D, int points, int ntables, int nterms, const uint32_t *coeffs,
                                 const int32_t *term_ptr, const int32_t *term_tables) {
     if (!ctx) return SC_EINVAL;
@@ -509,6 +547,19 @@ extern "C" int sc_set_statement(sc_ctx *ctx, int D, int points, int ntables, int
             }
         }
     }
+    int term_at[SC_MAX_TERMS];
+    for (int t = 0; t < SC_MAX_TERMS; t++) term_at[t] = t;
+    const ListedInfo *listed_match = nullptr;
+    if (shape == SHAPE_GENERIC && nterms >= 1 && !ctx->force_generic) {
+        static const ListedInfo listed[LISTED_SHAPES] = {listed_info<0>(), listed_info<1>(), listed_info<2>()};
+        for (int k = 0; k < LISTED_SHAPES; k++)
+            if (points == listed[k].pts && match_listed(listed[k], D, ntables, nterms, coeffs, term_ptr, term_tables, used, first, term_at)) {
+                shape = SHAPE_LISTED + k;
+                nfirst = listed[k].nt;
+                listed_match = &listed[k];
+                break;
+            }
+    }
     bool placed[SC_MAX_TABLES] = {false};
     for (int k = 0; k < nfirst; k++) { ctx->order[npos] = first[k]; pos_of[first[k]] = npos++; placed[first[k]] = true; }
     for (int s = 0; s < ntables; s++) if (used[s] && !placed[s]) { ctx->order[npos] = s; pos_of[s] = npos++; placed[s] = true; }
@@ -527,7 +578,7 @@ extern "C" int sc_set_statement(sc_ctx *ctx, int D, int points, int ntables, int
     ctx->use_factor = false;
     for (int t = 0; t < nterms; t++) {
         // the GKR kernel reads lam from term 0
-        const int at = shape == SHAPE_GKR ? (t == lam_term ? 0 : (t < lam_term ? t + 1 : t)) : t;
+        const int at = shape == SHAPE_GKR ? (t == lam_term ? 0 : (t < lam_term ? t + 1 : t)) : (shape >= SHAPE_LISTED ? term_at[t] : t);
         DevTerm &tm = ctx->st.terms[at];
         tm.nf = (uint8_t)(term_ptr[t + 1] - term_ptr[t]);
         for (int k = 0; k < tm.nf; k++) tm.f[k] = (uint8_t)pos_of[term_tables[term_ptr[t] + k]];
@@ -578,6 +629,13 @@ extern "C" int sc_set_statement(sc_ctx *ctx, int D, int points, int ntables, int
         memset(ctx->gcoef, 0, sizeof ctx->gcoef);
         ctx->gcoef[0][0] = R1;
         if (shape == SHAPE_PRODUCT) { ctx->base_groups = 1; ok = false; }   // the product's coefficient rides in the final factor
+        if (shape >= SHAPE_LISTED) {   // a listed statement keeps the sums its entry says, whatever kind its coefficients happen to be
+            ok = false;
+            ctx->base_groups = listed_base_groups(shape);
+            for (int e = 0; e < nterms && ctx->base_groups; e++)   // the terms lie in the entry's order by now
+                if (listed_match->ck[e] == CK_EXT)
+                    for (int c = 0; c < D; c++) ctx->gcoef[listed_base_group_of(shape, e)][c] = ctx->st.terms[e].coeff[c];
+        }
         for (int t = 0; t < nterms && ok; t++) {
             DevTerm &tm = ctx->st.terms[t];
             tm.group = 0;
@@ -713,10 +771,12 @@ static int low_bits_cap(int D) { return D == 4 ? 11 : 10; }   // 2^a multipliers
 // The split of the v = (variables after the round's own) eq variables of a round: the lower a of
 // them index the low multipliers held in shared memory, the others the high weights.  Any split
 // gives the same sums (SPLIT-WEIGHTS, src/sumcheck.lisp:43-49, splits in the middle).
-static int split_bits(int D, int v) {
+static int split_bits(int D, int v, bool round0 = false) {
     if (v < 20) return 0;
     int a = v - 12;
-    return a < low_bits_cap(D) ? a : low_bits_cap(D);
+    // a round 0 that stages its loads through shared memory: half the low weights leave room for two blocks per SM
+    const int cap = low_bits_cap(D) - (round0 && round_is_staged(D, 1, 0) ? 1 : 0);
+    return a < cap ? a : cap;
 }
 
 // The host transcript of the proof that follows (or NULL): with it the resident kernel of the last rounds
@@ -806,7 +866,7 @@ extern "C" int sc_reserve(sc_ctx *ctx, int D, int n, int K, int ntables) {
     }
     u64 words = 0;
     for (int j = 0; j < n; j++) {   // as sc_begin lays the weights out, with eq and block weights present
-        const int v = n - 1 - j, a = split_bits(D, v);
+        const int v = n - 1 - j, a = split_bits(D, v, j == 0);
         if (a > 0) words += ((u64)1 << a) * 2 * D;
         words += ((u64)1 << (v - a)) * (u64)K * D;
     }
@@ -875,6 +935,9 @@ extern "C" int sc_begin(sc_ctx *ctx, int n, const uint32_t *eq, int K, const uin
         ctx->use_post = true;
     }
 
+    // round 0 runs the base-table kernel (which stages nothing) when every table of the statement is a base table
+    bool base_round0 = ctx->base_groups > 0 && !ctx->force_generic;
+    for (int k = 0; k < ctx->nt_used && base_round0; k++) base_round0 = ctx->tab[ctx->order[k]].stride == 1;
     // one LOW and one HIGH table per round
     std::vector<WeightDesc> &descs = ctx->stage_descs;
     descs.clear();
@@ -885,7 +948,7 @@ extern "C" int sc_begin(sc_ctx *ctx, int n, const uint32_t *eq, int K, const uin
         const int end = local ? nloc : n;            // eq variables of this stage end here
         const int v = end - 1 - j;
         const int blocks = local ? K : 1;
-        const int a = split_bits(D, v);
+        const int a = split_bits(D, v, j == 0 && !base_round0);
         pl.logL = a;
         pl.use_low = eq && a > 0;
         const bool has_bw = block_weights && local;
@@ -1294,9 +1357,8 @@ static int enqueue_round(sc_ctx *ctx, int j, bool fold, bool chain, bool chain_f
     }
     if (all_base) {
         a.ngroups = ctx->base_groups;
-        a.product = ctx->shape == SHAPE_PRODUCT;
         memcpy(a.gcoef, ctx->gcoef, sizeof a.gcoef);
-        CU(launch_round_base(D, ctx->points, ctx->nt_used, a.ngroups, a, grid, smem, ctx->stream));
+        CU(launch_round_base(D, ctx->shape, ctx->points, ctx->nt_used, a.ngroups, a, grid, smem, ctx->stream));
     } else {
         CU(launch_round(D, ctx->shape, ctx->points, ctx->nt_used, bind2 ? 2 : (fold ? 1 : 0), a, grid, smem, ctx->stream));
     }
@@ -1355,6 +1417,7 @@ static bool chain_wanted(const sc_ctx *ctx) {
 static int chain_start(sc_ctx *ctx) {
     u32 state[B3_STATE_WORDS];
     if (!transcript_state_now(ctx, state)) return fail(ctx, SC_ESTATE, "no transcript state for the device to start from");
+    const auto t_begin = std::chrono::steady_clock::now();
     ctx->have_state = false;
     const int j0 = ctx->j;
     ctx->chain_first = j0;
@@ -1385,6 +1448,8 @@ static int chain_start(sc_ctx *ctx) {
     ctx->chain_end = j;
     ctx->chain_active = true;
     ctx->have_r = false;
+    ctx->chain_t0 = std::chrono::steady_clock::now();
+    if (getenv("SABLE_B200_TRACE")) fprintf(stderr, "  chain of rounds %d..%d enqueued in %.1f us (%d round kernels)\n", j0, ctx->n - 1, std::chrono::duration<double, std::micro>(ctx->chain_t0 - t_begin).count(), j - j0);
     return SC_OK;
 }
 
@@ -1395,6 +1460,8 @@ static int chain_round(sc_ctx *ctx, uint32_t *sums) {
     const u32 *slot = ctx->h_chain + (size_t)j * CHAIN_SLOT_WORDS;
     int rc = await_round(ctx, j, slot + MAX_PARTIAL_WORDS, ctx->chain_seq + (u32)j);
     if (rc) { ctx->chain_active = false; ctx->begun = false; return rc; }
+    static const bool trace = getenv("SABLE_B200_TRACE") != nullptr;
+    if (trace) fprintf(stderr, "  chained round %d seen %.1f us after the chain was enqueued\n", j, std::chrono::duration<double, std::micro>(std::chrono::steady_clock::now() - ctx->chain_t0).count());
     memcpy(sums, slot, (size_t)ctx->points * ctx->D * 4);
     ctx->have_r = false;
     ctx->j = j + 1;

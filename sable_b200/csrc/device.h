@@ -18,7 +18,57 @@ enum CoeffKind : uint8_t { CK_ONE = 0, CK_BASE = 1, CK_EXT = 2 };
 //   SHAPE_PRODUCT  c t0 t1 .. t(k-1), each table once, k points; c rides in the round's final factor
 //   SHAPE_GKR      a d + b c + lam c d over the tables (a, b, c, d) = positions (0, 1, 2, 3);
 //                  lam is the coefficient of term 0
-enum Shape : int { SHAPE_GENERIC = 0, SHAPE_PRODUCT = 1, SHAPE_GKR = 2 };
+//   SHAPE_LISTED + k  statement k of the list below, its term table resolved at compile time
+enum Shape : int { SHAPE_GENERIC = 0, SHAPE_PRODUCT = 1, SHAPE_GKR = 2, SHAPE_LISTED = 3 };
+
+// Statements instantiated ahead of time.  The reference compiles a kernel per statement at run time
+// (ROUND-KERNEL, src/sumcheck.lisp:270-280); here a statement on this list gets kernels of its own at build time:
+// the description below is all compile-time, so the term loop unrolls into straight-line code with every table
+// index fixed.  A statement matches an entry when its tables can be put into the entry's positions so that the
+// terms' table lists agree and no coefficient needs more than the entry's kind allows (CK_EXT takes any
+// coefficient, CK_BASE one in the base field).  Every other statement runs the term-table kernel.  To add one:
+// a specialisation here, a line in LISTED_SHAPES, and the instantiations in the launchers (launch_round_listed,
+// launch_tail, launch_round_base).
+template <int K> struct Listed;
+#ifdef __CUDACC__
+#define SC_CX static constexpr __host__ __device__
+#else
+#define SC_CX static constexpr
+#endif
+// c0 t0 t1 + c1 t1: a product and one of its tables again, e.g. (+ (* alpha t0 t1) (* 3 t1))
+template <> struct Listed<0> {
+    static constexpr int NT = 2, PTS = 2, NTERMS = 2;
+    SC_CX int nf(int t) { return t == 0 ? 2 : 1; }
+    SC_CX int f(int t, int k) { return t == 0 ? k : 1; }
+    SC_CX int ck(int t) { return t == 0 ? CK_EXT : CK_BASE; }
+};
+// c0 t0 t1 t2 + c1 t2, e.g. the reference's base-table test statement (+ (* t0 t1 t2) (* 7 t1)) (tests/tests.lisp:333)
+template <> struct Listed<1> {
+    static constexpr int NT = 3, PTS = 3, NTERMS = 2;
+    SC_CX int nf(int t) { return t == 0 ? 3 : 1; }
+    SC_CX int f(int t, int k) { return t == 0 ? k : 2; }
+    SC_CX int ck(int t) { return t == 0 ? CK_EXT : CK_BASE; }
+};
+// c0 t0 t1 + c1 t2 t3: a sum of two products over different tables
+template <> struct Listed<2> {
+    static constexpr int NT = 4, PTS = 2, NTERMS = 2;
+    SC_CX int nf(int) { return 2; }
+    SC_CX int f(int t, int k) { return 2 * t + k; }
+    SC_CX int ck(int) { return CK_EXT; }
+};
+constexpr int LISTED_SHAPES = 3;
+constexpr int LISTED_MAX_TERMS = 3, LISTED_MAX_FACTORS = 4;
+// the same descriptions as data, for the host's matching
+struct ListedInfo { int nt, pts, nterms, nf[LISTED_MAX_TERMS], f[LISTED_MAX_TERMS][LISTED_MAX_FACTORS], ck[LISTED_MAX_TERMS]; };
+template <int K> inline ListedInfo listed_info() {
+    ListedInfo o = {};
+    o.nt = Listed<K>::NT; o.pts = Listed<K>::PTS; o.nterms = Listed<K>::NTERMS;
+    for (int t = 0; t < o.nterms; t++) {
+        o.nf[t] = Listed<K>::nf(t); o.ck[t] = Listed<K>::ck(t);
+        for (int k = 0; k < o.nf[t]; k++) o.f[t][k] = Listed<K>::f(t, k);
+    }
+    return o;
+}
 
 // One term of the statement: coefficient times a product of tables.  Tables hold canonical words
 // and constants (coefficients, weights, challenges) are in Montgomery form c R, so REDC of
@@ -40,6 +90,18 @@ struct DevStatement {
 };
 
 constexpr int ROUND_THREADS = 256;
+
+// Round 0 on the caller's tables at D = 4 can stage each pair's entries through shared memory with asynchronous
+// copies (two stages per thread: 8 bytes per base table and 32 per extension table, behind the low weights, which
+// are then halved to leave room for two blocks per SM).  Measured on B200 on the layer statement at n = 28
+// (two base and two extension tables): 4.00 ms staged against 3.70 ms with plain loads, so it is compiled out.
+#ifndef SC_STAGE_R0
+#define SC_STAGE_R0 0
+#endif
+#ifdef __CUDACC__
+__host__ __device__
+#endif
+constexpr bool round_is_staged(int D, int NT, int FOLD) { return SC_STAGE_R0 && FOLD == 0 && D == 4 && NT <= 4; }
 constexpr int MAX_PARTIAL_WORDS = SC_MAX_POINTS * 8;   // points * D words per partial sum
 
 // Everything one round kernel needs.  The kernel reads the current tables (entries 2i, 2i+1 of
@@ -92,7 +154,6 @@ struct RoundArgs {
     u32 tstate0[B3_STATE_WORDS - 4];
     u32 bind[4][8];       // FOLD = 2: eq(rho0 rho1, b), b < 4, Montgomery form: entry y of the bound table is sum_b bind[b] T[4y + b]
     int ngroups;
-    int product;          // 1: the statement is the product of the tables (no term table needed)
     u32 gcoef[2][8];      // Montgomery form
 };
 constexpr int CHAIN_CHAL_WORD = 72;   // out_host: sums at [0, 64), the posted launch number at 64, the challenge at [72, 80)
@@ -107,14 +168,18 @@ constexpr int BASE_MAX_TERMS = 4;      // the base-table kernel keeps its term d
 constexpr int BASE_MAX_FACTORS = 4;    // statements beyond these run the general kernel
 constexpr int PARTIAL_ROW_WORDS = MAX_PARTIAL_WORDS > MAX_GROUPS * FAST_POINTS * 8 ? MAX_PARTIAL_WORDS : MAX_GROUPS * FAST_POINTS * 8;   // words per block in the partials buffer
 
-// Launchers (defined next to their kernels).  Each returns the CUDA error of the launch.
+// Launchers (defined next to their kernels).  Each returns the CUDA error of the launch.  SMEM is the size of the
+// round's low weights; launch_round adds what the kernel stages its loads through.
 // fold: 0 the tables as they are, 1 folded by r on the way in, 2 base tables bound to two challenges at once (args.bind)
 cudaError_t launch_round(int D, int shape, int points, int nt_used, int fold, const RoundArgs &args, int grid, size_t smem,
                          cudaStream_t stream);
 bool round_supported(int D, int points, int nt_used);
 // The round on tables that are all in the base field (no fold): see RoundArgs::ngroups.
-cudaError_t launch_round_base(int D, int points, int nt_used, int ngroups, const RoundArgs &args, int grid, size_t smem,
+cudaError_t launch_round_base(int D, int shape, int points, int nt_used, int ngroups, const RoundArgs &args, int grid, size_t smem,
                               cudaStream_t stream);
+// a listed statement in that kernel: the number of sums it keeps (0: it cannot run there) and the sum of a term
+int listed_base_groups(int shape);
+int listed_base_group_of(int shape, int term);
 
 // The first two rounds of a product of base-field tables from one pass over the tables (the
 // reference's small-value rounds with L0 = 2, src/sumcheck.lisp:319-337): for every block y of four

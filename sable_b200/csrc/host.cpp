@@ -590,7 +590,9 @@ extern "C" int sc_prove(sc_ctx *ctx, sc_transcript *tr, int n, const char *state
     if (world > 1 && (((u64)1 << n) < (u64)world)) return SC_EINVAL;
     for (int t = 0; t < ntables; t++)
         if (tables && tables[t] && (rc = sc_upload_table(ctx, t, tables[t], ((u64)blocks << n) / (u64)world, strides[t]))) return rc;
+    const auto t_start = std::chrono::steady_clock::now();
     if ((rc = sc_begin(ctx, n, eq, blocks, block_weights))) return rc;
+    const auto t_begun = std::chrono::steady_clock::now();
     // the last rounds may derive their challenges on the device from a copy of this transcript's state
     struct Attach { sc_ctx *c; ~Attach() { sc_attach_transcript(c, nullptr); } } attach{ctx};
     if ((rc = sc_attach_transcript(ctx, tr))) return rc;
@@ -620,8 +622,10 @@ extern "C" int sc_prove(sc_ctx *ctx, sc_transcript *tr, int n, const char *state
         if ((rc = sc_challenge(ctx, r))) return rc;
         if (trace) fprintf(stderr, "round %d: device %.1f us, transcript %.1f us\n", j, us(t0, t1), us(t1, t2));
     }
+    const auto t_rounds = now();
     std::vector<u32> out((size_t)ntables * blocks * D);
     if ((rc = sc_finish(ctx, out.data()))) return rc;   // :564-571
+    if (trace) fprintf(stderr, "sc_prove: begin %.1f us, rounds %.1f us, finish %.1f us\n", us(t_start, t_begun), us(t_begun, t_rounds), us(t_rounds, now()));
     if (folded) memcpy(folded, out.data(), 4 * out.size());
     if (finals) for (int t = 0; t < ntables; t++) memcpy(finals + (size_t)t * D, out.data() + (size_t)t * blocks * D, 4 * (size_t)D);
     return SC_OK;

@@ -20,7 +20,14 @@ template <int NT> __device__ __forceinline__ u32 pick_base(const u32 (&val)[NT],
     return o;
 }
 
-template <int D, int PTS, int NT, int NG>
+// The sums a listed statement (device.h) keeps in this kernel: one for its terms with base-field coefficients, if it
+// has any, and one for its term with an extension-field coefficient, if it has one (at most one: MAX_GROUPS).
+template <class S> __host__ __device__ constexpr int listed_ext_terms() { int n = 0; for (int t = 0; t < S::NTERMS; t++) n += S::ck(t) == CK_EXT; return n; }
+template <class S> __host__ __device__ constexpr int listed_groups() { return (listed_ext_terms<S>() < S::NTERMS ? 1 : 0) + listed_ext_terms<S>(); }
+template <class S> __host__ __device__ constexpr int listed_group(int t) { return S::ck(t) == CK_EXT && listed_ext_terms<S>() < S::NTERMS ? 1 : 0; }
+
+// SHAPE: SHAPE_GENERIC (term descriptors from the arguments, kept in registers), SHAPE_PRODUCT, or a listed statement
+template <int D, int PTS, int NT, int NG, int SHAPE>
 __global__ void __launch_bounds__(ROUND_THREADS, 2) round_base_kernel(const __grid_constant__ RoundArgs a) {
     extern __shared__ __align__(16) u32 smem[];
     constexpr int W = NG * PTS * D;
@@ -175,11 +182,22 @@ __global__ void __launch_bounds__(ROUND_THREADS, 2) round_base_kernel(const __gr
                 u32 m[NG];
 #pragma unroll
                 for (int g = 0; g < NG; g++) m[g] = 0;
-                if (a.product) {
+                if (SHAPE == SHAPE_PRODUCT) {
                     u32 pr = val[0];
 #pragma unroll
                     for (int t = 1; t < NT; t++) pr = mmul(pr, val[t]);
                     m[0] = pr;
+                } else if (SHAPE >= SHAPE_LISTED) {
+                    typedef Listed<(SHAPE >= SHAPE_LISTED ? SHAPE - SHAPE_LISTED : 0)> S;
+#pragma unroll
+                    for (int t = 0; t < S::NTERMS; t++) {
+                        u32 pr = val[S::f(t, 0) < NT ? S::f(t, 0) : 0];
+#pragma unroll
+                        for (int k = 1; k < S::nf(t); k++) pr = mmul(pr, val[S::f(t, k) < NT ? S::f(t, k) : 0]);
+                        if (S::ck(t) == CK_BASE) pr = mmul(pr, coef[t < BASE_MAX_TERMS ? t : 0]);
+                        const int g = listed_group<S>(t) < NG ? listed_group<S>(t) : 0;
+                        m[g] = fadd(m[g], pr);
+                    }
                 } else {
                     // the terms, from the descriptors held in registers (see BASE_MAX_TERMS)
 #pragma unroll
@@ -278,16 +296,16 @@ __global__ void __launch_bounds__(ROUND_THREADS, 2) round_base_kernel(const __gr
     }
 }
 
+template <int D, int PTS, int NT, int NG, int SHAPE>
+static cudaError_t launch_base_one(const RoundArgs &args, int grid, size_t smem, cudaStream_t stream) {
+    if (smem > 40 * 1024) cudaFuncSetAttribute(round_base_kernel<D, PTS, NT, NG, SHAPE>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    round_base_kernel<D, PTS, NT, NG, SHAPE><<<grid, ROUND_THREADS, smem, stream>>>(args);
+    return cudaGetLastError();
+}
 template <int D, int PTS, int NT>
 static cudaError_t launch_base_dpn(int ng, const RoundArgs &args, int grid, size_t smem, cudaStream_t stream) {
-    if (ng == 1) {
-        if (smem > 48 * 1024) cudaFuncSetAttribute(round_base_kernel<D, PTS, NT, 1>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-        round_base_kernel<D, PTS, NT, 1><<<grid, ROUND_THREADS, smem, stream>>>(args);
-    } else {
-        if (smem > 48 * 1024) cudaFuncSetAttribute(round_base_kernel<D, PTS, NT, 2>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-        round_base_kernel<D, PTS, NT, 2><<<grid, ROUND_THREADS, smem, stream>>>(args);
-    }
-    return cudaGetLastError();
+    if (ng == 1) return launch_base_one<D, PTS, NT, 1, SHAPE_GENERIC>(args, grid, smem, stream);
+    return launch_base_one<D, PTS, NT, 2, SHAPE_GENERIC>(args, grid, smem, stream);
 }
 template <int D, int PTS>
 static cudaError_t launch_base_dp(int nt, int ng, const RoundArgs &args, int grid, size_t smem, cudaStream_t stream) {
@@ -299,8 +317,24 @@ static cudaError_t launch_base_dp(int nt, int ng, const RoundArgs &args, int gri
     default: return cudaErrorInvalidValue;
     }
 }
+template <int D, int K>
+static cudaError_t launch_base_listed(const RoundArgs &args, int grid, size_t smem, cudaStream_t stream) {
+    typedef Listed<K> S;
+    return launch_base_one<D, S::PTS, S::NT, listed_groups<S>(), SHAPE_LISTED + K>(args, grid, smem, stream);
+}
 template <int D>
-static cudaError_t launch_base_d(int points, int nt, int ng, const RoundArgs &args, int grid, size_t smem, cudaStream_t stream) {
+static cudaError_t launch_base_d(int shape, int points, int nt, int ng, const RoundArgs &args, int grid, size_t smem, cudaStream_t stream) {
+    if (shape == SHAPE_PRODUCT && points == nt && ng == 1) {
+        switch (nt) {
+        case 1: return launch_base_one<D, 1, 1, 1, SHAPE_PRODUCT>(args, grid, smem, stream);
+        case 2: return launch_base_one<D, 2, 2, 1, SHAPE_PRODUCT>(args, grid, smem, stream);
+        case 3: return launch_base_one<D, 3, 3, 1, SHAPE_PRODUCT>(args, grid, smem, stream);
+        case 4: return launch_base_one<D, 4, 4, 1, SHAPE_PRODUCT>(args, grid, smem, stream);
+        }
+    }
+    // the listed statements with at most one extension-field coefficient (the kernel keeps two sums at most)
+    if (shape == SHAPE_LISTED + 0) return launch_base_listed<D, 0>(args, grid, smem, stream);
+    if (shape == SHAPE_LISTED + 1) return launch_base_listed<D, 1>(args, grid, smem, stream);
     switch (points) {
     case 1: return launch_base_dp<D, 1>(nt, ng, args, grid, smem, stream);
     case 2: return launch_base_dp<D, 2>(nt, ng, args, grid, smem, stream);
@@ -310,11 +344,23 @@ static cudaError_t launch_base_d(int points, int nt, int ng, const RoundArgs &ar
     }
 }
 
-cudaError_t launch_round_base(int D, int points, int nt_used, int ngroups, const RoundArgs &args, int grid, size_t smem,
+// the groups a listed statement runs this kernel with, or 0 when it cannot (more than one extension-field coefficient)
+int listed_base_groups(int shape) {
+    if (shape == SHAPE_LISTED + 0) return listed_groups<Listed<0>>();
+    if (shape == SHAPE_LISTED + 1) return listed_groups<Listed<1>>();
+    return 0;
+}
+int listed_base_group_of(int shape, int term) {
+    if (shape == SHAPE_LISTED + 0) return listed_group<Listed<0>>(term);
+    if (shape == SHAPE_LISTED + 1) return listed_group<Listed<1>>(term);
+    return 0;
+}
+
+cudaError_t launch_round_base(int D, int shape, int points, int nt_used, int ngroups, const RoundArgs &args, int grid, size_t smem,
                               cudaStream_t stream) {
     if (ngroups < 1 || ngroups > MAX_GROUPS) return cudaErrorInvalidValue;
-    if (D == 4) return launch_base_d<4>(points, nt_used, ngroups, args, grid, smem, stream);
-    if (D == 8) return launch_base_d<8>(points, nt_used, ngroups, args, grid, smem, stream);
+    if (D == 4) return launch_base_d<4>(shape, points, nt_used, ngroups, args, grid, smem, stream);
+    if (D == 8) return launch_base_d<8>(shape, points, nt_used, ngroups, args, grid, smem, stream);
     return cudaErrorInvalidValue;
 }
 

@@ -45,6 +45,17 @@ template <int D> __device__ __forceinline__ void store_ext(u32 *p, const Ext<D> 
 #pragma unroll
     for (int q = 0; q < D; q += 4) *reinterpret_cast<uint4 *>(p + q) = make_uint4(e.v[q], e.v[q + 1], e.v[q + 2], e.v[q + 3]);
 }
+// Asynchronous copies from global to shared memory (cp.async, 8 or 16 bytes each): the data of a thread's next pair
+// is on its way while the thread works on the current one, without holding registers.
+__device__ __forceinline__ void cp_async8(void *smem, const void *gmem) {
+    asm volatile("cp.async.ca.shared.global [%0], [%1], 8;" ::"r"((unsigned)__cvta_generic_to_shared(smem)), "l"(gmem) : "memory");
+}
+__device__ __forceinline__ void cp_async16(void *smem, const void *gmem) {
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"((unsigned)__cvta_generic_to_shared(smem)), "l"(gmem) : "memory");
+}
+__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
+__device__ __forceinline__ void cp_async_wait_all() { asm volatile("cp.async.wait_group 0;" ::: "memory"); }
+
 template <int D> __device__ __forceinline__ Ext<D> lift(u32 x) { Ext<D> e = ezero<D>(); e.v[0] = x; return e; }
 
 template <int D, int NT> __device__ __forceinline__ Ext<D> pick(const Ext<D> (&val)[NT], int idx) {
@@ -159,6 +170,46 @@ __device__ __forceinline__ Ext<D> eval_statement(const DevStatement &st, const E
             Ext<D> c;
 #pragma unroll
             for (int q = 0; q < D; q++) c.v[q] = tm.coeff[q];
+            if (BASEAWARE && pbase) { prod = escale<D>(c, prod.v[0]); pbase = false; }
+            else prod = emul<D>(prod, c);
+        }
+        abase = abase && pbase;
+        acc = eadd<D>(acc, prod);
+    }
+    if (BASEAWARE) *all_base = abase;
+    return acc;
+}
+
+// A statement of the list (device.h): the same evaluation as eval_statement with every loop bound, table index
+// and coefficient kind a compile-time constant, so it unrolls into straight-line code.
+template <int D, class S, bool BASEAWARE>
+__device__ __forceinline__ Ext<D> eval_listed(const DevStatement &st, const Ext<D> (&val)[S::NT], unsigned base_mask, bool *all_base) {
+    Ext<D> acc = ezero<D>();
+    bool abase = true;
+#pragma unroll
+    for (int t = 0; t < S::NTERMS; t++) {
+        Ext<D> prod = val[S::f(t, 0)];
+        bool pbase = BASEAWARE && ((base_mask >> S::f(t, 0)) & 1);
+#pragma unroll
+        for (int k = 1; k < S::nf(t); k++) {
+            const Ext<D> &v = val[S::f(t, k)];
+            if (BASEAWARE) {
+                const bool vbase = (base_mask >> S::f(t, k)) & 1;
+                if (pbase && vbase) prod.v[0] = mmul(prod.v[0], v.v[0]);
+                else if (vbase) prod = escale<D>(prod, v.v[0]);
+                else if (pbase) { prod = escale<D>(v, prod.v[0]); pbase = false; }
+                else prod = emul<D>(prod, v);
+            } else {
+                prod = emul<D>(prod, v);
+            }
+        }
+        if (S::ck(t) == CK_BASE) {
+            if (BASEAWARE && pbase) prod.v[0] = mmul(prod.v[0], st.terms[t].coeff[0]);
+            else prod = escale<D>(prod, st.terms[t].coeff[0]);
+        } else {
+            Ext<D> c;
+#pragma unroll
+            for (int q = 0; q < D; q++) c.v[q] = st.terms[t].coeff[q];
             if (BASEAWARE && pbase) { prod = escale<D>(c, prod.v[0]); pbase = false; }
             else prod = emul<D>(prod, c);
         }
@@ -289,10 +340,45 @@ __global__ void __launch_bounds__(ROUND_THREADS, NT > 4 ? 1 : (D == 8 ? SC_MINBL
     };
 
     const u64 chunk = L > (u32)ROUND_THREADS ? L : ROUND_THREADS;
-    for (u64 base = (u64)blockIdx.x * chunk; base < a.npairs; base += (u64)gridDim.x * chunk) {
-        for (u64 q = tid; q < chunk; q += ROUND_THREADS) {
-            const u64 i = base + q;
+    // the thread's k-th pair: the chunks go round the blocks, and a thread takes pairs tid, tid + 256, .. of a chunk
+    const int perlog = a.logL > 8 ? a.logL - 8 : 0;   // chunk / ROUND_THREADS = 2^perlog
+    auto pair_of = [&](u64 k) {
+        return ((u64)blockIdx.x + (k >> perlog) * (u64)gridDim.x) * chunk + (u64)tid + ((k & ((1ull << perlog) - 1)) << 8);
+    };
+    constexpr bool STAGED = round_is_staged(D, NT, FOLD);
+    // staging area: after the low weights; per stage, table t's entries at toff[t]: base pairs 8 bytes per thread,
+    // extension pairs as two rows of 16 bytes per thread
+    char *const stage_base = reinterpret_cast<char *>(smem) + (a.use_low ? (size_t)L * 2 * D * 4 : 0);
+    u32 toff[NT], stage_bytes = 0;
+#pragma unroll
+    for (int t = 0; t < NT; t++) { toff[t] = stage_bytes; stage_bytes += ((base_mask >> t) & 1) ? ROUND_THREADS * 8 : ROUND_THREADS * 32; }
+    auto prefetch = [&](u64 i, u32 stage) {
+        char *sp = stage_base + stage * stage_bytes;
+#pragma unroll
+        for (int t = 0; t < NT; t++) {
+            if ((base_mask >> t) & 1) cp_async8(sp + toff[t] + tid * 8, a.src[t] + 2 * i);
+            else {
+                cp_async16(sp + toff[t] + tid * 16, a.src[t] + (2 * i) * D);
+                cp_async16(sp + toff[t] + ROUND_THREADS * 16 + tid * 16, a.src[t] + (2 * i + 1) * D);
+            }
+        }
+    };
+    if (STAGED) {
+        const u64 i0 = pair_of(0);
+        if (i0 < a.npairs) prefetch(i0, 0);
+        cp_async_commit();
+    }
+    for (u64 k = 0;; k++) {
+        {
+            const u64 i = pair_of(k);
             if (i >= a.npairs) break;
+            if (STAGED) {   // this pair's entries have arrived; the next pair's set out
+                cp_async_wait_all();
+                const u64 inext = pair_of(k + 1);
+                if (inext < a.npairs) prefetch(inext, (u32)((k + 1) & 1));
+                cp_async_commit();
+            }
+            const char *const sp = stage_base + (u32)(k & 1) * stage_bytes;
             const u64 h = i >> a.logL;
             if (h != cur_h) {
                 if (cur_h != ~0ull) flush();
@@ -300,9 +386,19 @@ __global__ void __launch_bounds__(ROUND_THREADS, NT > 4 ? 1 : (D == 8 ? SC_MINBL
             }
             // F_p^4: every load of the pair first, so that they are all in flight together; F_p^8: table by
             // table (the entries of four tables at once would not fit the register file)
-            constexpr bool HOIST = D == 4 && NT <= 4;
+            constexpr bool HOIST = D == 4 && NT <= 4 && !STAGED;
             auto load_table = [&](int t, Ext<D> (&et)[NE]) {
-                if (FOLD == 2) {
+                if (STAGED) {
+                    if ((base_mask >> t) & 1) {
+                        const uint2 w = *reinterpret_cast<const uint2 *>(sp + toff[t] + tid * 8);
+                        et[0].v[0] = w.x; et[1 % NE].v[0] = w.y;
+                    } else {
+                        const uint4 w0 = *reinterpret_cast<const uint4 *>(sp + toff[t] + tid * 16);
+                        const uint4 w1 = *reinterpret_cast<const uint4 *>(sp + toff[t] + ROUND_THREADS * 16 + tid * 16);
+                        et[0].v[0] = w0.x; et[0].v[1] = w0.y; et[0].v[2] = w0.z; et[0].v[3] = w0.w;
+                        et[1 % NE].v[0] = w1.x; et[1 % NE].v[1] = w1.y; et[1 % NE].v[2] = w1.z; et[1 % NE].v[3] = w1.w;
+                    }
+                } else if (FOLD == 2) {
                     const uint4 w0 = __ldcs(reinterpret_cast<const uint4 *>(a.src[t]) + 2 * i), w1 = __ldcs(reinterpret_cast<const uint4 *>(a.src[t]) + 2 * i + 1);
                     et[0].v[0] = w0.x; et[0].v[1] = w0.y; et[0].v[2] = w0.z; et[0].v[3] = w0.w;
                     et[1].v[0] = w1.x; et[1].v[1] = w1.y; et[1].v[2] = w1.z; et[1].v[3] = w1.w;
@@ -316,7 +412,7 @@ __global__ void __launch_bounds__(ROUND_THREADS, NT > 4 ? 1 : (D == 8 ? SC_MINBL
                     }
                 } else {
 #pragma unroll
-                    for (int k = 0; k < NE; k++) et[k] = load_ext<D>(a.src[t] + (NE * i + k) * D);
+                    for (int k2 = 0; k2 < NE; k2++) et[k2] = load_ext<D>(a.src[t] + (NE * i + k2) * D);
                 }
             };
             Ext<D> e[HOIST ? NT : 1][NE];
@@ -420,6 +516,10 @@ __global__ void __launch_bounds__(ROUND_THREADS, NT > 4 ? 1 : (D == 8 ? SC_MINBL
                 Ext<D> f;
                 if (SHAPE == SHAPE_PRODUCT) f = eval_product<D, NT, FOLD == 0>(val, base_mask, &fbase);
                 else if (SHAPE == SHAPE_GKR) f = eval_gkr<D, FOLD == 0>(reinterpret_cast<const Ext<D>(&)[4]>(val), lam, base_mask);
+                else if (SHAPE >= SHAPE_LISTED) {
+                    typedef Listed<(SHAPE >= SHAPE_LISTED ? SHAPE - SHAPE_LISTED : 0)> S;
+                    f = eval_listed<D, S, FOLD == 0>(a.st, reinterpret_cast<const Ext<D>(&)[S::NT]>(val), FOLD ? 0u : base_mask, &fbase);
+                }
                 else f = eval_statement<D, NT, FOLD == 0>(a.st, val, FOLD ? 0u : base_mask, &fbase);
                 if (a.use_low) {
                     if (!FOLD && fbase) {   // a base value times the weight: D base products (EXT-SCALE, src/sumcheck.lisp:246)
@@ -504,10 +604,10 @@ __global__ void __launch_bounds__(ROUND_THREADS, NT > 4 ? 1 : (D == 8 ? SC_MINBL
 template <int D, int PTS, int NT, int SHAPE>
 static cudaError_t launch_round_dpns(int fold, const RoundArgs &args, int grid, size_t smem, cudaStream_t stream) {
     if (fold == 1) {
-        if (smem > 48 * 1024) cudaFuncSetAttribute(round_kernel<D, PTS, NT, 1, SHAPE>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        if (smem > 40 * 1024) cudaFuncSetAttribute(round_kernel<D, PTS, NT, 1, SHAPE>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
         round_kernel<D, PTS, NT, 1, SHAPE><<<grid, ROUND_THREADS, smem, stream>>>(args);
     } else if (fold == 0) {
-        if (smem > 48 * 1024) cudaFuncSetAttribute(round_kernel<D, PTS, NT, 0, SHAPE>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        if (smem > 40 * 1024) cudaFuncSetAttribute(round_kernel<D, PTS, NT, 0, SHAPE>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
         round_kernel<D, PTS, NT, 0, SHAPE><<<grid, ROUND_THREADS, smem, stream>>>(args);
     } else {
         return cudaErrorInvalidValue;
@@ -517,7 +617,7 @@ static cudaError_t launch_round_dpns(int fold, const RoundArgs &args, int grid, 
 // base tables bound to two challenges on the way in: only the product kernels have this variant
 template <int D, int NT>
 static cudaError_t launch_round_bind2(const RoundArgs &args, int grid, size_t smem, cudaStream_t stream) {
-    if (smem > 48 * 1024) cudaFuncSetAttribute(round_kernel<D, NT, NT, 2, SHAPE_PRODUCT>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    if (smem > 40 * 1024) cudaFuncSetAttribute(round_kernel<D, NT, NT, 2, SHAPE_PRODUCT>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     round_kernel<D, NT, NT, 2, SHAPE_PRODUCT><<<grid, ROUND_THREADS, smem, stream>>>(args);
     return cudaGetLastError();
 }
@@ -546,6 +646,9 @@ static cudaError_t launch_round_shape(int shape, int points, int nt, int fold, c
         }
     }
     if (shape == SHAPE_GKR && points == 2 && nt == 4) return launch_round_dpns<D, 2, 4, SHAPE_GKR>(fold, args, grid, smem, stream);
+    if (shape == SHAPE_LISTED + 0) return launch_round_dpns<D, Listed<0>::PTS, Listed<0>::NT, SHAPE_LISTED + 0>(fold, args, grid, smem, stream);
+    if (shape == SHAPE_LISTED + 1) return launch_round_dpns<D, Listed<1>::PTS, Listed<1>::NT, SHAPE_LISTED + 1>(fold, args, grid, smem, stream);
+    if (shape == SHAPE_LISTED + 2) return launch_round_dpns<D, Listed<2>::PTS, Listed<2>::NT, SHAPE_LISTED + 2>(fold, args, grid, smem, stream);
     if (shape == SHAPE_PRODUCT && points == nt) {
         switch (nt) {
         case 1: return launch_round_dpns<D, 1, 1, SHAPE_PRODUCT>(fold, args, grid, smem, stream);

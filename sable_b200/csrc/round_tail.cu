@@ -126,6 +126,10 @@ __global__ void __launch_bounds__(ROUND_THREADS) tail_kernel(const __grid_consta
                 bool unused = false;
                 if (SHAPE == SHAPE_PRODUCT) sum[x] = eval_product<D, NT, false>(val, 0u, &unused);
                 else if (SHAPE == SHAPE_GKR) sum[x] = eval_gkr<D, false>(reinterpret_cast<const Ext<D>(&)[4]>(val), lam, 0u);
+                else if (SHAPE >= SHAPE_LISTED) {
+                    typedef Listed<(SHAPE >= SHAPE_LISTED ? SHAPE - SHAPE_LISTED : 0)> S;
+                    sum[x] = eval_listed<D, S, false>(a.st, reinterpret_cast<const Ext<D>(&)[S::NT]>(val), 0u, &unused);
+                }
                 else sum[x] = eval_statement<D, NT, false>(a.st, val, 0u, &unused);
             }
             if (rd.use_high) {
@@ -245,6 +249,9 @@ template <int D, int PTS> static cudaError_t launch_tail_dp(int nt, const TailAr
 }
 template <int D> static cudaError_t launch_tail_d(int shape, int points, int nt, const TailArgs &args, cudaStream_t stream) {
     if (shape == SHAPE_GKR && points == 2 && nt == 4) return launch_tail_one<D, 2, 4, SHAPE_GKR>(args, stream);
+    if (shape == SHAPE_LISTED + 0) return launch_tail_one<D, Listed<0>::PTS, Listed<0>::NT, SHAPE_LISTED + 0>(args, stream);
+    if (shape == SHAPE_LISTED + 1) return launch_tail_one<D, Listed<1>::PTS, Listed<1>::NT, SHAPE_LISTED + 1>(args, stream);
+    if (shape == SHAPE_LISTED + 2) return launch_tail_one<D, Listed<2>::PTS, Listed<2>::NT, SHAPE_LISTED + 2>(args, stream);
     if (shape == SHAPE_PRODUCT && points == nt) {
         switch (nt) {
         case 1: return launch_tail_one<D, 1, 1, SHAPE_PRODUCT>(args, stream);

@@ -74,6 +74,9 @@ STATEMENTS = [
     ("(- (* alpha (expt t0 2) t1) t1)", 2, 1),
     ("(+ (* t0 t3) (* t1 t2) (* alpha t2 t3))", 4, 1),
     ("(* (+ t0 alpha) (- t1 beta))", 2, 2),
+    ("(+ (* alpha t0 t1) (* beta t2 t3))", 4, 2),
+    ("(+ (* 5 t1 t0) t0)", 2, 0),
+    ("(- (* t2 t0 t1) (* 2 t0))", 3, 0),
 ]
 
 
