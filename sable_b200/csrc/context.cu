@@ -771,12 +771,10 @@ static int low_bits_cap(int D) { return D == 4 ? 11 : 10; }   // 2^a multipliers
 // The split of the v = (variables after the round's own) eq variables of a round: the lower a of
 // them index the low multipliers held in shared memory, the others the high weights.  Any split
 // gives the same sums (SPLIT-WEIGHTS, src/sumcheck.lisp:43-49, splits in the middle).
-static int split_bits(int D, int v, bool round0 = false) {
+static int split_bits(int D, int v) {
     if (v < 20) return 0;
     int a = v - 12;
-    // a round 0 that stages its loads through shared memory: half the low weights leave room for two blocks per SM
-    const int cap = low_bits_cap(D) - (round0 && round_is_staged(D, 1, 0) ? 1 : 0);
-    return a < cap ? a : cap;
+    return a < low_bits_cap(D) ? a : low_bits_cap(D);
 }
 
 // The host transcript of the proof that follows (or NULL): with it the resident kernel of the last rounds
@@ -866,7 +864,7 @@ extern "C" int sc_reserve(sc_ctx *ctx, int D, int n, int K, int ntables) {
     }
     u64 words = 0;
     for (int j = 0; j < n; j++) {   // as sc_begin lays the weights out, with eq and block weights present
-        const int v = n - 1 - j, a = split_bits(D, v, j == 0);
+        const int v = n - 1 - j, a = split_bits(D, v);
         if (a > 0) words += ((u64)1 << a) * 2 * D;
         words += ((u64)1 << (v - a)) * (u64)K * D;
     }
@@ -935,9 +933,6 @@ extern "C" int sc_begin(sc_ctx *ctx, int n, const uint32_t *eq, int K, const uin
         ctx->use_post = true;
     }
 
-    // round 0 runs the base-table kernel (which stages nothing) when every table of the statement is a base table
-    bool base_round0 = ctx->base_groups > 0 && !ctx->force_generic;
-    for (int k = 0; k < ctx->nt_used && base_round0; k++) base_round0 = ctx->tab[ctx->order[k]].stride == 1;
     // one LOW and one HIGH table per round
     std::vector<WeightDesc> &descs = ctx->stage_descs;
     descs.clear();
@@ -948,7 +943,7 @@ extern "C" int sc_begin(sc_ctx *ctx, int n, const uint32_t *eq, int K, const uin
         const int end = local ? nloc : n;            // eq variables of this stage end here
         const int v = end - 1 - j;
         const int blocks = local ? K : 1;
-        const int a = split_bits(D, v, j == 0 && !base_round0);
+        const int a = split_bits(D, v);
         pl.logL = a;
         pl.use_low = eq && a > 0;
         const bool has_bw = block_weights && local;

@@ -91,17 +91,7 @@ struct DevStatement {
 
 constexpr int ROUND_THREADS = 256;
 
-// Round 0 on the caller's tables at D = 4 can stage each pair's entries through shared memory with asynchronous
-// copies (two stages per thread: 8 bytes per base table and 32 per extension table, behind the low weights, which
-// are then halved to leave room for two blocks per SM).  Measured on B200 on the layer statement at n = 28
-// (two base and two extension tables): 4.00 ms staged against 3.70 ms with plain loads, so it is compiled out.
-#ifndef SC_STAGE_R0
-#define SC_STAGE_R0 0
-#endif
-#ifdef __CUDACC__
-__host__ __device__
-#endif
-constexpr bool round_is_staged(int D, int NT, int FOLD) { return SC_STAGE_R0 && FOLD == 0 && D == 4 && NT <= 4; }
+
 constexpr int MAX_PARTIAL_WORDS = SC_MAX_POINTS * 8;   // points * D words per partial sum
 
 // Everything one round kernel needs.  The kernel reads the current tables (entries 2i, 2i+1 of
@@ -168,8 +158,7 @@ constexpr int BASE_MAX_TERMS = 4;      // the base-table kernel keeps its term d
 constexpr int BASE_MAX_FACTORS = 4;    // statements beyond these run the general kernel
 constexpr int PARTIAL_ROW_WORDS = MAX_PARTIAL_WORDS > MAX_GROUPS * FAST_POINTS * 8 ? MAX_PARTIAL_WORDS : MAX_GROUPS * FAST_POINTS * 8;   // words per block in the partials buffer
 
-// Launchers (defined next to their kernels).  Each returns the CUDA error of the launch.  SMEM is the size of the
-// round's low weights; launch_round adds what the kernel stages its loads through.
+// Launchers (defined next to their kernels).  Each returns the CUDA error of the launch.
 // fold: 0 the tables as they are, 1 folded by r on the way in, 2 base tables bound to two challenges at once (args.bind)
 cudaError_t launch_round(int D, int shape, int points, int nt_used, int fold, const RoundArgs &args, int grid, size_t smem,
                          cudaStream_t stream);

@@ -45,17 +45,6 @@ template <int D> __device__ __forceinline__ void store_ext(u32 *p, const Ext<D> 
 #pragma unroll
     for (int q = 0; q < D; q += 4) *reinterpret_cast<uint4 *>(p + q) = make_uint4(e.v[q], e.v[q + 1], e.v[q + 2], e.v[q + 3]);
 }
-// Asynchronous copies from global to shared memory (cp.async, 8 or 16 bytes each): the data of a thread's next pair
-// is on its way while the thread works on the current one, without holding registers.
-__device__ __forceinline__ void cp_async8(void *smem, const void *gmem) {
-    asm volatile("cp.async.ca.shared.global [%0], [%1], 8;" ::"r"((unsigned)__cvta_generic_to_shared(smem)), "l"(gmem) : "memory");
-}
-__device__ __forceinline__ void cp_async16(void *smem, const void *gmem) {
-    asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"((unsigned)__cvta_generic_to_shared(smem)), "l"(gmem) : "memory");
-}
-__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
-__device__ __forceinline__ void cp_async_wait_all() { asm volatile("cp.async.wait_group 0;" ::: "memory"); }
-
 template <int D> __device__ __forceinline__ Ext<D> lift(u32 x) { Ext<D> e = ezero<D>(); e.v[0] = x; return e; }
 
 template <int D, int NT> __device__ __forceinline__ Ext<D> pick(const Ext<D> (&val)[NT], int idx) {
@@ -340,45 +329,10 @@ __global__ void __launch_bounds__(ROUND_THREADS, NT > 4 ? 1 : (D == 8 ? SC_MINBL
     };
 
     const u64 chunk = L > (u32)ROUND_THREADS ? L : ROUND_THREADS;
-    // the thread's k-th pair: the chunks go round the blocks, and a thread takes pairs tid, tid + 256, .. of a chunk
-    const int perlog = a.logL > 8 ? a.logL - 8 : 0;   // chunk / ROUND_THREADS = 2^perlog
-    auto pair_of = [&](u64 k) {
-        return ((u64)blockIdx.x + (k >> perlog) * (u64)gridDim.x) * chunk + (u64)tid + ((k & ((1ull << perlog) - 1)) << 8);
-    };
-    constexpr bool STAGED = round_is_staged(D, NT, FOLD);
-    // staging area: after the low weights; per stage, table t's entries at toff[t]: base pairs 8 bytes per thread,
-    // extension pairs as two rows of 16 bytes per thread
-    char *const stage_base = reinterpret_cast<char *>(smem) + (a.use_low ? (size_t)L * 2 * D * 4 : 0);
-    u32 toff[NT], stage_bytes = 0;
-#pragma unroll
-    for (int t = 0; t < NT; t++) { toff[t] = stage_bytes; stage_bytes += ((base_mask >> t) & 1) ? ROUND_THREADS * 8 : ROUND_THREADS * 32; }
-    auto prefetch = [&](u64 i, u32 stage) {
-        char *sp = stage_base + stage * stage_bytes;
-#pragma unroll
-        for (int t = 0; t < NT; t++) {
-            if ((base_mask >> t) & 1) cp_async8(sp + toff[t] + tid * 8, a.src[t] + 2 * i);
-            else {
-                cp_async16(sp + toff[t] + tid * 16, a.src[t] + (2 * i) * D);
-                cp_async16(sp + toff[t] + ROUND_THREADS * 16 + tid * 16, a.src[t] + (2 * i + 1) * D);
-            }
-        }
-    };
-    if (STAGED) {
-        const u64 i0 = pair_of(0);
-        if (i0 < a.npairs) prefetch(i0, 0);
-        cp_async_commit();
-    }
-    for (u64 k = 0;; k++) {
-        {
-            const u64 i = pair_of(k);
+    for (u64 base = (u64)blockIdx.x * chunk; base < a.npairs; base += (u64)gridDim.x * chunk) {
+        for (u64 q = tid; q < chunk; q += ROUND_THREADS) {
+            const u64 i = base + q;
             if (i >= a.npairs) break;
-            if (STAGED) {   // this pair's entries have arrived; the next pair's set out
-                cp_async_wait_all();
-                const u64 inext = pair_of(k + 1);
-                if (inext < a.npairs) prefetch(inext, (u32)((k + 1) & 1));
-                cp_async_commit();
-            }
-            const char *const sp = stage_base + (u32)(k & 1) * stage_bytes;
             const u64 h = i >> a.logL;
             if (h != cur_h) {
                 if (cur_h != ~0ull) flush();
@@ -386,19 +340,9 @@ __global__ void __launch_bounds__(ROUND_THREADS, NT > 4 ? 1 : (D == 8 ? SC_MINBL
             }
             // F_p^4: every load of the pair first, so that they are all in flight together; F_p^8: table by
             // table (the entries of four tables at once would not fit the register file)
-            constexpr bool HOIST = D == 4 && NT <= 4 && !STAGED;
+            constexpr bool HOIST = D == 4 && NT <= 4;
             auto load_table = [&](int t, Ext<D> (&et)[NE]) {
-                if (STAGED) {
-                    if ((base_mask >> t) & 1) {
-                        const uint2 w = *reinterpret_cast<const uint2 *>(sp + toff[t] + tid * 8);
-                        et[0].v[0] = w.x; et[1 % NE].v[0] = w.y;
-                    } else {
-                        const uint4 w0 = *reinterpret_cast<const uint4 *>(sp + toff[t] + tid * 16);
-                        const uint4 w1 = *reinterpret_cast<const uint4 *>(sp + toff[t] + ROUND_THREADS * 16 + tid * 16);
-                        et[0].v[0] = w0.x; et[0].v[1] = w0.y; et[0].v[2] = w0.z; et[0].v[3] = w0.w;
-                        et[1 % NE].v[0] = w1.x; et[1 % NE].v[1] = w1.y; et[1 % NE].v[2] = w1.z; et[1 % NE].v[3] = w1.w;
-                    }
-                } else if (FOLD == 2) {
+                if (FOLD == 2) {
                     const uint4 w0 = __ldcs(reinterpret_cast<const uint4 *>(a.src[t]) + 2 * i), w1 = __ldcs(reinterpret_cast<const uint4 *>(a.src[t]) + 2 * i + 1);
                     et[0].v[0] = w0.x; et[0].v[1] = w0.y; et[0].v[2] = w0.z; et[0].v[3] = w0.w;
                     et[1].v[0] = w1.x; et[1].v[1] = w1.y; et[1].v[2] = w1.z; et[1].v[3] = w1.w;
@@ -412,7 +356,7 @@ __global__ void __launch_bounds__(ROUND_THREADS, NT > 4 ? 1 : (D == 8 ? SC_MINBL
                     }
                 } else {
 #pragma unroll
-                    for (int k2 = 0; k2 < NE; k2++) et[k2] = load_ext<D>(a.src[t] + (NE * i + k2) * D);
+                    for (int k = 0; k < NE; k++) et[k] = load_ext<D>(a.src[t] + (NE * i + k) * D);
                 }
             };
             Ext<D> e[HOIST ? NT : 1][NE];
