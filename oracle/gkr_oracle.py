@@ -247,6 +247,15 @@ def _receive_finals(rp, tables, D):
 def verify_upper(tr_label, D, messages, n, k, lookups, label="gkr"):
     """:91-145.  Returns (roots, ri, rb, cp, cq); raises VerificationFailure."""
     rp = _Replay(tr_label, D, messages)
+    out = verify_upper_on(rp, n, k, lookups, label)
+    if not rp.finished():
+        raise VerificationFailure("messages left over")
+    return out
+
+
+def verify_upper_on(rp, n, k, lookups, label="gkr"):
+    """VERIFY-UPPER on a running verifier transcript (a caller such as VERIFY-DOMAIN goes on after it)."""
+    D = rp.tr.degree
     lk = block_bits(k)
     roots = []
     for _ in range(lookups):
@@ -287,6 +296,4 @@ def verify_upper(tr_label, D, messages, n, k, lookups, label="gkr"):
         cp, cq = next_claims(D, dict(finals), lookups, tt)
         ri = rho + [tt]
         rb = rbn
-    if not rp.finished():
-        raise VerificationFailure("messages left over")
     return roots, ri, rb, cp, cq
