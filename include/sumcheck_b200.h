@@ -286,6 +286,38 @@ int sc_gkr_prove_upper(sc_ctx *const *ctxs, int lookups, sc_transcript *tr, int 
                        const uint32_t *const *leaves_q, int leaves_on_device, const char *label, uint32_t *ri, uint32_t *rb,
                        uint32_t *cp, uint32_t *cq);
 
+/* PROVE-DOMAIN (src/domain.lisp:336-372): a domain of BLOCKS blocks of 2^N elements with base-field columns,
+   constraints that must vanish everywhere and lookups, proved by one batched LogUp-GKR over the lookups' trees
+   (sc_gkr_prove_upper) and one sumcheck over the halves of the columns (sc_prove), with the reference's messages
+   and challenges.  The domain is data, as in MAKE-DOMAIN (:39-53):
+     column   NAME; KIND 0 :full (every variable), 1 :row C (the variables from C on), 2 :col C (the variables
+              below C); SHARED: the same in every block (never a :full column); DATA in host memory: K 2^N words
+              (:full), K 2^(N-C) (:row), K 2^C (:col), without the factor K when shared
+     constraints  forms over the column names, as text
+     lookup   TAG, VALUES and NUM (or NULL): forms; a leaf of the lookup's tree is NUM / (Z - TAG - sum_i BETA_i VALUE_i)
+   With MERGE the block index is bound inside the protocol (a second sumcheck) and a claim is one value. */
+typedef struct sc_domain_column { const char *name; int kind; int c; int shared; const uint32_t *data; } sc_domain_column;
+typedef struct sc_domain_lookup { const char *tag; int nvalues; const char *const *values; const char *num; } sc_domain_lookup;
+typedef struct sc_domain {
+    const char *name;
+    int n, blocks, merge;
+    int ncolumns; const sc_domain_column *columns;
+    int nconstraints; const char *const *constraints;
+    int nlookups; const sc_domain_lookup *lookups;
+} sc_domain;
+/* DOMAIN-STATEMENT (:104-125) as text (STATEMENT, CAP bytes; SC_EINVAL when it does not fit), the number of tables
+   of the sumcheck (DOMAIN-TABLES, :60-78: two per column that depends on the top in-block variable), and
+   DOMAIN-DEGREE (:127-156) of the main sumcheck and of the block phase.  Any output may be NULL. */
+int sc_domain_statement(const sc_domain *domain, char *statement, size_t cap, int *ntables, int *degree, int *block_degree);
+/* CTXS: max(1, lookups) contexts on the current device, without a communicator (the first also proves the
+   sumcheck; a statement wider than one kernel runs in parts on its children).  Z (D words) and BETAS (NBETAS
+   elements, at least the lookups' largest number of values) are the lookup challenges, drawn by the caller.
+   LABEL: NULL for "dom".  Outputs, the column claims (DOMAIN-CLAIMS, :179-210), any may be NULL: for column c,
+   POINT_LEN[c] elements at POINTS + c (N + ceil(log2 K)) D and VALUE_ROWS[c] elements at VALUES + c K D (one
+   value when merged or shared, else K). */
+int sc_prove_domain(sc_ctx *const *ctxs, int nctx, sc_transcript *tr, const sc_domain *domain, const uint32_t *z, const uint32_t *betas,
+                    int nbetas, const char *label, int *point_len, uint32_t *points, int *value_rows, uint32_t *values);
+
 #ifdef __cplusplus
 }
 #endif

@@ -32,7 +32,7 @@ SYMBOLS = [
     "sc_transcript_challenge_base", "sc_transcript_challenge_bits", "sc_transcript_digest",
     "sc_transcript_message_count", "sc_transcript_message", "sc_transcript_sent_bytes", "sc_transcript_encode",
     "sc_lower_statement", "sc_prove", "sc_borrow_table", "sc_transcript_degree", "sc_gkr_prove_upper", "sc_reserve", "sc_workspace", "sc_child", "sc_attach_transcript", "sc_transcript_state",
-    "sc_transcript_device_round", "sc_attach_transcript_state", "sc_set_device_transcript",
+    "sc_transcript_device_round", "sc_attach_transcript_state", "sc_set_device_transcript", "sc_domain_statement", "sc_prove_domain",
 ]
 
 
@@ -468,3 +468,94 @@ def gkr_prove_upper(tr, n, k, leaves, label="gkr", provers=None):
                 _check(rc, p._h)
         _check(rc)
     return ri[:n - 1].tolist(), rb[:lk].tolist(), cp.tolist(), cq.tolist()
+
+
+# ------------------------------------------------------------------ domains (reference src/domain.lisp)
+
+class _DomainColumn(C.Structure):
+    _fields_ = [("name", C.c_char_p), ("kind", C.c_int), ("c", C.c_int), ("shared", C.c_int), ("data", _u32p)]
+
+
+class _DomainLookup(C.Structure):
+    _fields_ = [("tag", C.c_char_p), ("nvalues", C.c_int), ("values", C.POINTER(C.c_char_p)), ("num", C.c_char_p)]
+
+
+class _Domain(C.Structure):
+    _fields_ = [("name", C.c_char_p), ("n", C.c_int), ("blocks", C.c_int), ("merge", C.c_int),
+                ("ncolumns", C.c_int), ("columns", C.POINTER(_DomainColumn)),
+                ("nconstraints", C.c_int), ("constraints", C.POINTER(C.c_char_p)),
+                ("nlookups", C.c_int), ("lookups", C.POINTER(_DomainLookup))]
+
+
+KINDS = {"full": 0, "row": 1, "col": 2}
+
+
+class Domain:
+    """The reference's (make-domain :name :n :blocks :merge :columns :constraints :lookups), src/domain.lisp:39-53.
+
+    columns: (name, kind, c, shared, data) with kind "full", "row" or "col" and data a vector of base elements;
+    constraints: forms as text; lookups: dicts with "tag", "values" (forms) and optionally "num".
+    """
+
+    def __init__(self, name, n, blocks=1, merge=False, columns=(), constraints=(), lookups=()):
+        self.name, self.n, self.blocks, self.merge = name, n, blocks, merge
+        self.columns = [(nm, kind, c, shared, _u32(data)) for nm, kind, c, shared, data in columns]
+        self.constraints, self.lookups = list(constraints), list(lookups)
+        self._keep = []
+        cols = (_DomainColumn * max(len(self.columns), 1))()
+        for i, (nm, kind, c, shared, data) in enumerate(self.columns):
+            cols[i] = _DomainColumn(nm.encode(), KINDS[kind], c, 1 if shared else 0, _ptr(data))
+        cons = _strs(self.constraints)
+        looks = (_DomainLookup * max(len(self.lookups), 1))()
+        for i, lk in enumerate(self.lookups):
+            vals = _strs(list(lk.get("values", [])))
+            self._keep.append(vals)
+            looks[i] = _DomainLookup(lk["tag"].encode(), len(lk.get("values", [])), vals, lk["num"].encode() if lk.get("num") is not None else None)
+        self._keep += [cols, cons, looks]
+        self.struct = _Domain(name.encode(), n, blocks, 1 if merge else 0, len(self.columns), cols, len(self.constraints), cons,
+                              len(self.lookups), looks)
+
+    def statement(self):
+        """(statement text, number of tables, degree, degree of the block phase): DOMAIN-STATEMENT, DOMAIN-TABLES, DOMAIN-DEGREE."""
+        buf = C.create_string_buffer(1 << 16)
+        nt, deg, bdeg = C.c_int(), C.c_int(), C.c_int()
+        _check(library().sc_domain_statement(C.byref(self.struct), buf, C.c_size_t(1 << 16), C.byref(nt), C.byref(deg), C.byref(bdeg)))
+        return buf.value.decode(), nt.value, deg.value, bdeg.value
+
+
+_domain_provers = []
+
+
+def prove_domain(tr, domain, z, betas, label="dom", provers=None):
+    """The reference's (prove-domain tr domain z betas :label label), src/domain.lisp:336-372.
+
+    Returns the column claims, a list of (name, point, value): value is one element when the domain is merged,
+    else a list of the blocks' elements (one for a shared column).
+    """
+    D = tr.degree
+    need = max(1, len(domain.lookups))
+    if provers is None:
+        while len(_domain_provers) < need:
+            _domain_provers.append(Prover(0))
+        provers = _domain_provers[:need]
+    lk = (domain.blocks - 1).bit_length()
+    ncol, K, n = len(domain.columns), domain.blocks, domain.n
+    za = _u32(z)
+    ba = _u32(betas).reshape(-1, D)
+    point_len = (C.c_int * ncol)()
+    value_rows = (C.c_int * ncol)()
+    points = np.zeros((ncol, n + lk, D), dtype=np.uint32)
+    values = np.zeros((ncol, K, D), dtype=np.uint32)
+    ctxs = (C.c_void_p * len(provers))(*[p._h.value for p in provers])
+    rc = library().sc_prove_domain(ctxs, len(provers), C.c_void_p(tr._h), C.byref(domain.struct), _ptr(za), _ptr(ba), len(ba), label.encode(),
+                                   point_len, _ptr(points), value_rows, _ptr(values))
+    if rc:
+        for p in provers:
+            if library().sc_last_error(p._h).decode():
+                _check(rc, p._h)
+        _check(rc)
+    out = []
+    for i, (name, _, _, shared, _) in enumerate(domain.columns):
+        vals = values[i, :value_rows[i]].tolist()
+        out.append((name.lower(), points[i, :point_len[i]].tolist(), vals[0] if domain.merge else vals))
+    return out

@@ -220,3 +220,47 @@ def test_device_transcript_code_against_the_oracle_transcript():
         ta.send(values); tb.send(values)
         want = tb.challenge()
         assert ta.challenge() == want and list(chal)[:d] == want
+
+
+def toy_columns(n, k, seed=5):
+    """The reference's toy domain (tests/tests.lisp:487-512): every kind of column."""
+    rng = np.random.default_rng(seed)
+    size = 1 << n
+    a = rng.integers(0, 2, size=k * size, dtype=np.uint32)
+    b = rng.integers(0, P, size=k * size, dtype=np.uint32)
+    c = ((a.astype(np.uint64) * b) % P).astype(np.uint32)
+    return [("a", "full", 0, False, a), ("b", "full", 0, False, b), ("c", "full", 0, False, c),
+            ("m", "row", 1, True, rng.integers(0, P, size=1 << (n - 1), dtype=np.uint32)),
+            ("s", "col", n, True, rng.integers(0, 2, size=size, dtype=np.uint32)),
+            ("kb", "row", n, False, rng.integers(0, P, size=k, dtype=np.uint32)),
+            ("w", "col", 2, False, rng.integers(0, P, size=k * 4, dtype=np.uint32))]
+
+
+TOY_CONSTRAINTS = ["(* a (- a 1))", "(- c (* a b))", "(* s (- s 1) m)"]
+TOY_LOOKUPS = [dict(tag="5", values=["a", "b"]), dict(tag="7", values=["c", "m", "w"], num="(+ s 2)"), dict(tag="9", values=["kb"])]
+
+
+@pytest.mark.parametrize("n,k,merge,lookups,constraints", [(3, 3, False, True, True), (2, 1, True, True, True), (4, 4, True, True, False),
+                                                         (3, 2, False, False, True), (5, 3, False, True, True)])
+def test_domain_statement_and_degree_match_the_oracle(n, k, merge, lookups, constraints):
+    # DOMAIN-STATEMENT, DOMAIN-TABLES and DOMAIN-DEGREE (reference src/domain.lisp:60-156): the library's text and degrees
+    # against the oracle's restatement, form for form
+    from oracle import domain_oracle as dom
+    cols = toy_columns(n, k)
+    mine = sb.Domain("12.toy", n, k, merge, cols, TOY_CONSTRAINTS if constraints else [], TOY_LOOKUPS if lookups else [])
+    theirs = dom.Domain("12.toy", n, k, merge, [dom.Column(nm, kind, c, sh, data) for nm, kind, c, sh, data in cols],
+                        TOY_CONSTRAINTS if constraints else [], TOY_LOOKUPS if lookups else [])
+    text, ntables, degree, block_degree = mine.statement()
+    assert text == dom.show(dom.domain_statement(theirs))
+    assert ntables == len(dom.domain_tables(theirs))
+    assert degree == dom.domain_degree(theirs) and block_degree == dom.domain_degree(theirs, block_phase=True)
+
+
+def test_domain_arguments_are_checked():
+    cols = toy_columns(3, 2)
+    with pytest.raises(sb.InvalidParameter):          # n at least 2 (reference src/domain.lisp:44)
+        sb.Domain("d", 1, 2, False, cols, [], []).statement()
+    with pytest.raises(sb.InvalidParameter):          # a :full column is never shared (:48-49)
+        sb.Domain("d", 3, 2, False, [("a", "full", 0, True, cols[0][4])], [], []).statement()
+    with pytest.raises(sb.InvalidParameter):          # a form that does not read
+        sb.Domain("d", 3, 2, False, cols, ["(* a (- a 1)"], []).statement()
