@@ -1340,7 +1340,8 @@ static int enqueue_round(sc_ctx *ctx, int j, bool fold, bool chain, bool chain_f
 
     const u64 chunk = (1ull << a.logL) > (u64)ROUND_THREADS ? (1ull << a.logL) : (u64)ROUND_THREADS;
     u64 chunks = (a.npairs + chunk - 1) / chunk;
-    const u64 max_grid = (u64)ctx->sms * ctx->blocks_per_sm;
+    u64 max_grid = (u64)ctx->sms * ctx->blocks_per_sm;
+    if (all_base && ctx->blocks_per_sm == 2) max_grid = (u64)ctx->sms * round_base_blocks_per_sm(D, ctx->shape, ctx->points, ctx->base_groups);
     int grid = (int)(chunks < max_grid ? chunks : max_grid);
     if (grid < 1) grid = 1;
     const size_t smem = a.use_low ? ((size_t)1 << a.logL) * 2 * D * 4 : 0;

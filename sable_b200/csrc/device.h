@@ -166,6 +166,14 @@ bool round_supported(int D, int points, int nt_used);
 // The round on tables that are all in the base field (no fold): see RoundArgs::ngroups.
 cudaError_t launch_round_base(int D, int shape, int points, int nt_used, int ngroups, const RoundArgs &args, int grid, size_t smem,
                               cudaStream_t stream);
+// Blocks of that kernel an SM holds: three where the sums are few enough for 80 registers a thread (the built-in
+// statements at D = 4 with at most 16 words of sums), else two.  The grid is sized to match.
+#ifdef __CUDACC__
+__host__ __device__
+#endif
+constexpr int round_base_blocks_per_sm(int D, int shape, int points, int ngroups) {
+    return D == 4 && shape != SHAPE_GENERIC && ngroups * points * D <= 16 && points <= 3 ? 3 : 2;
+}
 // a listed statement in that kernel: the number of sums it keeps (0: it cannot run there) and the sum of a term
 int listed_base_groups(int shape);
 int listed_base_group_of(int shape, int term);

@@ -28,7 +28,7 @@ template <class S> __host__ __device__ constexpr int listed_group(int t) { retur
 
 // SHAPE: SHAPE_GENERIC (term descriptors from the arguments, kept in registers), SHAPE_PRODUCT, or a listed statement
 template <int D, int PTS, int NT, int NG, int SHAPE>
-__global__ void __launch_bounds__(ROUND_THREADS, 2) round_base_kernel(const __grid_constant__ RoundArgs a) {
+__global__ void __launch_bounds__(ROUND_THREADS, round_base_blocks_per_sm(D, SHAPE, PTS, NG)) round_base_kernel(const __grid_constant__ RoundArgs a) {
     extern __shared__ __align__(16) u32 smem[];
     constexpr int W = NG * PTS * D;
     __shared__ u32 red[ROUND_THREADS / 32][W];
