@@ -130,6 +130,28 @@ def host_cores():
         return max(1, os.cpu_count() or 1)
 
 
+def bind_near_gpu(index):
+    """Run this process on the host cores next to GPU INDEX, so that the pinned buffers it allocates from now on lie on
+    that GPU's NUMA node (first touch).  Returns (the affinity before, the NUMA node or None)."""
+    before = None
+    try:
+        import torch
+        before = os.sched_getaffinity(0)
+        p = torch.cuda.get_device_properties(index)
+        base = "/sys/bus/pci/devices/%04x:%02x:%02x.0/" % (p.pci_domain_id, p.pci_bus_id, p.pci_device_id)
+        cpus = set()
+        for part in open(base + "local_cpulist").read().strip().split(","):
+            lo, _, hi = part.partition("-")
+            cpus.update(range(int(lo), int(hi or lo) + 1))
+        node = int(open(base + "numa_node").read().strip())
+        cpus &= before
+        if cpus:
+            os.sched_setaffinity(0, cpus)
+        return before, node
+    except (OSError, ValueError, AttributeError, RuntimeError):
+        return before, None
+
+
 def cpu_port(cfg, D, n_sample, steps, warmup, threads=0):
     """The CPU oracle (a port of the reference prover) on a bounded sample of the workload: Mentries/s."""
     from oracle import pyoracle as orc
@@ -419,7 +441,9 @@ def main():
 
     # end to end: the tables start in pinned host memory and are uploaded inside the timed region
     e2e = None
+    affinity_before, numa_node = None, None
     if not args.no_e2e:
+        affinity_before, numa_node = bind_near_gpu(local_rank)      # the pinned buffers below: on this GPU's NUMA node
         host = []
         for slot, (name, _, _) in enumerate(cfg["tables"]):
             words = strides[slot] << n_loc
@@ -434,8 +458,23 @@ def main():
         assert etr.proof() == proof_bytes and eout == out, "the end-to-end proof differs from the resident one"
         h2d = sum(4 * (strides[s] << n_loc) for s in range(len(strides))) + eq.nbytes + 4 * D * len(constants)
         d2h = 4 * D * (n * max(len(tr.messages[0]) if n else 1, 1) + len(strides))
+        # the uploads alone, per rank (all ranks at once, as in the proof): the slowest rank's rate
+        barrier()
+        t0 = time.perf_counter()
+        for slot, (_, _, t) in enumerate(host):
+            prover.upload_pointer(slot, t.data_ptr(), 1 << n_loc, strides[slot])
+        torch.cuda.synchronize()
+        up_s = time.perf_counter() - t0
+        up_gbs = sum(4 * (strides[s] << n_loc) for s in range(len(strides))) / up_s / 1e9
+        if world > 1:
+            t = torch.tensor([up_gbs], dtype=torch.float64, device="cuda")
+            dist.all_reduce(t, op=dist.ReduceOp.MIN)
+            up_gbs = t.item()
         e2e = {"value": (1 << n) / (ewall / e2e_steps * 1e-3) / 1e6, "unit": "Mentries/s", "h2d_bytes_per_step": h2d * world,
-               "d2h_bytes_per_step": d2h, "steps": e2e_steps, "ms_per_step": ewall / e2e_steps}
+               "d2h_bytes_per_step": d2h, "steps": e2e_steps, "ms_per_step": ewall / e2e_steps,
+               "h2d_gbs_slowest_rank": round(up_gbs, 2), "pinned_on_numa_node": numa_node}
+        if affinity_before:
+            os.sched_setaffinity(0, affinity_before)
 
     clocks = sampler.stop() if rank == 0 else None
     cpu = None

@@ -19,6 +19,7 @@ bool round_supported(int D, int points, int nt_used) {
     return points <= FAST_POINTS || nt_used <= 4;   // degree above four: at most four tables in the statement
 }
 cudaError_t launch_round(int D, int shape, int points, int nt_used, int fold, const RoundArgs &args, int grid, size_t smem, cudaStream_t stream) {
+    if (fold == 2 && (points > 3 || nt_used > 3)) return cudaErrorInvalidValue;
     if (points > FAST_POINTS) {
         if (fold == 2 || nt_used > 4) return cudaErrorInvalidValue;
         return D == 4 ? launch_round_d4h(points, nt_used, fold, args, grid, smem, stream) : launch_round_d8h(points, nt_used, fold, args, grid, smem, stream);

@@ -107,6 +107,7 @@ struct sc_ctx {
     int st_e = 0;                    // e of the statement (see DevTerm)
     u32 st_re = 0;                   // R^e in Montgomery form
     u32 seq = 0;                     // number of the last round launch; the kernel posts it after the sums
+    bool sv_statement = false;       // the statement can take the small-value rounds: base-field coefficients, few short terms
     int base_groups = 0;             // > 0: the statement can run the base-table kernel with this many groups
     u32 gcoef[2][8];                 // the groups' coefficients (Montgomery form)
     int shape = SHAPE_GENERIC;       // the kernel family of the statement
@@ -645,6 +646,12 @@ extern "C" int sc_set_statement(sc_ctx *ctx, int D, int points, int ntables, int
             }
         }
     }
+    {   // the small-value rounds: every coefficient in the base field, terms within the base-table kernel's descriptors
+        bool ok = nterms >= 1 && nterms <= BASE_MAX_TERMS && nt_used >= 1 && nt_used <= 3 && points <= 3;
+        for (int t = 0; t < nterms && ok; t++) ok = ctx->st.terms[t].ckind != CK_EXT && ctx->st.terms[t].nf <= BASE_MAX_FACTORS;
+        if (shape == SHAPE_PRODUCT) ok = nt_used <= 3;   // its coefficient, whatever it is, rides in the final factor
+        ctx->sv_statement = ok;
+    }
     ctx->have_statement = true;
     ctx->begun = false;
     return SC_OK;
@@ -977,7 +984,9 @@ extern "C" int sc_begin(sc_ctx *ctx, int n, const uint32_t *eq, int K, const uin
     // base tables, large enough for split weights, on one GPU, one block
     {
         const char *env = getenv("SABLE_B200_SMALL_VALUES");
-        bool ok = !(env && env[0] == '0') && ctx->shape == SHAPE_PRODUCT && K == 1 && n >= 3 && ctx->gather_round > 2 &&
+        // any statement over base tables whose coefficients are base-field elements: what the reference takes this way
+        // (no constants, src/sumcheck.lisp:535-539), as far as the base-table kernel's descriptors reach
+        bool ok = !(env && env[0] == '0') && !ctx->force_generic && ctx->sv_statement && K == 1 && n >= 3 && ctx->gather_round > 2 &&
                   small_values_supported(D, ctx->points + 1, ctx->nt_used) && ctx->plan[1].logL >= 8;
         for (int s = 0; s < ctx->ntables && ok; s++) ok = ctx->tab[s].stride == 1;
         ctx->sv_ok = ok;
@@ -1038,20 +1047,29 @@ static int gather_tables(sc_ctx *ctx) {
     return SC_OK;
 }
 
-// ---- host arithmetic on canonical F_p^4 elements, for the handful of products the small-value rounds need
+// ---- host arithmetic on canonical extension elements (D = 4 or 8), for the handful of products the small-value rounds need
 namespace {
-struct E4 { u32 v[4]; };
-E4 e4_mul(const E4 &a, const E4 &b) {   // REDC(a * bR) = a b
-    Ext<4> x, y;
-    for (int c = 0; c < 4; c++) { x.v[c] = a.v[c]; y.v[c] = to_mont(b.v[c]); }
-    const Ext<4> z = emul<4>(x, y);
-    E4 o; for (int c = 0; c < 4; c++) o.v[c] = z.v[c];
+struct EX { u32 v[8]; };
+EX ex_mul(int D, const EX &a, const EX &b) {   // REDC(a * bR) = a b
+    EX o = {};
+    if (D == 4) {
+        Ext<4> x, y;
+        for (int c = 0; c < 4; c++) { x.v[c] = a.v[c]; y.v[c] = to_mont(b.v[c]); }
+        const Ext<4> z = emul<4>(x, y);
+        for (int c = 0; c < 4; c++) o.v[c] = z.v[c];
+    } else {
+        Ext<8> x, y;
+        for (int c = 0; c < 8; c++) { x.v[c] = a.v[c]; y.v[c] = to_mont(b.v[c]); }
+        const Ext<8> z = emul<8>(x, y);
+        for (int c = 0; c < 8; c++) o.v[c] = z.v[c];
+    }
     return o;
 }
-E4 e4_add(const E4 &a, const E4 &b) { E4 o; for (int c = 0; c < 4; c++) o.v[c] = fadd(a.v[c], b.v[c]); return o; }
-E4 e4_sub(const E4 &a, const E4 &b) { E4 o; for (int c = 0; c < 4; c++) o.v[c] = fsub(a.v[c], b.v[c]); return o; }
-E4 e4_base(u32 x) { E4 o = {{x, 0, 0, 0}}; return o; }
-E4 e4_scale(const E4 &a, u32 s) { E4 o; for (int c = 0; c < 4; c++) o.v[c] = (u32)(((u64)a.v[c] * s) % P); return o; }
+EX ex_add(const EX &a, const EX &b) { EX o; for (int c = 0; c < 8; c++) o.v[c] = fadd(a.v[c], b.v[c]); return o; }
+EX ex_sub(const EX &a, const EX &b) { EX o; for (int c = 0; c < 8; c++) o.v[c] = fsub(a.v[c], b.v[c]); return o; }
+EX ex_base(u32 x) { EX o = {{x, 0, 0, 0, 0, 0, 0, 0}}; return o; }
+EX ex_scale(const EX &a, u32 s) { EX o; for (int c = 0; c < 8; c++) o.v[c] = (u32)(((u64)a.v[c] * s) % P); return o; }
+EX ex_load(int D, const u32 *w) { EX o = {}; memcpy(o.v, w, 4 * (size_t)D); return o; }
 u32 fp_inv(u32 a) { u64 r = 1, x = a; for (u64 e = P - 2; e; e >>= 1) { if (e & 1) r = r * x % P; x = x * x % P; } return (u32)r; }
 }  // namespace
 
@@ -1072,6 +1090,7 @@ static int sv_round0(sc_ctx *ctx, uint32_t *sums) {
     for (int c = 0; c < D; c++) a.post[c] = ctx->use_factor ? mmul(to_mont(ctx->st_factor[c]), ctx->st_re) : (c == 0 ? ctx->st_re : 0u);
     if (sharded && ctx->use_post) ext_mul_host(D, a.post, ctx->post, a.post);   // this rank's eq weight
     a.partials = ctx->d_partials; a.counter = ctx->d_counter;
+    a.st = ctx->st;
     a.seq = ++ctx->seq;
     if (sharded) {
         int rc;
@@ -1090,7 +1109,7 @@ static int sv_round0(sc_ctx *ctx, uint32_t *sums) {
         while (ctx->ev.size() < 2) { cudaEvent_t e; CU(cudaEventCreate(&e)); ctx->ev.push_back(e); }
         CU(cudaEventRecord(ctx->ev[0], ctx->stream));
     }
-    CU(launch_small_values(D, G, ctx->nt_used, a, grid, ctx->stream));
+    CU(launch_small_values(D, ctx->shape, G, ctx->nt_used, a, grid, ctx->stream));
     ctx->launches++;
     if (ctx->timing) CU(cudaEventRecord(ctx->ev[1], ctx->stream));
     if (sharded) {   // every rank's accumulators, then their sum mod p
@@ -1111,13 +1130,13 @@ static int sv_round0(sc_ctx *ctx, uint32_t *sums) {
         ctx->stats.push_back(st);
     }
     memcpy(ctx->sv_A, ctx->h_sv, (size_t)Z * D * 4);
-    const E4 *A = reinterpret_cast<const E4 *>(ctx->sv_A);
-    E4 w0 = e4_base(1), w1 = e4_base(1);
-    if (ctx->have_eq) { E4 r1; memcpy(r1.v, ctx->eq1, 16); w1 = r1; w0 = e4_sub(e4_base(1), r1); }
+    auto A = [&](int z) { return ex_load(D, ctx->sv_A + (size_t)z * D); };
+    EX w0 = ex_base(1), w1 = ex_base(1);
+    if (ctx->have_eq) { const EX r1 = ex_load(D, ctx->eq1); w1 = r1; w0 = ex_sub(ex_base(1), r1); }
     for (int xi = 0; xi < ctx->points; xi++) {
         const int X = xi ? xi + 1 : 0;
-        const E4 g = e4_add(e4_mul(A[X], w0), e4_mul(A[X + G], w1));
-        memcpy(sums + (size_t)xi * D, g.v, 16);
+        const EX g = ex_add(ex_mul(D, A(X), w0), ex_mul(D, A(X + G), w1));
+        memcpy(sums + (size_t)xi * D, g.v, 4 * (size_t)D);
     }
     ctx->have_r = false;
     ctx->j = 1;
@@ -1127,25 +1146,25 @@ static int sv_round0(sc_ctx *ctx, uint32_t *sums) {
 // Round 1: g_1(X) = sum_v L_v(rho_0) A[v, X], L_v the Lagrange basis on the nodes 0 .. d (LAGRANGE-TENSOR, :463-474).
 static int sv_round1(sc_ctx *ctx, uint32_t *sums) {
     const int D = ctx->D, G = ctx->points + 1, d = ctx->points;
-    E4 rho; memcpy(rho.v, ctx->r, 16);
-    memcpy(ctx->sv_rho0, ctx->r, 16);
-    const E4 *A = reinterpret_cast<const E4 *>(ctx->sv_A);
-    E4 L[8];
+    const EX rho = ex_load(D, ctx->r);
+    memcpy(ctx->sv_rho0, ctx->r, 4 * (size_t)D);
+    auto A = [&](int z) { return ex_load(D, ctx->sv_A + (size_t)z * D); };
+    EX L[8];
     for (int v = 0; v <= d; v++) {
-        E4 num = e4_base(1);
+        EX num = ex_base(1);
         u32 den = 1;
         for (int j = 0; j <= d; j++) {
             if (j == v) continue;
-            num = e4_mul(num, e4_sub(rho, e4_base((u32)j)));
+            num = ex_mul(D, num, ex_sub(rho, ex_base((u32)j)));
             den = (u32)(((u64)den * (u32)((v - j + (long long)P) % P)) % P);
         }
-        L[v] = e4_scale(num, fp_inv(den));
+        L[v] = ex_scale(num, fp_inv(den));
     }
     for (int xi = 0; xi < ctx->points; xi++) {
         const int X = xi ? xi + 1 : 0;
-        E4 g = e4_base(0);
-        for (int v = 0; v <= d; v++) g = e4_add(g, e4_mul(A[v + G * X], L[v]));
-        memcpy(sums + (size_t)xi * D, g.v, 16);
+        EX g = ex_base(0);
+        for (int v = 0; v <= d; v++) g = ex_add(g, ex_mul(D, A(v + G * X), L[v]));
+        memcpy(sums + (size_t)xi * D, g.v, 4 * (size_t)D);
     }
     if (ctx->timing) { sc_round_stat st; st.kernel_ms = 0; st.bytes = 0; st.pairs = 0; ctx->stats.push_back(st); }
     ctx->have_r = false;
@@ -1293,9 +1312,9 @@ static int enqueue_round(sc_ctx *ctx, int j, bool fold, bool chain, bool chain_f
         else challenge_words(ctx, a.r);
     }
     if (bind2) {   // eq(rho0 rho1, b): bit 0 of b pairs with rho0 (EQ-TABLE, src/field.lisp:354-363)
-        E4 r0, r1; memcpy(r0.v, ctx->sv_rho0, 16); memcpy(r1.v, ctx->r, 16);
-        const E4 one = e4_base(1), n0 = e4_sub(one, r0), n1 = e4_sub(one, r1);
-        const E4 w[4] = {e4_mul(n0, n1), e4_mul(r0, n1), e4_mul(n0, r1), e4_mul(r0, r1)};
+        const EX r0 = ex_load(D, ctx->sv_rho0), r1 = ex_load(D, ctx->r);
+        const EX one = ex_base(1), n0 = ex_sub(one, r0), n1 = ex_sub(one, r1);
+        const EX w[4] = {ex_mul(D, n0, n1), ex_mul(D, r0, n1), ex_mul(D, n0, r1), ex_mul(D, r0, r1)};
         for (int b = 0; b < 4; b++) for (int c = 0; c < D; c++) a.bind[b][c] = to_mont(w[b].v[c]);
     }
     a.logL = pl.logL;

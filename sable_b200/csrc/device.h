@@ -178,12 +178,12 @@ constexpr int round_base_blocks_per_sm(int D, int shape, int points, int ngroups
 int listed_base_groups(int shape);
 int listed_base_group_of(int shape, int term);
 
-// The first two rounds of a product of base-field tables from one pass over the tables (the
+// The first two rounds of a statement over base-field tables from one pass over the tables (the
 // reference's small-value rounds with L0 = 2, src/sumcheck.lisp:319-337): for every block y of four
 // consecutive entries the tables' values on the grid {0..G-1}^2 of the two lowest variables are
-// made by additions, multiplied in the base field, and summed with the eq weights of the other
-// variables: A[z0 + G z1] = sum_y w(y) prod_t T_t(z0, z1, y).  The host reads both round messages
-// off A; the tables are then bound to both challenges at once on the way into round 2.
+// made by additions, the statement is evaluated on them in the base field, and the values are summed with
+// the eq weights of the other variables: A[z0 + G z1] = sum_y w(y) F(T_t(z0, z1, y)).  The host reads both round
+// messages off A; the tables are then bound to both challenges at once on the way into round 2.
 struct SvArgs {
     const u32 *src[SC_MAX_TABLES];
     u64 nblocks;          // blocks of four entries
@@ -198,10 +198,11 @@ struct SvArgs {
     u32 *out_dev;         // G * G * D canonical words (for the all-gather of several GPUs; may be NULL)
     u32 *out_host;        // the same in mapped host memory (may be NULL), then the word below
     u32 seq;              // posted at word SV_FLAG of out_host
+    DevStatement st;      // the statement, for the kernels that read the term table
 };
-constexpr int SV_MAX_WORDS = 64;   // G^2 D words: G <= 4 at D = 4
+constexpr int SV_MAX_WORDS = 128;  // G^2 D words: G <= 4, D <= 8
 constexpr int SV_FLAG = SV_MAX_WORDS;
-cudaError_t launch_small_values(int D, int G, int nt, const SvArgs &args, int grid, cudaStream_t stream);
+cudaError_t launch_small_values(int D, int shape, int G, int nt, const SvArgs &args, int grid, cudaStream_t stream);
 bool small_values_supported(int D, int G, int nt);
 
 // The last rounds in one launch.  Once the tables are small a round is all latency (launch,

@@ -553,19 +553,19 @@ static cudaError_t launch_round_dpns(int fold, const RoundArgs &args, int grid, 
     } else if (fold == 0) {
         if (smem > 40 * 1024) cudaFuncSetAttribute(round_kernel<D, PTS, NT, 0, SHAPE>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
         round_kernel<D, PTS, NT, 0, SHAPE><<<grid, ROUND_THREADS, smem, stream>>>(args);
+    } else if (fold == 2) {
+        // base tables bound to two challenges on the way in (after the small-value rounds: at most three tables, degree three)
+        if constexpr (NT <= 3 && PTS <= 3 && SHAPE != SHAPE_GKR) {
+            if (smem > 40 * 1024) cudaFuncSetAttribute(round_kernel<D, PTS, NT, 2, SHAPE>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+            round_kernel<D, PTS, NT, 2, SHAPE><<<grid, ROUND_THREADS, smem, stream>>>(args);
+        } else {
+            return cudaErrorInvalidValue;
+        }
     } else {
         return cudaErrorInvalidValue;
     }
     return cudaGetLastError();
 }
-// base tables bound to two challenges on the way in: only the product kernels have this variant
-template <int D, int NT>
-static cudaError_t launch_round_bind2(const RoundArgs &args, int grid, size_t smem, cudaStream_t stream) {
-    if (smem > 40 * 1024) cudaFuncSetAttribute(round_kernel<D, NT, NT, 2, SHAPE_PRODUCT>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-    round_kernel<D, NT, NT, 2, SHAPE_PRODUCT><<<grid, ROUND_THREADS, smem, stream>>>(args);
-    return cudaGetLastError();
-}
-
 template <int D, int PTS>
 static cudaError_t launch_round_dp(int nt, int fold, const RoundArgs &args, int grid, size_t smem, cudaStream_t stream) {
     switch (nt) {
@@ -580,15 +580,6 @@ static cudaError_t launch_round_dp(int nt, int fold, const RoundArgs &args, int 
 // The kernels with the statement built in: a product of nt tables at nt points, the GKR layer.
 template <int D>
 static cudaError_t launch_round_shape(int shape, int points, int nt, int fold, const RoundArgs &args, int grid, size_t smem, cudaStream_t stream) {
-    if (fold == 2) {
-        if (shape != SHAPE_PRODUCT || points != nt || D != 4) return cudaErrorInvalidValue;
-        switch (nt) {
-        case 1: return launch_round_bind2<4, 1>(args, grid, smem, stream);
-        case 2: return launch_round_bind2<4, 2>(args, grid, smem, stream);
-        case 3: return launch_round_bind2<4, 3>(args, grid, smem, stream);
-        default: return cudaErrorInvalidValue;
-        }
-    }
     if (shape == SHAPE_GKR && points == 2 && nt == 4) return launch_round_dpns<D, 2, 4, SHAPE_GKR>(fold, args, grid, smem, stream);
     if (shape == SHAPE_LISTED + 0) return launch_round_dpns<D, Listed<0>::PTS, Listed<0>::NT, SHAPE_LISTED + 0>(fold, args, grid, smem, stream);
     if (shape == SHAPE_LISTED + 1) return launch_round_dpns<D, Listed<1>::PTS, Listed<1>::NT, SHAPE_LISTED + 1>(fold, args, grid, smem, stream);

@@ -1,4 +1,5 @@
-// round_sv.cu -- rounds 0 and 1 of a product of base-field tables from one pass (see SvArgs).
+// round_sv.cu -- rounds 0 and 1 of a statement over base-field tables from one pass (see SvArgs): the reference's
+// small-value rounds (SMALL-VALUE-CODE and GRID-CODE, src/sumcheck.lisp:344-427) with L0 = 2.
 //
 // Work split: a thread keeps one low index l of the split eq weights and walks the high indices h
 // of its block's share, reading block y = h L + l of every table (one 128-bit load per table;
@@ -6,15 +7,25 @@
 // 64-bit sums, four blocks per reduction (four products below p^2 fit 64 bits, as in REDUCED-SUM,
 // src/field.lisp:213-218); the reduced sums wait in shared memory, and the low weight multiplies
 // once at the very end.  Blocks' rows are added by the last block to finish (no waiting).
-// With G > 2 the grid is cut in two along its second variable (blockIdx.y): rows z1 < 2, which
-// are the entries' own rows, and rows z1 >= 2; half the sums per thread lets two blocks share an SM.
+// The grid of G^2 points is cut along its second variable (blockIdx.y) so that a thread's sums fit its
+// registers: two rows per block at D = 4 (rows z1 < 2 are the entries' own rows), one row at D = 8.
+// The statement at a grid point is a product of the tables (SHAPE_PRODUCT), a listed statement resolved at
+// compile time, or the term table with its descriptors in registers, as in the base-table round kernel.
 #include "round_kernel.cuh"
 
 namespace sc {
 
-template <int D, int G, int NT>
+template <int NT> __device__ __forceinline__ u32 sv_pick(const u32 (&val)[NT], int idx) {
+    u32 o = val[0];
+#pragma unroll
+    for (int t = 1; t < NT; t++)
+        if (idx == t) o = val[t];
+    return o;
+}
+
+template <int D, int G, int NT, int SHAPE>
 __global__ void __launch_bounds__(ROUND_THREADS, G > 2 ? 2 : 1) sv_kernel(const __grid_constant__ SvArgs a) {
-    constexpr int ROWS1 = 2;                      // rows of the grid (values of z1) a block handles, at most
+    constexpr int ROWS1 = D == 4 ? 2 : 1;         // rows of the grid (values of z1) a block handles, at most
     constexpr int Z = G * ROWS1, W = Z * D;       // this block's share of the accumulators
     constexpr int WALL = G * G * D;               // all of them
     const int z1lo = blockIdx.y * ROWS1;          // its first row
@@ -28,6 +39,63 @@ __global__ void __launch_bounds__(ROUND_THREADS, G > 2 ? 2 : 1) sv_kernel(const 
     const u64 NH = a.nblocks >> a.logL;
     const u64 h0 = NH * hg / nhg, h1 = NH * (hg + 1) / nhg;
     const u32 l = lc * ROUND_THREADS + tid;
+
+    // the term table's descriptors in registers: factors | positions, and the base coefficient
+    const int nterms = a.st.nterms;
+    u32 desc[BASE_MAX_TERMS], coef[BASE_MAX_TERMS];
+#pragma unroll
+    for (int t = 0; t < BASE_MAX_TERMS; t++) {
+        desc[t] = 0; coef[t] = 0;
+        if (SHAPE != SHAPE_PRODUCT && t < nterms) {
+            const DevTerm &tm = a.st.terms[t];
+            u32 ds = (u32)tm.nf | ((u32)tm.ckind << 4);
+            for (int k = 0; k < BASE_MAX_FACTORS && k < tm.nf; k++) ds |= (u32)tm.f[k] << (8 + 4 * k);
+            desc[t] = ds;
+            coef[t] = tm.coeff[0];
+        }
+    }
+    // the statement on the tables' values at one grid point (base field; the factor R^-e the products leave behind
+    // is the final factor's business, as in every round kernel)
+    auto statement = [&](const u32 (&val)[NT]) -> u32 {
+        if (SHAPE == SHAPE_PRODUCT) {
+            u32 f = val[0];
+#pragma unroll
+            for (int t = 1; t < NT; t++) f = mmul(f, val[t]);
+            return f;
+        } else if (SHAPE >= SHAPE_LISTED) {
+            typedef Listed<(SHAPE >= SHAPE_LISTED ? SHAPE - SHAPE_LISTED : 0)> S;
+            u32 f = 0;
+#pragma unroll
+            for (int t = 0; t < S::NTERMS; t++) {
+                u32 pr = val[S::f(t, 0) < NT ? S::f(t, 0) : 0];
+#pragma unroll
+                for (int k = 1; k < S::nf(t); k++) pr = mmul(pr, val[S::f(t, k) < NT ? S::f(t, k) : 0]);
+                pr = mmul(pr, coef[t < BASE_MAX_TERMS ? t : 0]);   // a listed statement's coefficients here are base elements
+                f = fadd(f, pr);
+            }
+            return f;
+        } else {
+            u32 f = 0;
+#pragma unroll
+            for (int t = 0; t < BASE_MAX_TERMS; t++) {
+                if (t < nterms) {
+                    const u32 ds = desc[t];
+                    const int nf = ds & 15, ckind = (ds >> 4) & 3;
+                    u32 pr;
+                    if (nf == 0) pr = coef[t];
+                    else {
+                        pr = sv_pick<NT>(val, (ds >> 8) & 15);
+#pragma unroll
+                        for (int k = 1; k < BASE_MAX_FACTORS; k++)
+                            if (k < nf) pr = mmul(pr, sv_pick<NT>(val, (ds >> (8 + 4 * k)) & 15));
+                        if (ckind == CK_BASE) pr = mmul(pr, coef[t]);
+                    }
+                    f = fadd(f, pr);
+                }
+            }
+            return f;
+        }
+    };
 
     u64 acc[Z][D];
 #pragma unroll
@@ -78,13 +146,20 @@ __global__ void __launch_bounds__(ROUND_THREADS, G > 2 ? 2 : 1) sv_kernel(const 
             }
 #pragma unroll
             for (int z0 = 0; z0 < G; z0++) {
-                if (z1lo == 0) {           // rows 0 and 1: the entries' own rows
-                    g[t][z0] = row[0][z0];
-                    g[t][z0 + G] = row[1][z0];
-                } else {                   // rows 2 and 3: row 1 plus one and two slopes
+                if (ROWS1 == 2) {
+                    if (z1lo == 0) {           // rows 0 and 1: the entries' own rows
+                        g[t][z0] = row[0][z0];
+                        g[t][(z0 + G) % Z] = row[1][z0];
+                    } else {                   // rows 2 and 3: row 1 plus one and two slopes
+                        const u32 s = fsub(row[1][z0], row[0][z0]);
+                        g[t][z0] = fadd(row[1][z0], s);
+                        g[t][(z0 + G) % Z] = fadd(g[t][z0], s);
+                    }
+                } else {                       // one row: z1 = z1lo, row 0 plus z1lo slopes
+                    u32 v = z1lo == 0 ? row[0][z0] : row[1][z0];
                     const u32 s = fsub(row[1][z0], row[0][z0]);
-                    g[t][z0] = fadd(row[1][z0], s);
-                    g[t][z0 + G] = fadd(g[t][z0], s);
+                    for (int k = 1; k < z1lo; k++) v = fadd(v, s);
+                    g[t][z0] = v;
                 }
             }
         }
@@ -99,9 +174,10 @@ __global__ void __launch_bounds__(ROUND_THREADS, G > 2 ? 2 : 1) sv_kernel(const 
         }
 #pragma unroll
         for (int z = 0; z < Z; z++) {
-            u32 f = g[0][z];
+            u32 val[NT];
 #pragma unroll
-            for (int t = 1; t < NT; t++) f = mmul(f, g[t][z]);
+            for (int t = 0; t < NT; t++) val[t] = g[t][z];
+            const u32 f = statement(val);
 #pragma unroll
             for (int c = 0; c < D; c++) acc[z][c] += (u64)hw[c] * f;
         }
@@ -172,21 +248,44 @@ __global__ void __launch_bounds__(ROUND_THREADS, G > 2 ? 2 : 1) sv_kernel(const 
     }
 }
 
-template <int D, int G, int NT> static cudaError_t launch_sv_one(const SvArgs &args, int grid, cudaStream_t stream) {
-    const size_t smem = (size_t)G * 2 * D * ROUND_THREADS * 4;
-    cudaFuncSetAttribute(sv_kernel<D, G, NT>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-    sv_kernel<D, G, NT><<<dim3(grid, G > 2 ? 2 : 1), ROUND_THREADS, smem, stream>>>(args);
+template <int D, int G, int NT, int SHAPE> static cudaError_t launch_sv_one(const SvArgs &args, int grid, cudaStream_t stream) {
+    constexpr int ROWS1 = D == 4 ? 2 : 1;
+    const size_t smem = (size_t)G * ROWS1 * D * ROUND_THREADS * 4;
+    cudaFuncSetAttribute(sv_kernel<D, G, NT, SHAPE>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    sv_kernel<D, G, NT, SHAPE><<<dim3(grid, (G + ROWS1 - 1) / ROWS1), ROUND_THREADS, smem, stream>>>(args);
     return cudaGetLastError();
 }
-bool small_values_supported(int D, int G, int nt) { return D == 4 && nt >= 1 && nt <= 3 && G == nt + 1; }
-cudaError_t launch_small_values(int D, int G, int nt, const SvArgs &args, int grid, cudaStream_t stream) {
-    if (!small_values_supported(D, G, nt)) return cudaErrorInvalidValue;
+template <int D, int G> static cudaError_t launch_sv_generic(int nt, const SvArgs &args, int grid, cudaStream_t stream) {
     switch (nt) {
-    case 1: return launch_sv_one<4, 2, 1>(args, grid, stream);
-    case 2: return launch_sv_one<4, 3, 2>(args, grid, stream);
-    case 3: return launch_sv_one<4, 4, 3>(args, grid, stream);
+    case 1: return launch_sv_one<D, G, 1, SHAPE_GENERIC>(args, grid, stream);
+    case 2: return launch_sv_one<D, G, 2, SHAPE_GENERIC>(args, grid, stream);
+    case 3: return launch_sv_one<D, G, 3, SHAPE_GENERIC>(args, grid, stream);
     }
     return cudaErrorInvalidValue;
+}
+template <int D> static cudaError_t launch_sv_d(int shape, int G, int nt, const SvArgs &args, int grid, cudaStream_t stream) {
+    if (shape == SHAPE_PRODUCT && G == nt + 1) {
+        switch (nt) {
+        case 1: return launch_sv_one<D, 2, 1, SHAPE_PRODUCT>(args, grid, stream);
+        case 2: return launch_sv_one<D, 3, 2, SHAPE_PRODUCT>(args, grid, stream);
+        case 3: return launch_sv_one<D, 4, 3, SHAPE_PRODUCT>(args, grid, stream);
+        }
+    }
+    if (shape == SHAPE_LISTED + 0) return launch_sv_one<D, Listed<0>::PTS + 1, Listed<0>::NT, SHAPE_LISTED + 0>(args, grid, stream);
+    if (shape == SHAPE_LISTED + 1) return launch_sv_one<D, Listed<1>::PTS + 1, Listed<1>::NT, SHAPE_LISTED + 1>(args, grid, stream);
+    switch (G) {
+    case 2: return launch_sv_generic<D, 2>(nt, args, grid, stream);
+    case 3: return launch_sv_generic<D, 3>(nt, args, grid, stream);
+    case 4: return launch_sv_generic<D, 4>(nt, args, grid, stream);
+    }
+    return cudaErrorInvalidValue;
+}
+// G = points + 1 grid values per variable: degree at most three, at most three tables in the statement
+bool small_values_supported(int D, int G, int nt) { return (D == 4 || D == 8) && nt >= 1 && nt <= 3 && G >= 2 && G <= 4; }
+cudaError_t launch_small_values(int D, int shape, int G, int nt, const SvArgs &args, int grid, cudaStream_t stream) {
+    if (!small_values_supported(D, G, nt)) return cudaErrorInvalidValue;
+    if (shape == SHAPE_LISTED + 2 || shape == SHAPE_GKR) shape = SHAPE_GENERIC;
+    return D == 4 ? launch_sv_d<4>(shape, G, nt, args, grid, stream) : launch_sv_d<8>(shape, G, nt, args, grid, stream);
 }
 
 }  // namespace sc

@@ -101,10 +101,46 @@ def test_borrowed_tables_prove_like_uploaded_ones():
         prover.close()
 
 
-def test_one_lookup_with_the_device_transcript(monkeypatch):
-    # with one lookup the resident last rounds of every layer may derive their challenges on the device
-    monkeypatch.setenv("SABLE_B200_DEVICE_TRANSCRIPT", "1")
-    for n, k, d in ((9, 1, 4), (6, 3, 8)):
-        leaves, ta, got, tb, want = both(n, k, 1, d, 21 + n)
-        assert got == tuple(want)
-        assert ta.proof() == tb.proof()
+def test_one_lookup_with_the_device_transcript():
+    # with one lookup every layer's rounds are enqueued at once, the kernels drawing the challenges themselves
+    prover = sb.Prover(0)
+    prover.set_device_transcript(True)
+    try:
+        for n, k, d in ((9, 1, 4), (6, 3, 8), (16, 1, 4)):
+            leaves = random_leaves(1, n, k, d, 21 + n)
+            ta, tb = sb.Transcript("gkr-test", d), orc.Transcript("gkr-test", d)
+            got = sb.gkr_prove_upper(ta, n, k, leaves, provers=[prover])
+            want = gkr.prove_upper(tb, n, k, leaves, threads=0)
+            assert got == tuple(want)
+            assert ta.proof() == tb.proof()
+    finally:
+        prover.close()
+
+
+def test_device_roots_are_the_sums_of_the_leaf_fractions():
+    # reference tests/tests.lisp:423-427 on the device's messages: each root is the sum of its leaf fractions
+    n, k, lookups, d = 4, 3, 2, 4
+    leaves = random_leaves(lookups, n, k, d, 31)
+    ta = sb.Transcript("gkr-test", d)
+    sb.gkr_prove_upper(ta, n, k, leaves)
+    roots = [(m[0].tolist(), m[1].tolist()) for m in ta.messages[:lookups]]
+    for (p, q), (rp, rq) in zip(leaves, roots):
+        total = [0] * d
+        for a, b in zip(p, q):
+            total = orc.ext_add(d, total, orc.ext_mul(d, a.tolist(), orc.ext_inv(d, b.tolist())))
+        assert orc.ext_mul(d, rp, orc.ext_inv(d, rq)) == total
+
+
+@pytest.mark.parametrize("n,k,lookups,d", [(3, 3, 2, 4), (4, 1, 1, 8)])
+def test_forged_device_proofs_are_rejected(n, k, lookups, d):
+    # reference tests/tests.lisp:444-462 (test-gkr-rejects-forgeries) on the device's messages: one changed word in any message and the verifier rejects
+    leaves = random_leaves(lookups, n, k, d, 41)
+    ta = sb.Transcript("gkr-test", d)
+    sb.gkr_prove_upper(ta, n, k, leaves)
+    messages = ta.messages
+    gkr.verify_upper("gkr-test", d, messages, n, k, lookups)
+    for i in range(len(messages)):
+        forged = [m.copy() for m in messages]
+        forged[i].reshape(-1)[0] = (int(forged[i].reshape(-1)[0]) + 1) % P
+        with pytest.raises(gkr.VerificationFailure):
+            gkr.verify_upper("gkr-test", d, forged, n, k, lookups)

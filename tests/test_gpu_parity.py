@@ -304,28 +304,39 @@ def test_abandoned_proof_does_not_block_the_next(prover):
     assert_same(got, want, ta, tb)
 
 
+@pytest.mark.parametrize("d", [4, 8])
 @pytest.mark.parametrize("statement,names,with_eq", [
     ("(* t0 t1 t2)", ["t0", "t1", "t2"], True),
     ("(* t0 t1 t2)", ["t0", "t1", "t2"], False),
     ("(* 5 t0 t1)", ["t0", "t1"], True),
     ("t0", ["t0"], True),
     ("(* alpha t1 t0)", ["t0", "u", "t1"], True),       # an extension coefficient, a table outside the statement
+    # the reference's own small-value statements (tests/tests.lisp:377-378) that fit three tables and degree three
+    ("(+ (* t0 t1 t2) (* 7 t1) -1)", ["t0", "t1", "t2"], True),
+    ("(+ (* t0 t1 t2) (* 7 t1) -1)", ["t0", "t1", "t2"], False),
+    ("(- (expt t0 3) (* t0 t1))", ["t0", "t1"], True),
+    ("(* t0 t1)", ["t0", "t1"], False),
+    ("(+ (* 5 t1 t0) t0)", ["t0", "t1"], True),          # a listed statement
 ])
-def test_small_value_rounds_match_folding(prover, statement, names, with_eq, monkeypatch):
+def test_small_value_rounds_match_folding(prover, d, statement, names, with_eq, monkeypatch):
     # reference tests/tests.lisp:374-395: the small-value rounds give the same proof as folding, byte for byte.
-    # Here they run for products of base tables that are large enough for split eq weights (n >= 22).
-    d, n = 4, 22
-    rng = np.random.default_rng(len(statement) + with_eq)
+    # Here they run for statements over base tables with base-field coefficients, large enough for split eq weights (n >= 22).
+    n = 22
+    rng = np.random.default_rng(len(statement) + with_eq + d)
     tables = [(nm, rng.integers(0, P, size=1 << n, dtype=np.uint32)) for nm in names]
     constants = [("alpha", rand_ext(rng, d).tolist())] if "alpha" in statement else []
     eq = rand_ext(rng, d, n) if with_eq else None
+    before = prover.launches
     got, want, ta, tb = both(prover, d, n, statement, tables, eq=eq, constants=constants, threads=0)
     assert_same(got, want, ta, tb)
-    # and the device's own folding path agrees (small values switched off)
+    with_small_values = prover.launches - before
+    # and the device's own folding path agrees (small values switched off); it takes one launch more (rounds 0 and 1 apart)
     monkeypatch.setenv("SABLE_B200_SMALL_VALUES", "0")
     tc = sb.Transcript("par", d)
+    before = prover.launches
     again = sb.prove(tc, n, statement, tables, eq=eq, constants=constants, prover=prover)
     assert again == got and tc.proof() == ta.proof()
+    assert prover.launches - before == with_small_values + 1, "the small-value rounds did not run"
 
 
 def test_download_gives_the_table_back_and_refuses_in_the_small_value_rounds(prover):
@@ -657,3 +668,27 @@ def test_generated_tables_are_the_oracle_generator_s(prover, stride, nonzero, fi
     want = orc.generate(1, 3, first, entries, stride, nonzero=nonzero)
     assert (back.numpy().view(np.uint32) == want.reshape(-1)).all()
     assert (want < P).all()
+
+
+# ------------------------------------------------------------------ the benchmark's workloads
+
+BENCH_PROOFS = {   # recorded from a run against the CPU port at the configs' own sizes (bench.py --verify)
+    "C1": (20, "(* t0 t1)", 2, "d486796f96c2cb854fa7bad8a0cc8eafc68aeee6aaa6ba8a90ead994060a8744"),
+    "C2": (24, "(* t0 t1 t2)", 3, "e3b71aa9011f9877504442ecb40cc00b5f57a0387689ba58a8e6d1eb6900fde8"),
+}
+
+
+@pytest.mark.parametrize("config", sorted(BENCH_PROOFS))
+def test_bench_configs_have_the_recorded_proofs(prover, config):
+    # BASELINE configs 1 and 2 at their own n on the seeded tables of the benchmark: the proof's hash is the one the
+    # CPU port gave at that size
+    import hashlib
+    import bench
+    n, statement, nt, want = BENCH_PROOFS[config]
+    d = 4
+    for slot in range(nt):
+        prover.generate_table(slot, bench.SEED, slot, 1 << n, 1)
+    eq = np.array([bench.seeded_ext(bench.EQ_ID, i, d) for i in range(n)], dtype=np.uint32)
+    tr = sb.Transcript("bench", d)
+    sb.prove(tr, n, statement, [("t%d" % t, sb.DeviceTable(1)) for t in range(nt)], eq=eq, prover=prover)
+    assert hashlib.sha256(tr.proof()).hexdigest() == want
