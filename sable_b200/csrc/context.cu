@@ -309,7 +309,7 @@ extern "C" int sc_create(int device, sc_ctx **out) {
     ctx->grid_cap = ctx->sms * 8;
     bool ok = cudaMalloc(&ctx->d_partials, (size_t)ctx->grid_cap * PARTIAL_ROW_WORDS * 4) == cudaSuccess &&
               cudaMalloc(&ctx->d_counter, 64) == cudaSuccess && cudaMemset(ctx->d_counter, 0, 64) == cudaSuccess &&
-              cudaMalloc(&ctx->d_out, MAX_PARTIAL_WORDS * 4) == cudaSuccess &&
+              cudaMalloc(&ctx->d_out, (MAX_PARTIAL_WORDS + 32) * 4) == cudaSuccess &&
               cudaHostAlloc(&ctx->h_out, (MAX_PARTIAL_WORDS + 32) * 4, cudaHostAllocMapped) == cudaSuccess &&
               cudaHostGetDevicePointer(&ctx->h_out_dev, ctx->h_out, 0) == cudaSuccess;
     ok = ok && cudaHostAlloc(&ctx->h_tail, TAIL_WORDS * 4, cudaHostAllocMapped) == cudaSuccess &&
@@ -1333,13 +1333,11 @@ static int enqueue_round(sc_ctx *ctx, int j, bool fold, bool chain, bool chain_f
     }
     a.partials = ctx->d_partials; a.counter = ctx->d_counter;
     a.out_dev = ctx->d_out;
-    if (chain) {
+    if (chain) {   // the transcript kernel behind this launch posts to the host
         a.seq = ctx->chain_seq + (u32)j;
-        a.out_host = ctx->h_chain_dev + (size_t)j * CHAIN_SLOT_WORDS;
-        a.tstate = ctx->d_tstate;
-        a.chal_dev = ctx->d_chal + (size_t)j * 16;
-        a.tinit = chain_first;
-        if (chain_first) memcpy(a.tstate0, state0, sizeof a.tstate0);
+        a.out_host = nullptr;
+        a.chained = 1;
+        a.dead = chain_first ? nullptr : ctx->d_tstate + CHAIN_DEAD;
     } else {
         a.seq = ++ctx->seq;
         a.out_host = local ? nullptr : ctx->h_out_dev;
@@ -1354,6 +1352,17 @@ static int enqueue_round(sc_ctx *ctx, int j, bool fold, bool chain, bool chain_f
         a.world = ctx->world; a.rank = ctx->rank; a.xseq = ++ctx->xseq;
         a.mail_polls = ctx->mail_polls;
         if (!chain) a.out_host = ctx->h_out_dev;
+    }
+    TranscriptArgs ta;
+    if (chain) {
+        memset(&ta, 0, sizeof ta);
+        ta.sums = ctx->d_out; ta.W = W; ta.D = D;
+        ta.tstate = ctx->d_tstate;
+        ta.chal_dev = ctx->d_chal + (size_t)j * 16;
+        ta.tinit = chain_first;
+        if (chain_first) memcpy(ta.tstate0, state0, sizeof ta.tstate0);
+        ta.out_host = ctx->h_chain_dev + (size_t)j * CHAIN_SLOT_WORDS;
+        ta.seq = a.seq;
     }
     if (chain && local && !fused_exchange) return fail(ctx, SC_ESTATE, "a chained round without peer access");
 
@@ -1379,6 +1388,10 @@ static int enqueue_round(sc_ctx *ctx, int j, bool fold, bool chain, bool chain_f
     }
     ctx->launches++;
     if (ctx->timing) CU(cudaEventRecord(out->e1, ctx->stream));
+    if (chain) {   // the transcript's part of the round, behind it
+        CU(launch_transcript_round(ta, ctx->stream));
+        ctx->launches++;
+    }
     if (local && !fused_exchange) {   // the whole job's sums: all-gather of the ranks' words, then their sum mod p
         if (!ctx->d_gather) { if ((rc = dev_alloc(ctx, (void **)&ctx->d_gather, (u64)ctx->world * SV_MAX_WORDS * 4))) return rc; }
         ncclResult_t r = g_nccl.AllGather(ctx->d_out, ctx->d_gather, (size_t)W, NCCL_UINT32, ctx->comm, ctx->stream);

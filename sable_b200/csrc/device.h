@@ -130,25 +130,41 @@ struct RoundArgs {
     int world, rank;
     u32 xseq;
     unsigned mail_polls;  // polls (with a short sleep each) the last block waits for the other ranks' sums
-    // The transcript carried on by the device (transcript.cuh).  With TSTATE the last block does the transcript's part of
-    // the round itself: SEND of the sums and CHALLENGE, from the hash state in TSTATE (or, for the first launch of a
-    // chain, from TSTATE0, the host transcript's state), leaves the new state in TSTATE and the challenge in CHAL_DEV
-    // (D words in Montgomery form, then the D canonical words) and, canonical, at word CHAIN_CHAL_WORD of out_host.
-    // The next launch folds by the challenge it finds at its R_DEV, so the host can enqueue every round of a proof
-    // without waiting for any of them.  Word CHAIN_DEAD of TSTATE: a round of this chain failed (another rank's sums
-    // never came); the launches after it post the failure at once instead of waiting again.
+    // A chain of launches (the transcript on the device, see TranscriptArgs): the fold challenge lies at R_DEV (D words,
+    // Montgomery form), left there by the transcript kernel of the round before, instead of in r; the launch number
+    // is also written behind the sums at out_dev (word MAX_PARTIAL_WORDS), with EXCHANGE_FAILED when another rank's
+    // sums never came; DEAD points at the chain's failure word: once it is set the last block does not wait again.
     const u32 *r_dev;
-    u32 *tstate;
-    u32 *chal_dev;
-    int tinit;
-    u32 tstate0[B3_STATE_WORDS - 4];
+    const u32 *dead;
+    int chained;          // 1: the launch is part of a chain (out_dev has room for the launch number)
     u32 bind[4][8];       // FOLD = 2: eq(rho0 rho1, b), b < 4, Montgomery form: entry y of the bound table is sum_b bind[b] T[4y + b]
     int ngroups;
     u32 gcoef[2][8];      // Montgomery form
 };
-constexpr int CHAIN_CHAL_WORD = 72;   // out_host: sums at [0, 64), the posted launch number at 64, the challenge at [72, 80)
+constexpr int CHAIN_CHAL_WORD = 72;   // a chain's slot in mapped host memory: sums at [0, 64), the posted launch number at 64, the challenge at [72, 80)
 constexpr int CHAIN_SLOT_WORDS = 96;
-constexpr int CHAIN_DEAD = 31;
+constexpr int CHAIN_DEAD = 31;        // word of the hash state's buffer: a round of the chain failed
+
+// The transcript's part of a round, on the device (transcript.cuh): one block, launched behind the round kernel of a
+// chain.  It reads the round's sums (and the launch number behind them) where the round kernel left them, SENDs them
+// and draws the CHALLENGE from the hash state in TSTATE (or, for the first launch of a chain, from TSTATE0, the host
+// transcript's state), leaves the new state in TSTATE and the challenge in CHAL_DEV (D words in Montgomery form for the
+// next launch's fold, then the D canonical words), and posts sums, challenge and the launch number to the chain's slot
+// in mapped host memory.  So the host can enqueue every round of a proof without waiting for any of them.
+// It is a kernel of its own, not the round kernel's last block, because transcript code inside the round kernels --
+// called or inlined, and run by one block only -- slowed every round kernel's main loop by 2 % (measured on the
+// layer statement at n = 28, alternating builds on one GPU: 12.25 ms without, 12.47 ms with).
+struct TranscriptArgs {
+    const u32 *sums;      // W words, then at word MAX_PARTIAL_WORDS the launch number the round kernel wrote
+    int W, D;
+    u32 *tstate;
+    u32 *chal_dev;
+    int tinit;
+    u32 tstate0[B3_STATE_WORDS - 4];
+    u32 *out_host;        // the chain's slot of this round
+    u32 seq;
+};
+cudaError_t launch_transcript_round(const TranscriptArgs &args, cudaStream_t stream);
 constexpr int MAIL_WORDS = 128, MAIL_FLAG = 64;
 constexpr unsigned MAIL_POLL_LIMIT = 20000000u;   // polls (with a short sleep each) a rank waits for the others' sums
 constexpr u32 EXCHANGE_FAILED = 0x80000000u;      // or-ed into the posted launch number when a rank's sums never came

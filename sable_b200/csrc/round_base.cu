@@ -33,7 +33,6 @@ __global__ void __launch_bounds__(ROUND_THREADS, round_base_blocks_per_sm(D, SHA
     constexpr int W = NG * PTS * D;
     __shared__ u32 red[ROUND_THREADS / 32][W];
     __shared__ u32 out[PTS * D];
-    __shared__ TrWork tw;
     __shared__ bool is_last;
     const int tid = threadIdx.x;
     const u32 L = 1u << a.logL;
@@ -292,7 +291,7 @@ __global__ void __launch_bounds__(ROUND_THREADS, round_base_blocks_per_sm(D, SHA
         }
         __syncthreads();
         if (tid == 0) *a.counter = 0;
-        publish_round(a, out, PTS * D, D, &tw);
+        publish_round(a, out, PTS * D);
     }
 }
 

@@ -56,15 +56,14 @@ template <int D, int NT> __device__ __forceinline__ Ext<D> pick(const Ext<D> (&v
 }
 
 // The end of a round, run by every thread of the one block that holds the round's W sums (canonical words, in
-// shared memory).  Several GPUs: the sums go to every rank's mailbox and come back added up.  With the transcript
-// on the device (RoundArgs::tstate) the block then sends the sums and draws the challenge.  Last the sums (and the
-// challenge) are written for the host, and the launch number after them.
-static __device__ __noinline__ void publish_round(const RoundArgs &a, u32 *sums, int W, int D, TrWork *tw) {
+// shared memory).  Several GPUs: the sums go to every rank's mailbox and come back added up.  Then the sums are
+// written for the host and for whatever follows on the device, and the launch number after them.
+static __device__ __forceinline__ void publish_round(const RoundArgs &a, u32 *sums, int W) {
     const int tid = threadIdx.x;
     __shared__ int missing;
     u32 posted = a.seq;
-    const bool dead = a.tstate && !a.tinit && *reinterpret_cast<const volatile u32 *>(a.tstate + CHAIN_DEAD) != 0;
     if (a.xseq) {
+        const bool dead = a.dead && *reinterpret_cast<const volatile u32 *>(a.dead) != 0;
         // hand the sums to every rank (this one included), the exchange number after them
         const size_t box = ((size_t)(a.xseq & 1) * a.world + a.rank) * MAIL_WORDS;
         if (tid < W)
@@ -91,27 +90,13 @@ static __device__ __noinline__ void publish_round(const RoundArgs &a, u32 *sums,
         }
         __syncthreads();
     }
-    if (a.tstate) {
-        if (posted & EXCHANGE_FAILED) {
-            if (tid == 0) a.tstate[CHAIN_DEAD] = 1;
-        } else {
-            transcript_round(tw, a.tinit ? a.tstate0 : a.tstate, sums, W, D, a.tstate);
-            __syncthreads();
-            if (tid < D) {
-                const u32 c = tw->chal[tid];
-                a.chal_dev[tid] = to_mont(c);
-                a.chal_dev[D + tid] = c;
-                if (a.out_host) a.out_host[CHAIN_CHAL_WORD + tid] = c;
-            }
-            if (tid == 0 && a.tinit) a.tstate[CHAIN_DEAD] = 0;
-        }
-    }
     if (tid < W) {
         a.out_dev[tid] = sums[tid];
         if (a.out_host) a.out_host[tid] = sums[tid];
     }
+    if (tid == 0 && a.chained) a.out_dev[MAX_PARTIAL_WORDS] = posted;
     __syncthreads();
-    if (tid == 0 && a.out_host) {   // the host polls this word: the words above are visible before it (the fence is cumulative)
+    if (tid == 0 && a.out_host) {   // the host polls this word: the sums above are visible before it (the fence is cumulative)
         __threadfence_system();
         *reinterpret_cast<volatile u32 *>(a.out_host + MAX_PARTIAL_WORDS) = posted;
     }
@@ -260,7 +245,6 @@ template <int D, int PTS, int NT, int FOLD, int SHAPE>
 __global__ void __launch_bounds__(ROUND_THREADS, NT > 4 ? 1 : (D == 8 ? SC_MINBLOCKS_D8 : (FOLD ? SC_MINBLOCKS : SC_MINBLOCKS_R0))) round_kernel(const __grid_constant__ RoundArgs a) {
     extern __shared__ __align__(16) u32 smem[];
     __shared__ u32 red[ROUND_THREADS / 32][PTS * D];
-    __shared__ TrWork tw;
     __shared__ bool is_last;
     const int tid = threadIdx.x;
     const u32 L = 1u << a.logL;
@@ -541,7 +525,7 @@ __global__ void __launch_bounds__(ROUND_THREADS, NT > 4 ? 1 : (D == 8 ? SC_MINBL
             for (int c = 0; c < D; c++) red[0][tid * D + c] = s.v[c];
         }
         __syncthreads();
-        publish_round(a, &red[0][0], W, D, &tw);
+        publish_round(a, &red[0][0], W);
     }
 }
 

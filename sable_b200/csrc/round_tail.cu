@@ -268,6 +268,43 @@ template <int D> static cudaError_t launch_tail_d(int shape, int points, int nt,
     default: return cudaErrorInvalidValue;
     }
 }
+// The transcript's part of a round kernel's round (see TranscriptArgs): one block behind the round kernel.
+__global__ void __launch_bounds__(ROUND_THREADS) transcript_kernel(const __grid_constant__ TranscriptArgs a) {
+    __shared__ u32 sums[MAX_PARTIAL_WORDS];
+    __shared__ u32 state[B3_STATE_WORDS];
+    __shared__ TrWork tw;
+    const int tid = threadIdx.x;
+    if (tid < a.W) sums[tid] = a.sums[tid];
+    if (tid < B3_STATE_WORDS - 4) state[tid] = a.tinit ? a.tstate0[tid] : a.tstate[tid];
+    u32 posted = a.sums[MAX_PARTIAL_WORDS];
+    if (!a.tinit && a.tstate[CHAIN_DEAD] != 0) posted |= EXCHANGE_FAILED;   // a round before this one failed
+    __syncthreads();
+    if (posted & EXCHANGE_FAILED) {
+        if (tid == 0) a.tstate[CHAIN_DEAD] = 1;
+    } else {
+        transcript_round(&tw, state, sums, a.W, a.D, state);
+        __syncthreads();
+        if (tid < B3_STATE_WORDS - 4) a.tstate[tid] = state[tid];
+        if (tid < a.D) {
+            const u32 c = tw.chal[tid];
+            a.chal_dev[tid] = to_mont(c);
+            a.chal_dev[a.D + tid] = c;
+            a.out_host[CHAIN_CHAL_WORD + tid] = c;
+        }
+        if (tid == 0 && a.tinit) a.tstate[CHAIN_DEAD] = 0;
+    }
+    if (tid < a.W) a.out_host[tid] = sums[tid];
+    __syncthreads();
+    if (tid == 0) {   // the host polls this word: the words above are visible before it (the fence is cumulative)
+        __threadfence_system();
+        *reinterpret_cast<volatile u32 *>(a.out_host + MAX_PARTIAL_WORDS) = (posted & EXCHANGE_FAILED) | a.seq;
+    }
+}
+cudaError_t launch_transcript_round(const TranscriptArgs &args, cudaStream_t stream) {
+    transcript_kernel<<<1, ROUND_THREADS, 0, stream>>>(args);
+    return cudaGetLastError();
+}
+
 cudaError_t launch_tail(int D, int shape, int points, int nt_used, const TailArgs &args, cudaStream_t stream) {
     if (D == 4) return launch_tail_d<4>(shape, points, nt_used, args, stream);
     if (D == 8) return launch_tail_d<8>(shape, points, nt_used, args, stream);

@@ -11,6 +11,10 @@
 // than its chain of dependent operations; spreading the four columns over four lanes would add the
 // shuffles of the diagonal step to that chain.
 //
+// Everything here is inlined into its caller and the compression has ONE call site (the loop in
+// transcript_round), which keeps the two kernels that carry it (the transcript kernel behind a round kernel,
+// and the resident kernel of the small rounds) small.
+//
 // The code is host/device: the host build runs the same statements with one "thread", so the device's
 // transcript can be checked against the host transcript without a GPU.
 #pragma once
@@ -41,7 +45,7 @@ struct TrWork {          // a block's scratch for one round of the transcript (s
 #define TR_TID ((int)threadIdx.x)
 #define TR_NT ((int)blockDim.x)
 #define TR_SYNC() __syncthreads()
-#define TR_FN __device__ __noinline__
+#define TR_FN __device__ __forceinline__
 #define TR_INL __device__ __forceinline__
 #else
 #define TR_TID 0
@@ -94,17 +98,6 @@ TR_FN void tr_compress(const u32 *cv, const u32 *block, u32 counter_lo, u32 coun
     out[12] = v12 ^ c4; out[13] = v13 ^ c5; out[14] = v14 ^ c6; out[15] = v15 ^ c7;
 }
 
-// B3S-UPDATE's rule (src/blake3.lisp:134-142): a full block is compressed only when more input has arrived,
-// so every block of the stream but the last one is compressed.
-TR_INL void tr_settle(TrWork *w) {
-    while (w->total - w->off > 64) {
-        tr_compress(w->cv, w->buf + w->off / 4, w->blocks[0], w->blocks[1], 64, 0, w->out);
-#pragma unroll
-        for (int i = 0; i < 8; i++) w->cv[i] = w->out[i];
-        if (++w->blocks[0] == 0) ++w->blocks[1];
-        w->off += 64;
-    }
-}
 TR_INL void tr_put_byte(TrWork *w, u32 at, u32 byte) { reinterpret_cast<unsigned char *>(w->buf)[at] = (unsigned char)byte; }
 
 // One round of the transcript, by every thread of the block (the host build: by the caller alone).
@@ -130,29 +123,40 @@ TR_FN void transcript_round(TrWork *w, const u32 *state_in, const u32 *sums, int
     if (tid == 0) {
         w->off = 0; w->total = fill0 + (u32)L;
         w->blocks[0] = state_in[25]; w->blocks[1] = state_in[26];
-        tr_settle(w);
-        // CHALLENGE-BASE (src/transcript.lisp:159-172): D words below p out of D - have + 4 squeezed ones, again if short
+        // One loop, one compression per turn.  While a full block has more input behind it, that block is chained
+        // (B3S-UPDATE, src/blake3.lisp:134-142: a full block is compressed only when more input has arrived).  Else,
+        // while challenge words are missing, SQUEEZE (src/transcript.lisp:152-157): the output block of the pending
+        // bytes, from which CHALLENGE-BASE (:159-172) keeps the words below p, then "squeeze" and the first 32 output
+        // bytes are absorbed -- which may fill a block again, and the loop chains it before it ends.
         int have = 0;
-        while (have < D) {
-            if (have > 0) {   // a second SQUEEZE (about once in 10^8 rounds): make room by moving the pending block to the front
+        for (;;) {
+            const bool chain = w->total - w->off > 64;
+            if (!chain && have >= D) break;
+            if (!chain && w->total + 39u > 4u * TR_BUF_WORDS) {   // a second SQUEEZE (about once in 10^8 rounds): make room
                 const u32 fill = w->total - w->off;
                 for (int k = 0; k < 16; k++) w->buf[k] = w->buf[w->off / 4 + k];
                 for (int k = 16; k < TR_BUF_WORDS; k++) w->buf[k] = 0;
                 w->off = 0; w->total = fill;
             }
-            const int nbytes = 4 * (D - have + 4);      // at most 48: one output block
-            tr_compress(w->cv, w->buf + w->off / 4, 0, 0, w->total - w->off, 2u | 8u, w->out);   // CHUNK_END | ROOT, counter 0 (:113-123)
-            for (int i = 0; i < nbytes / 4 && have < D; i++) {
-                const u32 v = w->out[i] & 0x7FFFFFFFu;
-                if (v < scf::P) w->chal[have++] = v;
+            tr_compress(w->cv, w->buf + w->off / 4, chain ? w->blocks[0] : 0u, chain ? w->blocks[1] : 0u, chain ? 64u : w->total - w->off,
+                        chain ? 0u : (2u | 8u), w->out);   // the output block: CHUNK_END | ROOT, counter 0 (:113-123)
+            if (chain) {
+#pragma unroll
+                for (int i = 0; i < 8; i++) w->cv[i] = w->out[i];
+                if (++w->blocks[0] == 0) ++w->blocks[1];
+                w->off += 64;
+            } else {
+                const int nbytes = 4 * (D - have + 4);      // at most 48: one output block
+                for (int i = 0; i < nbytes / 4 && have < D; i++) {
+                    const u32 v = w->out[i] & 0x7FFFFFFFu;
+                    if (v < scf::P) w->chal[have++] = v;
+                }
+                const u32 tag[2] = {0x65757173u, 0x00657a65u};   // "sque", "eze"
+                for (int k = 0; k < 7; k++) tr_put_byte(w, w->total + (u32)k, (tag[k >> 2] >> (8 * (k & 3))) & 0xffu);
+                const int take = nbytes < 32 ? nbytes : 32;
+                for (int k = 0; k < take; k++) tr_put_byte(w, w->total + 7u + (u32)k, (w->out[k >> 2] >> (8 * (k & 3))) & 0xffu);
+                w->total += 7u + (u32)take;
             }
-            // SQUEEZE (:152-157): after the output, "squeeze" and the first 32 output bytes are absorbed
-            const u32 tag[2] = {0x65757173u, 0x00657a65u};   // "sque", "eze"
-            for (int k = 0; k < 7; k++) tr_put_byte(w, w->total + (u32)k, (tag[k >> 2] >> (8 * (k & 3))) & 0xffu);
-            const int take = nbytes < 32 ? nbytes : 32;
-            for (int k = 0; k < take; k++) tr_put_byte(w, w->total + 7u + (u32)k, (w->out[k >> 2] >> (8 * (k & 3))) & 0xffu);
-            w->total += 7u + (u32)take;
-            tr_settle(w);     // overwrites w->out: the challenge and the absorbed bytes were taken from it above
         }
     }
     TR_SYNC();

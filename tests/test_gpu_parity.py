@@ -425,7 +425,7 @@ def test_device_transcript_from_a_bare_hash_state(chained):
         tr.send(chained.round())
         rho.append(tr.challenge())
         chained.challenge(rho[-1])
-    assert chained.launches - before <= n - 10    # one launch per large round and one for all the small ones, none per small round
+    assert chained.launches - before <= 2 * (n - 11) + 1    # two launches per large round (the round, its transcript step), one for all the small rounds
     finals = chained.finish(2)[:, 0, :].tolist()
     tb = orc.Transcript("bare", d)
     want = orc.prove(tb, n, "(* a b)", [("a", tabs[0]), ("b", tabs[1])], eq=eq)
