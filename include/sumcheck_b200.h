@@ -157,7 +157,8 @@ int sc_timer_stop(sc_ctx *ctx, float *ms);
 int sc_fetch_table(sc_ctx *ctx, int slot, uint32_t *host, uint64_t words);
 
 /* Several GPUs: the hypercube is cut on its top log2(WORLD) variables, rank RANK holding entries
-   [RANK * 2^N / WORLD, (RANK + 1) * 2^N / WORLD) of every table.  Each round's sums are combined
+   [RANK * 2^N / WORLD, (RANK + 1) * 2^N / WORLD) of every table (with block weights: of every block of
+   every table, block after block).  Each round's sums are combined
    with an NCCL all-gather of POINTS * D words and a sum mod p; when fewer than log2(WORLD)
    variables would remain per rank the tables are gathered and every rank finishes alike.
    NCCL_ID is the 128-byte ncclUniqueId made by rank 0 (sc_comm_unique_id) and handed to the

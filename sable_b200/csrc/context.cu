@@ -139,7 +139,7 @@ struct sc_ctx {
     // the resident kernel of the last rounds (see TailArgs)
     u32 *h_tail = nullptr, *h_tail_dev = nullptr;   // mapped host memory and its device alias
     bool tail_active = false;
-    int tail_first = 0, tail_rounds = 0, tail_bits = 12;
+    int tail_first = 0, tail_rounds = 0, tail_nofold = 0, tail_bits = 12;
     u32 tail_seq = 0;
     unsigned tail_polls = TAIL_POLL_LIMIT;
     u64 tail_entries = 0;            // entries of the tables the first round of the launch read
@@ -265,6 +265,31 @@ static bool wait_word(sc_ctx *ctx, const u32 *word, u32 want) {
                 cudaStreamSynchronize(ctx->stream);
                 std::atomic_thread_fence(std::memory_order_acquire);
                 return (*w & ~EXCHANGE_FAILED) == want;
+            }
+            if (std::chrono::steady_clock::now() - t0 > std::chrono::seconds(ctx->comm_timeout_s)) {
+                comm_abort(ctx);
+                return false;
+            }
+        }
+    }
+}
+
+// Wait until COUNT words of mapped memory all carry the mark TAIL_HERE (each word says for itself that the device has
+// written it).  Bounded like wait_word.
+static bool wait_here(sc_ctx *ctx, const u32 *words, int count) {
+    volatile const u32 *w = words;
+    const auto t0 = std::chrono::steady_clock::now();
+    for (u64 spin = 0;; spin++) {
+        u32 all = TAIL_HERE;
+        for (int k = 0; k < count; k++) all &= w[k];
+        if (all) { std::atomic_thread_fence(std::memory_order_acquire); return true; }
+        if ((spin & 0xfffff) == 0xfffff) {
+            if (cudaStreamQuery(ctx->stream) != cudaErrorNotReady) {
+                cudaStreamSynchronize(ctx->stream);
+                std::atomic_thread_fence(std::memory_order_acquire);
+                all = TAIL_HERE;
+                for (int k = 0; k < count; k++) all &= w[k];
+                return all != 0;
             }
             if (std::chrono::steady_clock::now() - t0 > std::chrono::seconds(ctx->comm_timeout_s)) {
                 comm_abort(ctx);
@@ -646,9 +671,9 @@ extern "C" int sc_set_statement(sc_ctx *ctx, int D, int points, int ntables, int
             }
         }
     }
-    {   // the small-value rounds: every coefficient in the base field, terms within the base-table kernel's descriptors
-        bool ok = nterms >= 1 && nterms <= BASE_MAX_TERMS && nt_used >= 1 && nt_used <= 3 && points <= 3;
-        for (int t = 0; t < nterms && ok; t++) ok = ctx->st.terms[t].ckind != CK_EXT && ctx->st.terms[t].nf <= BASE_MAX_FACTORS;
+    {   // the small-value rounds: what the base-table kernel takes (its groups and descriptors), up to three tables and degree three
+        bool ok = nterms >= 1 && nterms <= BASE_MAX_TERMS && nt_used >= 1 && nt_used <= 3 && points <= 3 && ctx->base_groups > 0;
+        for (int t = 0; t < nterms && ok; t++) ok = ctx->st.terms[t].nf <= BASE_MAX_FACTORS;
         if (shape == SHAPE_PRODUCT) ok = nt_used <= 3;   // its coefficient, whatever it is, rides in the final factor
         ctx->sv_statement = ok;
     }
@@ -890,8 +915,10 @@ extern "C" int sc_begin(sc_ctx *ctx, int n, const uint32_t *eq, int K, const uin
     if (n < 0 || n > 40) return fail(ctx, SC_EINVAL, "n = %d", n);
     if (block_weights && K < 1) return fail(ctx, SC_EINVAL, "K = %d block weights", K);
     if (!block_weights) K = 1;
+    static const bool trace = getenv("SABLE_B200_TRACE") != nullptr;   // the host time of each part on stderr
+    const auto t_in = std::chrono::steady_clock::now();
     const int D = ctx->D, w = ctx->logw;
-    if (ctx->world > 1 && (block_weights || n < w)) return fail(ctx, SC_EUNSUPPORTED, "several GPUs: no block weights, and n >= log2(world)");
+    if (ctx->world > 1 && n < w) return fail(ctx, SC_EUNSUPPORTED, "several GPUs: n >= log2(world)");
     cudaSetDevice(ctx->device);
     const int nloc = n - w;
     const u64 want = (u64)K << nloc;
@@ -949,11 +976,11 @@ extern "C" int sc_begin(sc_ctx *ctx, int n, const uint32_t *eq, int K, const uin
         const bool local = j < gather_round;         // before the gather
         const int end = local ? nloc : n;            // eq variables of this stage end here
         const int v = end - 1 - j;
-        const int blocks = local ? K : 1;
+        const int blocks = K;                         // every block in every round: with several GPUs each rank holds its slice of each
         const int a = split_bits(D, v);
         pl.logL = a;
         pl.use_low = eq && a > 0;
-        const bool has_bw = block_weights && local;
+        const bool has_bw = block_weights != nullptr;
         pl.use_high = (eq && v - a > 0) || has_bw;   // a single high weight without block weights is 1
         if (pl.use_low) {
             WeightDesc d; d.out_word = words; d.entries = 1ull << a; d.start = j + 1; d.bits = a; d.kind = 1; d.blocks = 0;
@@ -967,6 +994,7 @@ extern "C" int sc_begin(sc_ctx *ctx, int n, const uint32_t *eq, int K, const uin
         }
     }
     int rc;
+    const auto t_plan = std::chrono::steady_clock::now();
     if ((rc = ensure(ctx, &ctx->d_eq, &ctx->eq_cap, eqm.size() * 4))) return rc;
     if ((rc = ensure(ctx, &ctx->d_bw, &ctx->bw_cap, bwm.size() * 4))) return rc;
     if ((rc = ensure(ctx, &ctx->d_chunks, &ctx->chunks_cap, (u64)(n > 0 ? n : 1) * 512 * D * 4))) return rc;
@@ -975,6 +1003,7 @@ extern "C" int sc_begin(sc_ctx *ctx, int n, const uint32_t *eq, int K, const uin
     CU(cudaMemcpyAsync(ctx->d_eq, eqm.data(), eqm.size() * 4, cudaMemcpyHostToDevice, ctx->stream));
     CU(cudaMemcpyAsync(ctx->d_bw, bwm.data(), bwm.size() * 4, cudaMemcpyHostToDevice, ctx->stream));
     if (!descs.empty()) CU(cudaMemcpyAsync(ctx->d_descs, descs.data(), descs.size() * sizeof(WeightDesc), cudaMemcpyHostToDevice, ctx->stream));
+    const auto t_copied = std::chrono::steady_clock::now();
     if (eq && n > 0) { CU(launch_eq_chunks(D, ctx->d_eq, n, ctx->d_chunks, ctx->stream)); ctx->launches++; }
     if (total_entries) {
         CU(launch_weight_tables(D, ctx->d_chunks, ctx->d_descs, (int)descs.size(), ctx->d_bw, ctx->d_weights, total_entries, ctx->stream));
@@ -993,6 +1022,11 @@ extern "C" int sc_begin(sc_ctx *ctx, int n, const uint32_t *eq, int K, const uin
         if (ok && eq) for (int c = 0; c < D; c++) ctx->eq1[c] = eq[D + c] % P;
     }
     ctx->begun = true;
+    if (trace) {
+        auto us = [](std::chrono::steady_clock::time_point a, std::chrono::steady_clock::time_point b) { return std::chrono::duration<double, std::micro>(b - a).count(); };
+        const auto t_out = std::chrono::steady_clock::now();
+        fprintf(stderr, "  sc_begin n = %d: plan %.1f us, copies %.1f us, weight kernels %.1f us\n", n, us(t_in, t_plan), us(t_plan, t_copied), us(t_copied, t_out));
+    }
     return SC_OK;
 }
 
@@ -1032,16 +1066,18 @@ static int fold_all(sc_ctx *ctx, const u32 *r_dev = nullptr) {
 }
 
 // Gather every rank's slice of each table into whole tables, alike on every rank (rank k holds
-// entries [k N/W, (k+1) N/W), so the slices in rank order are the table).
+// entries [k N/W, (k+1) N/W) of each block, so a block's slices in rank order are the block: one all-gather per block).
 static int gather_tables(sc_ctx *ctx) {
-    const int D = ctx->D;
+    const int D = ctx->D, K = ctx->K;
     for (int s = 0; s < ctx->ntables; s++) {
         TableState &t = ctx->tab[s];
-        const u64 words = t.cur_entries * (u64)(t.cur_base ? 1 : D);
+        const u64 words = t.cur_entries * (u64)(t.cur_base ? 1 : D), slice = words / (u64)K;
         int rc = ensure(ctx, &ctx->d_gtab[s], &ctx->gtab_cap[s], (u64)ctx->world * words * 4);
         if (rc) return rc;
-        ncclResult_t r = g_nccl.AllGather(t.cur, ctx->d_gtab[s], (size_t)words, NCCL_UINT32, ctx->comm, ctx->stream);
-        if (r) return fail(ctx, SC_ECOMM, "ncclAllGather: %s", g_nccl.GetErrorString(r));
+        for (int b = 0; b < K; b++) {
+            ncclResult_t r = g_nccl.AllGather(t.cur + (u64)b * slice, ctx->d_gtab[s] + (u64)b * ctx->world * slice, (size_t)slice, NCCL_UINT32, ctx->comm, ctx->stream);
+            if (r) return fail(ctx, SC_ECOMM, "ncclAllGather: %s", g_nccl.GetErrorString(r));
+        }
         t.cur = ctx->d_gtab[s]; t.cur_buf = -1; t.cur_entries *= (u64)ctx->world;
     }
     return SC_OK;
@@ -1091,6 +1127,10 @@ static int sv_round0(sc_ctx *ctx, uint32_t *sums) {
     if (sharded && ctx->use_post) ext_mul_host(D, a.post, ctx->post, a.post);   // this rank's eq weight
     a.partials = ctx->d_partials; a.counter = ctx->d_counter;
     a.st = ctx->st;
+    a.ngroups = ctx->base_groups;
+    memcpy(a.gcoef, ctx->gcoef, sizeof a.gcoef);
+    a.use_gcoef = a.ngroups > 1;
+    for (int c = 0; c < D; c++) if (ctx->gcoef[0][c] != (c == 0 ? R1 : 0u)) a.use_gcoef = 1;
     a.seq = ++ctx->seq;
     if (sharded) {
         int rc;
@@ -1180,14 +1220,16 @@ static bool tail_wanted(const sc_ctx *ctx, int j) {
     return ctx->tab[ctx->order[0]].cur_entries <= (1ull << ctx->tail_bits);
 }
 
-// Launch the resident kernel for the rounds J .. n-1.  CHAIN: it carries the transcript on itself, from STATE0 (the
-// host transcript's state, when it is the chain's first launch) or from the state the launch before it left.
-static int tail_start(sc_ctx *ctx, int j, bool chain, bool chain_first, const u32 *state0) {
+// Launch the resident kernel for the rounds J .. n-1.  FOLD: round J folds by the pending challenge first (else it reads
+// the tables as they are: round 0, or the round after a gather).  CHAIN: it carries the transcript on itself, from STATE0
+// (the host transcript's state, when it is the chain's first launch) or from the state the launch before it left.
+static int tail_start(sc_ctx *ctx, int j, bool fold, bool chain, bool chain_first, const u32 *state0) {
     const int D = ctx->D;
     TailArgs a;
     memset(&a, 0, sizeof a);
     a.ntables = ctx->ntables;
     a.nrounds = ctx->n - j;
+    a.nofold = fold ? 0 : 1;
     u64 entries = 0;
     for (int k = 0; k < ctx->ntables; k++) {
         TableState &t = ctx->tab[ctx->order[k]];
@@ -1205,11 +1247,12 @@ static int tail_start(sc_ctx *ctx, int j, bool chain, bool chain_first, const u3
     for (int k = 0; k < a.nrounds; k++) {
         const RoundPlan &pl = ctx->plan[j + k];
         if (pl.logL != 0 || pl.use_low) return fail(ctx, SC_ESTATE, "a split round in the tail");
-        a.rd[k].npairs = entries >> (k + 2);
+        a.rd[k].npairs = fold ? entries >> (k + 2) : entries >> (k + 1);   // pairs summed: of the folded table, or (first round, no fold) of the table itself
         a.rd[k].high_word = pl.high_word;
         a.rd[k].use_high = pl.use_high;
     }
-    if (chain && !chain_first) a.r_dev = ctx->d_chal + (size_t)(j - 1) * 16;
+    if (!fold) {}   // no challenge yet
+    else if (chain && !chain_first) a.r_dev = ctx->d_chal + (size_t)(j - 1) * 16;
     else challenge_words(ctx, a.r);
     a.weights = ctx->d_weights;
     a.st = ctx->st;
@@ -1226,6 +1269,14 @@ static int tail_start(sc_ctx *ctx, int j, bool chain, bool chain_first, const u3
         if (chain_first) memcpy(a.tstate0, state0, sizeof a.tstate0);
         else a.tstate = ctx->d_tstate;
     }
+    // the words that carry their own mark once written: cleared here (the launch before is through with them: its
+    // final entries were seen, or it was stopped and the stream drained)
+    for (int k = 0; k < a.nrounds; k++) {
+        volatile u32 *slot = ctx->h_tail + (size_t)k * TAIL_SLOT_WORDS;
+        for (int c = 0; c < 32; c++) slot[c] = 0;
+        for (int c = 0; c < 8; c++) slot[40 + c] = 0;
+    }
+    for (int c = 0; c < SC_MAX_TABLES * 8; c++) ((volatile u32 *)ctx->h_tail)[TAIL_FINALS + c] = 0;
     ((volatile u32 *)ctx->h_tail)[TAIL_STATUS] = 0;
     std::atomic_thread_fence(std::memory_order_seq_cst);
     CU(launch_tail(D, ctx->shape, ctx->points, ctx->nt_used, a, ctx->stream));
@@ -1233,6 +1284,7 @@ static int tail_start(sc_ctx *ctx, int j, bool chain, bool chain_first, const u3
     ctx->tail_active = true;
     ctx->tail_first = j;
     ctx->tail_rounds = a.nrounds;
+    ctx->tail_nofold = a.nofold;
     return SC_OK;
 }
 
@@ -1241,10 +1293,11 @@ static int tail_start(sc_ctx *ctx, int j, bool chain, bool chain_first, const u3
 // proof goes on with one launch per round, and the context stops using the resident kernel.
 static bool tail_recover(sc_ctx *ctx, int done) {
     if (ctx->h_tail[TAIL_STATUS] != 2 || done < 1) return false;
-    for (int s = 0; s < ctx->ntables; s++) {
+    const int folds = done - ctx->tail_nofold;   // folds the kernel finished: none yet after a first round that had no challenge
+    for (int s = 0; s < ctx->ntables && folds > 0; s++) {
         TableState &t = ctx->tab[s];
-        const int b = ctx->tail_buf0[s] ^ ((done - 1) & 1);
-        t.cur = t.buf[b]; t.cur_buf = b; t.cur_base = false; t.cur_entries = ctx->tail_entries >> done;
+        const int b = ctx->tail_buf0[s] ^ ((folds - 1) & 1);
+        t.cur = t.buf[b]; t.cur_buf = b; t.cur_base = false; t.cur_entries = ctx->tail_entries >> folds;
     }
     ctx->tail_active = false;
     ctx->tail_bits = 0;
@@ -1255,14 +1308,15 @@ static bool tail_recover(sc_ctx *ctx, int done) {
 static int tail_round(sc_ctx *ctx, uint32_t *sums) {
     const int k = ctx->j - ctx->tail_first;
     const u32 *slot = ctx->h_tail + (size_t)k * TAIL_SLOT_WORDS;
-    if (!wait_word(ctx, slot + 32, ctx->tail_seq + (u32)k)) {
+    const int W = ctx->points * ctx->D;
+    if (!(ctx->tail_own ? wait_word(ctx, slot + 32, ctx->tail_seq + (u32)k) : wait_here(ctx, slot, W))) {
         if (!ctx->tail_own && tail_recover(ctx, k)) return sc_round(ctx, sums);
         ctx->tail_active = false;
         ctx->chain_active = false;
         ctx->begun = false;
         return fail(ctx, SC_ESTATE, "the device stopped waiting for a challenge (status %u)", ctx->h_tail[TAIL_STATUS]);
     }
-    memcpy(sums, slot, (size_t)ctx->points * ctx->D * 4);
+    for (int c = 0; c < W; c++) sums[c] = slot[c] & ~TAIL_HERE;
     ctx->have_r = false;
     ctx->j++;
     return SC_OK;
@@ -1464,8 +1518,8 @@ static int chain_start(sc_ctx *ctx) {
             }
         }
         const bool local = ctx->world > 1 && j < ctx->gather_round;
-        if (fold && !local && tail_wanted(ctx, j)) {
-            if ((rc = tail_start(ctx, j, true, first, state))) return rc;
+        if (!local && tail_wanted(ctx, j)) {
+            if ((rc = tail_start(ctx, j, fold, true, first, state))) return rc;
             break;
         }
         RoundLaunch L;
@@ -1523,8 +1577,8 @@ extern "C" int sc_round(sc_ctx *ctx, uint32_t *sums) {
         fold = false;   // folded already (fold_all cleared the pending challenge)
     }
     const bool local = ctx->world > 1 && j < ctx->gather_round;
-    if (fold && !local && tail_wanted(ctx, j)) {
-        if ((rc = tail_start(ctx, j, false, false, nullptr))) return rc;
+    if (!local && tail_wanted(ctx, j)) {
+        if ((rc = tail_start(ctx, j, fold, false, false, nullptr))) return rc;
         ctx->have_r = false;
         return tail_round(ctx, sums);
     }
@@ -1583,11 +1637,9 @@ extern "C" int sc_challenge(sc_ctx *ctx, const uint32_t *r) {
             }
         return SC_OK;
     }
-    if (ctx->tail_active) {   // hand the challenge to the resident kernel: the words first, then the word it polls
+    if (ctx->tail_active) {   // hand the challenge to the resident kernel: it polls the words themselves, each marked as written
         u32 *slot = ctx->h_tail + (size_t)(done - ctx->tail_first) * TAIL_SLOT_WORDS;
-        for (int c = 0; c < ctx->D; c++) ((volatile u32 *)slot)[40 + c] = ctx->r[c];
-        std::atomic_thread_fence(std::memory_order_seq_cst);
-        ((volatile u32 *)slot)[48] = ctx->tail_seq + (u32)(done - ctx->tail_first);
+        for (int c = 0; c < ctx->D; c++) ((volatile u32 *)slot)[40 + c] = ctx->r[c] | TAIL_HERE;
         std::atomic_thread_fence(std::memory_order_seq_cst);
     }
     return SC_OK;
@@ -1601,8 +1653,13 @@ extern "C" int sc_finish(sc_ctx *ctx, uint32_t *folded) {
     cudaSetDevice(ctx->device);
     int rc;
     if (ctx->tail_active) {   // the resident kernel folds by the last challenge and posts the final entries
-        const bool ok = wait_word(ctx, ctx->h_tail + TAIL_FINALS - 1, ctx->tail_seq);
-        CU(cudaStreamSynchronize(ctx->stream));
+        const auto t_in = std::chrono::steady_clock::now();
+        const bool ok = wait_here(ctx, ctx->h_tail + TAIL_FINALS, ctx->ntables * ctx->D);
+        // posting them was the launch's last act (its reads and writes of the tables are done, its status is written): no
+        // need to wait for the stream to drain, whatever follows on it is ordered behind the launch anyway
+        if (!ok) CU(cudaStreamSynchronize(ctx->stream));
+        if (getenv("SABLE_B200_TRACE"))
+            fprintf(stderr, "  sc_finish: final entries after %.1f us\n", std::chrono::duration<double, std::micro>(std::chrono::steady_clock::now() - t_in).count());
         if (ok && ctx->tail_own && getenv("SABLE_B200_TRACE"))
             for (int k = 0; k < ctx->tail_rounds; k++) {
                 const u32 *slot = ctx->h_tail + (size_t)k * TAIL_SLOT_WORDS;
@@ -1614,7 +1671,7 @@ extern "C" int sc_finish(sc_ctx *ctx, uint32_t *folded) {
             ctx->begun = false;
             if (folded)
                 for (int k = 0; k < ctx->ntables; k++)
-                    memcpy(folded + (size_t)ctx->order[k] * ctx->D, ctx->h_tail + TAIL_FINALS + (size_t)k * ctx->D, 4 * (size_t)ctx->D);
+                    for (int c = 0; c < ctx->D; c++) folded[(size_t)ctx->order[k] * ctx->D + c] = ctx->h_tail[TAIL_FINALS + (size_t)k * ctx->D + c] & ~TAIL_HERE;
             return SC_OK;
         }
         if (!tail_recover(ctx, ctx->tail_rounds)) {   // else: the last fold below, by the challenge it did not wait for

@@ -215,6 +215,9 @@ struct SvArgs {
     u32 *out_host;        // the same in mapped host memory (may be NULL), then the word below
     u32 seq;              // posted at word SV_FLAG of out_host
     DevStatement st;      // the statement, for the kernels that read the term table
+    int ngroups;          // sums kept per grid point, as in the base-table round kernel (see RoundArgs::gcoef) ...
+    int use_gcoef;        // ... 1: some group's coefficient is not one ...
+    u32 gcoef[MAX_GROUPS][8];   // ... the groups' coefficients (Montgomery form), applied by the last block
 };
 constexpr int SV_MAX_WORDS = 128;  // G^2 D words: G <= 4, D <= 8
 constexpr int SV_FLAG = SV_MAX_WORDS;
@@ -227,7 +230,8 @@ bool small_values_supported(int D, int G, int nt);
 // polls -- for the challenge the host's transcript derives from them, folds, and goes on; after
 // the last challenge it folds once more and posts the final entries.  The transcript stays on
 // the host.  Slot k of the mapped buffer (TAIL_SLOT_WORDS words) belongs to round k of the launch:
-//   [0, 32) sums   [32] posted = seq + k   [40, 48) challenge (canonical)   [48] sent = seq + k
+//   [0, 32) sums   [40, 48) challenge (canonical), each word with TAIL_HERE set once it is written (cleared by the host before the launch)
+//   the device's own transcript instead: [32] posted = seq + k, [50] challenge posted, [52, 60) the challenge
 // word TAIL_STATUS of the buffer: 0 running, 1 finished, 2 gave up waiting, 3 told to stop;
 // word TAIL_STOP: the host sets it to seq to make the kernel return at its next poll;
 // the final entries (ntables * D words) start at word TAIL_FINALS, posted at TAIL_FINALS - 1.
@@ -237,6 +241,7 @@ constexpr int TAIL_STATUS = TAIL_MAX_ROUNDS * TAIL_SLOT_WORDS;
 constexpr int TAIL_STOP = TAIL_STATUS + 1;
 constexpr int TAIL_FINALS = TAIL_STATUS + 16;
 constexpr int TAIL_WORDS = TAIL_FINALS + SC_MAX_TABLES * 8;
+constexpr u32 TAIL_HERE = 0x80000000u;           // set in a word that has been written (elements are below p < 2^31)
 constexpr unsigned TAIL_POLL_LIMIT = 1500000u;   // polls of mapped host memory (about a microsecond each) before giving up
 struct TailRound {
     u64 npairs;
@@ -249,6 +254,7 @@ struct TailArgs {
     uint8_t src_base[SC_MAX_TABLES];
     int ntables;
     int nrounds;
+    int nofold;                        // 1: the launch's first round has no challenge to fold by: it sums the pairs of src as they lie (2 entries per pair)
     TailRound rd[TAIL_MAX_ROUNDS];
     u32 r[8];                          // the challenge of the round before the launch, Montgomery form
     const u32 *weights;

@@ -139,6 +139,7 @@ static int prove_parts(sc_ctx *const *ctxs, std::vector<Part> &parts, sc_transcr
                        int blocks, const u32 *bw, int degree, std::vector<HostField::E> *challenges,
                        std::vector<std::vector<u32>> *folded, PartWorkers *workers) {
     const int D = sc_transcript_degree(tr), L = (int)parts.size();
+    const auto t_enter = std::chrono::steady_clock::now();
     int points = 1, rc;
     for (int l = 0; l < L; l++) {
         Part &pt = parts[l];
@@ -173,6 +174,8 @@ static int prove_parts(sc_ctx *const *ctxs, std::vector<Part> &parts, sc_transcr
         }
         if ((rc = sc_begin(ctxs[l], n, eq, blocks, blocks > 1 ? bw : nullptr))) return rc;   // one block: its weight is 1
     }
+    static const bool trace = getenv("SABLE_B200_TRACE") != nullptr;
+    const auto t_begun = std::chrono::steady_clock::now();
     std::vector<uint8_t> header(label, label + strlen(label));   // label | "|" | n u16 | degree u16 | blocks u32 (:24-27)
     header.push_back('|');
     header.push_back((uint8_t)n); header.push_back((uint8_t)(n >> 8));
@@ -200,11 +203,15 @@ static int prove_parts(sc_ctx *const *ctxs, std::vector<Part> &parts, sc_transcr
         challenges->push_back(r);
     }
     folded->clear();
+    const auto t_rounds = std::chrono::steady_clock::now();
     for (int l = 0; l < L; l++) {
         std::vector<u32> out(parts[l].names.size() * (size_t)blocks * D);
         if ((rc = sc_finish(ctxs[l], out.data()))) return rc;
         folded->push_back(out);
     }
+    if (trace) fprintf(stderr, "  proof of %d rounds: statement, tables and sc_begin %.1f us, rounds %.1f us, finish %.1f us\n", n,
+                       std::chrono::duration<double, std::micro>(t_begun - t_enter).count(), std::chrono::duration<double, std::micro>(t_rounds - t_begun).count(),
+                       std::chrono::duration<double, std::micro>(std::chrono::steady_clock::now() - t_rounds).count());
     return SC_OK;
 }
 
@@ -410,6 +417,7 @@ extern "C" int sc_gkr_prove_upper(sc_ctx *const *ctxs, int lookups, sc_transcrip
         const std::vector<u32> eq = flat(ri), bwf = flat(bw);
         std::vector<E> rho;
         std::vector<Part> saved = parts;
+        if (trace) fprintf(stderr, "gkr layer %d: %.1f us before its proof\n", layer, std::chrono::duration<double, std::micro>(std::chrono::steady_clock::now() - t_layer).count());
         if ((rc = prove_parts(ctxs, parts, tr, layer, layer > 0 ? eq.data() : nullptr, label, K, bwf.data(), layer > 0 ? 2 : 0, &rho, &folded, workers.get()))) return rc;
         std::vector<std::vector<E>> finals(L, std::vector<E>(4));
         std::vector<E> rbn;

@@ -20,12 +20,6 @@ template <int NT> __device__ __forceinline__ u32 pick_base(const u32 (&val)[NT],
     return o;
 }
 
-// The sums a listed statement (device.h) keeps in this kernel: one for its terms with base-field coefficients, if it
-// has any, and one for its term with an extension-field coefficient, if it has one (at most one: MAX_GROUPS).
-template <class S> __host__ __device__ constexpr int listed_ext_terms() { int n = 0; for (int t = 0; t < S::NTERMS; t++) n += S::ck(t) == CK_EXT; return n; }
-template <class S> __host__ __device__ constexpr int listed_groups() { return (listed_ext_terms<S>() < S::NTERMS ? 1 : 0) + listed_ext_terms<S>(); }
-template <class S> __host__ __device__ constexpr int listed_group(int t) { return S::ck(t) == CK_EXT && listed_ext_terms<S>() < S::NTERMS ? 1 : 0; }
-
 // SHAPE: SHAPE_GENERIC (term descriptors from the arguments, kept in registers), SHAPE_PRODUCT, or a listed statement
 template <int D, int PTS, int NT, int NG, int SHAPE>
 __global__ void __launch_bounds__(ROUND_THREADS, round_base_blocks_per_sm(D, SHAPE, PTS, NG)) round_base_kernel(const __grid_constant__ RoundArgs a) {

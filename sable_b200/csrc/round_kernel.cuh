@@ -154,6 +154,13 @@ __device__ __forceinline__ Ext<D> eval_statement(const DevStatement &st, const E
     return acc;
 }
 
+// The sums a listed statement (device.h) keeps in the kernels that sum base-field values (the base-table round kernel,
+// the small-value pass): one for its terms with base-field coefficients, if it has any, and one for its term with an
+// extension-field coefficient, if it has one (at most one: MAX_GROUPS).
+template <class S> __host__ __device__ constexpr int listed_ext_terms() { int n = 0; for (int t = 0; t < S::NTERMS; t++) n += S::ck(t) == CK_EXT; return n; }
+template <class S> __host__ __device__ constexpr int listed_groups() { return (listed_ext_terms<S>() < S::NTERMS ? 1 : 0) + listed_ext_terms<S>(); }
+template <class S> __host__ __device__ constexpr int listed_group(int t) { return S::ck(t) == CK_EXT && listed_ext_terms<S>() < S::NTERMS ? 1 : 0; }
+
 // A statement of the list (device.h): the same evaluation as eval_statement with every loop bound, table index
 // and coefficient kind a compile-time constant, so it unrolls into straight-line code.
 template <int D, class S, bool BASEAWARE>

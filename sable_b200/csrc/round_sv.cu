@@ -8,9 +8,13 @@
 // src/field.lisp:213-218); the reduced sums wait in shared memory, and the low weight multiplies
 // once at the very end.  Blocks' rows are added by the last block to finish (no waiting).
 // The grid of G^2 points is cut along its second variable (blockIdx.y) so that a thread's sums fit its
-// registers: two rows per block at D = 4 (rows z1 < 2 are the entries' own rows), one row at D = 8.
+// registers: two rows per block at D = 4 (rows z1 < 2 are the entries' own rows), one row at D = 8 or with two groups.
 // The statement at a grid point is a product of the tables (SHAPE_PRODUCT), a listed statement resolved at
-// compile time, or the term table with its descriptors in registers, as in the base-table round kernel.
+// compile time, or the term table with its descriptors in registers, as in the base-table round kernel; as there,
+// a term with an extension-field coefficient is summed without it in a group of its own (NG = 2), and the last
+// block multiplies each group's accumulators by the group's coefficient before it adds them up: so a statement
+// with constants takes these rounds too (the reference folds those from round 0: its kernel works on base values
+// only, src/sumcheck.lisp:535-539), and the proof bytes are the same.
 #include "round_kernel.cuh"
 
 namespace sc {
@@ -23,11 +27,14 @@ template <int NT> __device__ __forceinline__ u32 sv_pick(const u32 (&val)[NT], i
     return o;
 }
 
-template <int D, int G, int NT, int SHAPE>
+template <int D, int NG> __host__ __device__ constexpr int sv_rows() { return D == 4 && NG == 1 ? 2 : 1; }
+
+template <int D, int G, int NT, int SHAPE, int NG>
 __global__ void __launch_bounds__(ROUND_THREADS, G > 2 ? 2 : 1) sv_kernel(const __grid_constant__ SvArgs a) {
-    constexpr int ROWS1 = D == 4 ? 2 : 1;         // rows of the grid (values of z1) a block handles, at most
-    constexpr int Z = G * ROWS1, W = Z * D;       // this block's share of the accumulators
-    constexpr int WALL = G * G * D;               // all of them
+    constexpr int ROWS1 = sv_rows<D, NG>();       // rows of the grid (values of z1) a block handles, at most
+    constexpr int Z = G * ROWS1, W = NG * Z * D;  // this block's share of the accumulators
+    constexpr int WONE = G * G * D;               // one group's accumulators
+    constexpr int WALL = NG * WONE;               // all of them
     const int z1lo = blockIdx.y * ROWS1;          // its first row
     const int nrows = (G - z1lo) < ROWS1 ? (G - z1lo) : ROWS1;
     extern __shared__ __align__(16) u32 tot[];   // [W][ROUND_THREADS]
@@ -48,7 +55,7 @@ __global__ void __launch_bounds__(ROUND_THREADS, G > 2 ? 2 : 1) sv_kernel(const 
         desc[t] = 0; coef[t] = 0;
         if (SHAPE != SHAPE_PRODUCT && t < nterms) {
             const DevTerm &tm = a.st.terms[t];
-            u32 ds = (u32)tm.nf | ((u32)tm.ckind << 4);
+            u32 ds = (u32)tm.nf | ((u32)tm.ckind << 4) | ((u32)(tm.group & 1) << 6);
             for (int k = 0; k < BASE_MAX_FACTORS && k < tm.nf; k++) ds |= (u32)tm.f[k] << (8 + 4 * k);
             desc[t] = ds;
             coef[t] = tm.coeff[0];
@@ -56,31 +63,31 @@ __global__ void __launch_bounds__(ROUND_THREADS, G > 2 ? 2 : 1) sv_kernel(const 
     }
     // the statement on the tables' values at one grid point (base field; the factor R^-e the products leave behind
     // is the final factor's business, as in every round kernel)
-    auto statement = [&](const u32 (&val)[NT]) -> u32 {
-        if (SHAPE == SHAPE_PRODUCT) {
-            u32 f = val[0];
+    auto statement = [&](const u32 (&val)[NT], u32 (&f)[NG]) {
 #pragma unroll
-            for (int t = 1; t < NT; t++) f = mmul(f, val[t]);
-            return f;
+        for (int g = 0; g < NG; g++) f[g] = 0;
+        if (SHAPE == SHAPE_PRODUCT) {
+            u32 pr = val[0];
+#pragma unroll
+            for (int t = 1; t < NT; t++) pr = mmul(pr, val[t]);
+            f[0] = pr;
         } else if (SHAPE >= SHAPE_LISTED) {
             typedef Listed<(SHAPE >= SHAPE_LISTED ? SHAPE - SHAPE_LISTED : 0)> S;
-            u32 f = 0;
 #pragma unroll
             for (int t = 0; t < S::NTERMS; t++) {
                 u32 pr = val[S::f(t, 0) < NT ? S::f(t, 0) : 0];
 #pragma unroll
                 for (int k = 1; k < S::nf(t); k++) pr = mmul(pr, val[S::f(t, k) < NT ? S::f(t, k) : 0]);
-                pr = mmul(pr, coef[t < BASE_MAX_TERMS ? t : 0]);   // a listed statement's coefficients here are base elements
-                f = fadd(f, pr);
+                if (S::ck(t) == CK_BASE) pr = mmul(pr, coef[t < BASE_MAX_TERMS ? t : 0]);   // the others wait for the group's coefficient
+                const int g = listed_group<S>(t) < NG ? listed_group<S>(t) : 0;
+                f[g] = fadd(f[g], pr);
             }
-            return f;
         } else {
-            u32 f = 0;
 #pragma unroll
             for (int t = 0; t < BASE_MAX_TERMS; t++) {
                 if (t < nterms) {
                     const u32 ds = desc[t];
-                    const int nf = ds & 15, ckind = (ds >> 4) & 3;
+                    const int nf = ds & 15, ckind = (ds >> 4) & 3, group = (ds >> 6) & 1;
                     u32 pr;
                     if (nf == 0) pr = coef[t];
                     else {
@@ -90,30 +97,34 @@ __global__ void __launch_bounds__(ROUND_THREADS, G > 2 ? 2 : 1) sv_kernel(const 
                             if (k < nf) pr = mmul(pr, sv_pick<NT>(val, (ds >> (8 + 4 * k)) & 15));
                         if (ckind == CK_BASE) pr = mmul(pr, coef[t]);
                     }
-                    f = fadd(f, pr);
+                    if (NG > 1 && group) f[NG - 1] = fadd(f[NG - 1], pr);
+                    else f[0] = fadd(f[0], pr);
                 }
             }
-            return f;
         }
     };
 
-    u64 acc[Z][D];
+    u64 acc[NG][Z][D];
 #pragma unroll
-    for (int z = 0; z < Z; z++)
+    for (int g = 0; g < NG; g++)
 #pragma unroll
-        for (int c = 0; c < D; c++) acc[z][c] = 0;
+        for (int z = 0; z < Z; z++)
+#pragma unroll
+            for (int c = 0; c < D; c++) acc[g][z][c] = 0;
     for (int k = 0; k < W; k++) tot[k * ROUND_THREADS + tid] = 0;
     int pending = 0;
 
     auto reduce = [&]() {
 #pragma unroll
-        for (int z = 0; z < Z; z++)
+        for (int g = 0; g < NG; g++)
 #pragma unroll
-            for (int c = 0; c < D; c++) {
-                u32 *slot = tot + (z * D + c) * ROUND_THREADS + tid;
-                *slot = fadd(*slot, redc4(acc[z][c]));
-                acc[z][c] = 0;
-            }
+            for (int z = 0; z < Z; z++)
+#pragma unroll
+                for (int c = 0; c < D; c++) {
+                    u32 *slot = tot + ((g * Z + z) * D + c) * ROUND_THREADS + tid;
+                    *slot = fadd(*slot, redc4(acc[g][z][c]));
+                    acc[g][z][c] = 0;
+                }
         pending = 0;
     };
 
@@ -177,9 +188,12 @@ __global__ void __launch_bounds__(ROUND_THREADS, G > 2 ? 2 : 1) sv_kernel(const 
             u32 val[NT];
 #pragma unroll
             for (int t = 0; t < NT; t++) val[t] = g[t][z];
-            const u32 f = statement(val);
+            u32 f[NG];
+            statement(val, f);
 #pragma unroll
-            for (int c = 0; c < D; c++) acc[z][c] += (u64)hw[c] * f;
+            for (int g = 0; g < NG; g++)
+#pragma unroll
+                for (int c = 0; c < D; c++) acc[g][z][c] += (u64)hw[c] * f[g];
         }
         if (++pending == 4) reduce();
     }
@@ -191,7 +205,7 @@ __global__ void __launch_bounds__(ROUND_THREADS, G > 2 ? 2 : 1) sv_kernel(const 
         ExtM<D> lw;
 #pragma unroll
         for (int c = 0; c < D; c++) { lw.v[c] = __ldg(w + c); lw.t[c] = __ldg(w + D + c); }
-        for (int z = 0; z < Z; z++) {
+        for (int z = 0; z < NG * Z; z++) {
             Ext<D> v;
 #pragma unroll
             for (int c = 0; c < D; c++) v.v[c] = tot[(z * D + c) * ROUND_THREADS + tid];
@@ -202,12 +216,13 @@ __global__ void __launch_bounds__(ROUND_THREADS, G > 2 ? 2 : 1) sv_kernel(const 
     }
     __syncthreads();
     // the block's share of its row of partial sums: word k summed over the threads
-    for (int k = tid >> 5; k < nrows * G * D; k += ROUND_THREADS / 32) {
+    for (int gk = tid >> 5; gk < NG * nrows * G * D; gk += ROUND_THREADS / 32) {
+        const int g = gk / (nrows * G * D), k = gk % (nrows * G * D);
         u32 v = 0;
-        for (int j = tid & 31; j < ROUND_THREADS; j += 32) v = fadd(v, tot[k * ROUND_THREADS + j]);
+        for (int j = tid & 31; j < ROUND_THREADS; j += 32) v = fadd(v, tot[(g * Z * D + k) * ROUND_THREADS + j]);
 #pragma unroll
         for (int off = 16; off > 0; off >>= 1) v = fadd(v, __shfl_down_sync(0xffffffffu, v, off));
-        if ((tid & 31) == 0) a.partials[(size_t)blockIdx.x * WALL + z1lo * G * D + k] = v;
+        if ((tid & 31) == 0) a.partials[(size_t)blockIdx.x * WALL + g * WONE + z1lo * G * D + k] = v;
     }
     __threadfence();
     __syncthreads();
@@ -215,7 +230,8 @@ __global__ void __launch_bounds__(ROUND_THREADS, G > 2 ? 2 : 1) sv_kernel(const 
     __syncthreads();
     if (!is_last) return;
     __threadfence();
-    __shared__ u32 row[SV_MAX_WORDS];
+    __shared__ u32 row[MAX_GROUPS * SV_MAX_WORDS];
+    static_assert(WALL <= ROUND_THREADS && WALL <= MAX_GROUPS * SV_MAX_WORDS, "one thread per accumulator word");
     if (tid < WALL) {
         u32 v = 0;
         for (unsigned b = 0; b < gridDim.x; b++) v = fadd(v, __ldcg(a.partials + (size_t)b * WALL + tid));
@@ -226,6 +242,16 @@ __global__ void __launch_bounds__(ROUND_THREADS, G > 2 ? 2 : 1) sv_kernel(const 
         Ext<D> s;
 #pragma unroll
         for (int c = 0; c < D; c++) s.v[c] = row[tid * D + c];
+        if (NG > 1 || a.use_gcoef) {   // each group's accumulators times the group's coefficient
+            s = ezero<D>();
+#pragma unroll
+            for (int g = 0; g < NG; g++) {
+                Ext<D> v, gc;
+#pragma unroll
+                for (int c = 0; c < D; c++) { v.v[c] = row[g * WONE + tid * D + c]; gc.v[c] = a.gcoef[g][c]; }
+                s = eadd<D>(s, emul<D>(v, gc));
+            }
+        }
         if (a.use_post) {
             Ext<D> pf;
 #pragma unroll
@@ -248,44 +274,56 @@ __global__ void __launch_bounds__(ROUND_THREADS, G > 2 ? 2 : 1) sv_kernel(const 
     }
 }
 
-template <int D, int G, int NT, int SHAPE> static cudaError_t launch_sv_one(const SvArgs &args, int grid, cudaStream_t stream) {
-    constexpr int ROWS1 = D == 4 ? 2 : 1;
-    const size_t smem = (size_t)G * ROWS1 * D * ROUND_THREADS * 4;
-    cudaFuncSetAttribute(sv_kernel<D, G, NT, SHAPE>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-    sv_kernel<D, G, NT, SHAPE><<<dim3(grid, (G + ROWS1 - 1) / ROWS1), ROUND_THREADS, smem, stream>>>(args);
+template <int D, int G, int NT, int SHAPE, int NG> static cudaError_t launch_sv_one(const SvArgs &args, int grid, cudaStream_t stream) {
+    constexpr int ROWS1 = sv_rows<D, NG>();
+    const size_t smem = (size_t)NG * G * ROWS1 * D * ROUND_THREADS * 4;
+    cudaFuncSetAttribute(sv_kernel<D, G, NT, SHAPE, NG>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    sv_kernel<D, G, NT, SHAPE, NG><<<dim3(grid, (G + ROWS1 - 1) / ROWS1), ROUND_THREADS, smem, stream>>>(args);
     return cudaGetLastError();
 }
-template <int D, int G> static cudaError_t launch_sv_generic(int nt, const SvArgs &args, int grid, cudaStream_t stream) {
+template <int D, int G, int NG> static cudaError_t launch_sv_generic(int nt, const SvArgs &args, int grid, cudaStream_t stream) {
     switch (nt) {
-    case 1: return launch_sv_one<D, G, 1, SHAPE_GENERIC>(args, grid, stream);
-    case 2: return launch_sv_one<D, G, 2, SHAPE_GENERIC>(args, grid, stream);
-    case 3: return launch_sv_one<D, G, 3, SHAPE_GENERIC>(args, grid, stream);
+    case 1: return launch_sv_one<D, G, 1, SHAPE_GENERIC, NG>(args, grid, stream);
+    case 2: return launch_sv_one<D, G, 2, SHAPE_GENERIC, NG>(args, grid, stream);
+    case 3: return launch_sv_one<D, G, 3, SHAPE_GENERIC, NG>(args, grid, stream);
     }
     return cudaErrorInvalidValue;
 }
-template <int D> static cudaError_t launch_sv_d(int shape, int G, int nt, const SvArgs &args, int grid, cudaStream_t stream) {
-    if (shape == SHAPE_PRODUCT && G == nt + 1) {
+template <int D, int K> static cudaError_t launch_sv_listed(const SvArgs &args, int grid, cudaStream_t stream) {
+    typedef Listed<K> S;   // the groups its entry says, as in the base-table kernel
+    return launch_sv_one<D, S::PTS + 1, S::NT, SHAPE_LISTED + K, listed_groups<S>()>(args, grid, stream);
+}
+template <int D> static cudaError_t launch_sv_d(int shape, int G, int nt, int ng, const SvArgs &args, int grid, cudaStream_t stream) {
+    if (shape == SHAPE_PRODUCT && G == nt + 1 && ng == 1) {
         switch (nt) {
-        case 1: return launch_sv_one<D, 2, 1, SHAPE_PRODUCT>(args, grid, stream);
-        case 2: return launch_sv_one<D, 3, 2, SHAPE_PRODUCT>(args, grid, stream);
-        case 3: return launch_sv_one<D, 4, 3, SHAPE_PRODUCT>(args, grid, stream);
+        case 1: return launch_sv_one<D, 2, 1, SHAPE_PRODUCT, 1>(args, grid, stream);
+        case 2: return launch_sv_one<D, 3, 2, SHAPE_PRODUCT, 1>(args, grid, stream);
+        case 3: return launch_sv_one<D, 4, 3, SHAPE_PRODUCT, 1>(args, grid, stream);
         }
     }
-    if (shape == SHAPE_LISTED + 0) return launch_sv_one<D, Listed<0>::PTS + 1, Listed<0>::NT, SHAPE_LISTED + 0>(args, grid, stream);
-    if (shape == SHAPE_LISTED + 1) return launch_sv_one<D, Listed<1>::PTS + 1, Listed<1>::NT, SHAPE_LISTED + 1>(args, grid, stream);
-    switch (G) {
-    case 2: return launch_sv_generic<D, 2>(nt, args, grid, stream);
-    case 3: return launch_sv_generic<D, 3>(nt, args, grid, stream);
-    case 4: return launch_sv_generic<D, 4>(nt, args, grid, stream);
+    if (shape == SHAPE_LISTED + 0 && ng == listed_groups<Listed<0>>()) return launch_sv_listed<D, 0>(args, grid, stream);
+    if (shape == SHAPE_LISTED + 1 && ng == listed_groups<Listed<1>>()) return launch_sv_listed<D, 1>(args, grid, stream);
+    if (ng == 1) {
+        switch (G) {
+        case 2: return launch_sv_generic<D, 2, 1>(nt, args, grid, stream);
+        case 3: return launch_sv_generic<D, 3, 1>(nt, args, grid, stream);
+        case 4: return launch_sv_generic<D, 4, 1>(nt, args, grid, stream);
+        }
+    } else {
+        switch (G) {
+        case 2: return launch_sv_generic<D, 2, 2>(nt, args, grid, stream);
+        case 3: return launch_sv_generic<D, 3, 2>(nt, args, grid, stream);
+        case 4: return launch_sv_generic<D, 4, 2>(nt, args, grid, stream);
+        }
     }
     return cudaErrorInvalidValue;
 }
 // G = points + 1 grid values per variable: degree at most three, at most three tables in the statement
 bool small_values_supported(int D, int G, int nt) { return (D == 4 || D == 8) && nt >= 1 && nt <= 3 && G >= 2 && G <= 4; }
 cudaError_t launch_small_values(int D, int shape, int G, int nt, const SvArgs &args, int grid, cudaStream_t stream) {
-    if (!small_values_supported(D, G, nt)) return cudaErrorInvalidValue;
+    if (!small_values_supported(D, G, nt) || args.ngroups < 1 || args.ngroups > MAX_GROUPS) return cudaErrorInvalidValue;
     if (shape == SHAPE_LISTED + 2 || shape == SHAPE_GKR) shape = SHAPE_GENERIC;
-    return D == 4 ? launch_sv_d<4>(shape, G, nt, args, grid, stream) : launch_sv_d<8>(shape, G, nt, args, grid, stream);
+    return D == 4 ? launch_sv_d<4>(shape, G, nt, args.ngroups, args, grid, stream) : launch_sv_d<8>(shape, G, nt, args.ngroups, args, grid, stream);
 }
 
 }  // namespace sc

@@ -3,10 +3,16 @@
 // The arithmetic of a round is that of round_kernel with FOLD: entries 4i .. 4i+3 of every table
 // are folded by the last challenge into the pair (2i, 2i+1), written, and the statement is summed
 // over the pairs with the round's eq weights (one weight per pair: the tables are small, the
-// weights are not split).  What differs is that the block stays resident between rounds and gets
+// weights are not split); when the launch starts at a round that has no challenge to fold by (round 0, or the round
+// after a gather) its first round sums the pairs as they lie.  What differs is that the block stays resident between rounds and gets
 // each challenge from the host through mapped memory, so a round costs a few microseconds
 // instead of a launch and a completion.  Every wait is bounded: a block that hears nothing for
 // its limit of polls, or is told to stop, records why and returns.
+//
+// The words that cross PCIe on the way carry their own "here" mark: every element word is below p < 2^31, so bit 31
+// of each word says that the word has been written (the host clears the words before the launch).  The host polls the
+// sums' words and the block polls the challenge's words themselves -- one read over PCIe instead of a flag and then
+// the data, and no fence between data and flag on the device.
 //
 // With own_transcript the block does not wait at all: it carries the transcript's hash state on
 // (transcript.cuh) and derives every challenge itself (SEND of its sums, CHALLENGE), posting sums and
@@ -54,19 +60,66 @@ __global__ void __launch_bounds__(ROUND_THREADS) tail_kernel(const __grid_consta
     for (int k = 0; k < a.nrounds; k++) {
         const u32 t_round = timer_ns();
         const TailRound rd = a.rd[k];
-        const int out = k & 1;
+        const bool plain = a.nofold && k == 0;   // nothing to fold by yet: the pairs (2i, 2i+1) as they lie, nothing written
+        const int kk = k - a.nofold;             // the number of this round's fold
+        const int out = kk & 1;
         Ext<D> total[PTS];
 #pragma unroll
         for (int x = 0; x < PTS; x++) total[x] = ezero<D>();
-        for (u64 i = tid; i < rd.npairs; i += ROUND_THREADS) {
+        for (u64 i = tid; plain && i < rd.npairs; i += ROUND_THREADS) {
+            Ext<D> hw;
+            if (rd.use_high) hw = *reinterpret_cast<const Ext<D> *>(a.weights + rd.high_word + i * D);
+            Ext<D> val[NT], slope[NT];
+#pragma unroll
+            for (int t = 0; t < NT; t++) {
+                Ext<D> e0 = ezero<D>(), e1 = ezero<D>();
+                if (a.src_base[t]) {
+                    const uint2 w = *reinterpret_cast<const uint2 *>(a.src[t] + 2 * i);
+                    e0.v[0] = w.x; e1.v[0] = w.y;
+                } else {
+                    e0 = load_ext<D>(a.src[t] + (2 * i) * D);
+                    e1 = load_ext<D>(a.src[t] + (2 * i + 1) * D);
+                }
+                val[t] = e0;
+                slope[t] = esub<D>(e1, e0);
+            }
+            Ext<D> sum[PTS];
+#pragma unroll
+            for (int x = 0; x < PTS; x++) {
+                if (x == 1) {
+#pragma unroll
+                    for (int t = 0; t < NT; t++) val[t] = eadd<D>(eadd<D>(val[t], slope[t]), slope[t]);
+                } else if (x > 1) {
+#pragma unroll
+                    for (int t = 0; t < NT; t++) val[t] = eadd<D>(val[t], slope[t]);
+                }
+                bool unused = false;
+                if (SHAPE == SHAPE_PRODUCT) sum[x] = eval_product<D, NT, false>(val, 0u, &unused);
+                else if (SHAPE == SHAPE_GKR) sum[x] = eval_gkr<D, false>(reinterpret_cast<const Ext<D>(&)[4]>(val), lam, 0u);
+                else if (SHAPE >= SHAPE_LISTED) {
+                    typedef Listed<(SHAPE >= SHAPE_LISTED ? SHAPE - SHAPE_LISTED : 0)> S;
+                    sum[x] = eval_listed<D, S, false>(a.st, reinterpret_cast<const Ext<D>(&)[S::NT]>(val), 0u, &unused);
+                }
+                else sum[x] = eval_statement<D, NT, false>(a.st, val, 0u, &unused);
+            }
+            if (rd.use_high) {
+                const ExtM<D> hm = eprep<D>(hw);
+#pragma unroll
+                for (int x = 0; x < PTS; x++) total[x] = eadd<D>(total[x], emul<D>(sum[x], hm));
+            } else {
+#pragma unroll
+                for (int x = 0; x < PTS; x++) total[x] = eadd<D>(total[x], sum[x]);
+            }
+        }
+        for (u64 i = tid; !plain && i < rd.npairs; i += ROUND_THREADS) {
             // the weight and every table's entries are asked for first: a round here is a chain of latencies
             Ext<D> hw;
             if (rd.use_high) hw = *reinterpret_cast<const Ext<D> *>(a.weights + rd.high_word + i * D);
             Ext<D> e[NT][4];
 #pragma unroll
             for (int t = 0; t < NT; t++) {
-                const u32 *src = k == 0 ? a.src[t] : a.buf[out ^ 1][t];
-                if (k == 0 && a.src_base[t]) {
+                const u32 *src = kk == 0 ? a.src[t] : a.buf[out ^ 1][t];
+                if (kk == 0 && a.src_base[t]) {
                     const uint4 w = *reinterpret_cast<const uint4 *>(src + 4 * i);
                     e[t][0].v[0] = w.x; e[t][1].v[0] = w.y; e[t][2].v[0] = w.z; e[t][3].v[0] = w.w;
                 } else {
@@ -78,7 +131,7 @@ __global__ void __launch_bounds__(ROUND_THREADS) tail_kernel(const __grid_consta
 #pragma unroll
             for (int t = 0; t < NT; t++) {
                 Ext<D> lo, hi;
-                if (k == 0 && a.src_base[t]) {   // base entries: D base products (FOLD-FLAT-TABLE, src/sumcheck.lisp:95-98)
+                if (kk == 0 && a.src_base[t]) {   // base entries: D base products (FOLD-FLAT-TABLE, src/sumcheck.lisp:95-98)
                     const u32 s0 = fsub(e[t][1].v[0], e[t][0].v[0]), s1 = fsub(e[t][3].v[0], e[t][2].v[0]);
 #pragma unroll
                     for (int c = 0; c < D; c++) { lo.v[c] = mmul(rm.v[c], s0); hi.v[c] = mmul(rm.v[c], s1); }
@@ -95,9 +148,9 @@ __global__ void __launch_bounds__(ROUND_THREADS) tail_kernel(const __grid_consta
                 slope[t] = esub<D>(hi, lo);
             }
             for (int t = NT; t < a.ntables; t++) {   // tables outside the statement are only folded
-                const u32 *src = k == 0 ? a.src[t] : a.buf[out ^ 1][t];
+                const u32 *src = kk == 0 ? a.src[t] : a.buf[out ^ 1][t];
                 Ext<D> lo, hi;
-                if (k == 0 && a.src_base[t]) {
+                if (kk == 0 && a.src_base[t]) {
                     const uint4 w = *reinterpret_cast<const uint4 *>(src + 4 * i);
                     const u32 s0 = fsub(w.y, w.x), s1 = fsub(w.w, w.z);
 #pragma unroll
@@ -169,7 +222,10 @@ __global__ void __launch_bounds__(ROUND_THREADS) tail_kernel(const __grid_consta
                 s = emul<D>(s, pf);
             }
 #pragma unroll
-            for (int c = 0; c < D; c++) { slot[tid * D + c] = s.v[c]; msg[tid * D + c] = s.v[c]; }
+            for (int c = 0; c < D; c++) {
+                if (a.own_transcript) { slot[tid * D + c] = s.v[c]; msg[tid * D + c] = s.v[c]; }
+                else st_sys(slot + tid * D + c, s.v[c] | TAIL_HERE);   // each word says for itself that it is there
+            }
         }
         __syncthreads();   // also: every store of the folded tables is done before the next round reads them
         if (a.own_transcript) {
@@ -186,24 +242,22 @@ __global__ void __launch_bounds__(ROUND_THREADS) tail_kernel(const __grid_consta
                 st_sys(slot + 50, a.seq + (u32)k);
             }
         } else if (tid == 0) {
-            __threadfence_system();   // cumulative: the sums written before the barrier are visible before the word below
-            st_sys(slot + 32, a.seq + (u32)k);
-            // wait for the challenge, a bounded number of polls
+            // wait for the challenge, a bounded number of polls: its words in one 128-bit read per four (each read is a
+            // trip over PCIe), every one of them marked by the host
             int ok = 0;
             for (unsigned poll = 0; poll < a.poll_limit; poll++) {
-                if (ld_sys(slot + 48) == a.seq + (u32)k) { ok = 1; break; }
-                if ((poll & 63) == 63 && ld_sys(a.host + TAIL_STOP) == a.seq) { ok = -1; break; }
-            }
-            if (ok == 1) {   // the challenge in one 128-bit read per four words (each read is a trip over PCIe)
+                u32 here = TAIL_HERE;
 #pragma unroll
                 for (int c = 0; c < D; c += 4) {
                     uint4 v;
-                    asm volatile("ld.volatile.global.v4.u32 {%0, %1, %2, %3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "l"(slot + 40 + c));
-                    chal[c] = v.x; chal[c + 1] = v.y; chal[c + 2] = v.z; chal[c + 3] = v.w;
+                    asm volatile("ld.volatile.global.v4.u32 {%0, %1, %2, %3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "l"(slot + 40 + c) : "memory");
+                    chal[c] = v.x & ~TAIL_HERE; chal[c + 1] = v.y & ~TAIL_HERE; chal[c + 2] = v.z & ~TAIL_HERE; chal[c + 3] = v.w & ~TAIL_HERE;
+                    here &= v.x & v.y & v.z & v.w;
                 }
-            } else {
-                st_sys(a.host + TAIL_STATUS, ok == 0 ? 2u : 3u);
+                if (here) { ok = 1; break; }
+                if ((poll & 63) == 63 && ld_sys(a.host + TAIL_STOP) == a.seq) { ok = -1; break; }
             }
+            if (ok != 1) st_sys(a.host + TAIL_STATUS, ok == 0 ? 2u : 3u);
             go = ok == 1;
         }
         __syncthreads();
@@ -215,22 +269,21 @@ __global__ void __launch_bounds__(ROUND_THREADS) tail_kernel(const __grid_consta
     }
     // the last fold: one entry per table, posted to the host and left in the buffer the next round would read
     {
-        const int last = (a.nrounds - 1) & 1;
+        const int folds = a.nrounds - a.nofold;   // folds done so far: the tables are in the caller's arrays still when there was none
+        const int last = (folds - 1) & 1;
         if (tid < a.ntables) {
-            const u32 *e = a.buf[last][tid];
-            const Ext<D> e0 = load_ext<D>(e), e1 = load_ext<D>(e + D);
+            Ext<D> e0 = ezero<D>(), e1 = ezero<D>();
+            if (folds == 0 && a.src_base[tid]) { e0.v[0] = a.src[tid][0]; e1.v[0] = a.src[tid][1]; }
+            else {
+                const u32 *e = folds == 0 ? a.src[tid] : a.buf[last][tid];
+                e0 = load_ext<D>(e); e1 = load_ext<D>(e + D);
+            }
             const Ext<D> f = eadd<D>(e0, emul<D>(esub<D>(e1, e0), rm));
-            store_ext<D>(a.buf[last ^ 1][tid], f);
+            store_ext<D>(a.buf[folds == 0 ? 0 : last ^ 1][tid], f);
 #pragma unroll
-            for (int c = 0; c < D; c++) a.host[TAIL_FINALS + tid * D + c] = f.v[c];
-            __threadfence_system();
+            for (int c = 0; c < D; c++) st_sys(a.host + TAIL_FINALS + tid * D + c, f.v[c] | TAIL_HERE);
         }
-        __syncthreads();
-        if (tid == 0) {
-            __threadfence_system();
-            st_sys(a.host + TAIL_FINALS - 1, a.seq);
-            st_sys(a.host + TAIL_STATUS, 1u);
-        }
+        if (tid == 0) st_sys(a.host + TAIL_STATUS, 1u);
     }
 }
 

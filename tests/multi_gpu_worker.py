@@ -124,6 +124,41 @@ def main():
             results.append({"case": statement, "n": n, "d": d, "ok": bool(ok)})
         else:
             results.append({"proof": tr.proof().hex(), "finals": finals})
+    # block weights: every rank holds its slice of every block, block after block (reference :block-weights,
+    # src/sumcheck.lisp:519-525, 549-551); sharded rounds before the gather at n = 16, the gather at once at n = 6
+    for d, K, n in ((4, 3, 16), (8, 2, 6)):
+        rng = np.random.default_rng(2000 + n)
+        statement, names = "(+ (* a b) (* lam b c))", ["a", "b", "c"]
+        full = [("a", rng.integers(0, P, size=(K << n, d), dtype=np.uint32)), ("b", rng.integers(0, P, size=K << n, dtype=np.uint32)),
+                ("c", rng.integers(0, P, size=(K << n, d), dtype=np.uint32))]
+        constants = [("lam", rng.integers(0, P, size=d, dtype=np.uint32).tolist())]
+        eq = rng.integers(0, P, size=(n, d), dtype=np.uint32)
+        bw = rng.integers(0, P, size=(K, d), dtype=np.uint32)
+        size = (1 << n) >> logw
+        mine = [np.concatenate([a[(b << n) + rank * size:(b << n) + (rank + 1) * size] for b in range(K)]) for _, a in full]
+        tr = sb.Transcript("multi", d)
+        degree, terms = sb.lower_statement(statement, d, names, constants)
+        prover.set_statement(d, max(degree, 1), len(full), terms)
+        for slot, a in enumerate(mine):
+            prover.upload_table(slot, np.ascontiguousarray(a))
+        prover.begin(n, eq=eq, block_weights=bw)
+        prover.attach_transcript(tr)
+        tr.absorb(b"sc|" + n.to_bytes(2, "little") + degree.to_bytes(2, "little") + K.to_bytes(4, "little"))
+        rho = []
+        for _ in range(n):
+            tr.send(prover.round())
+            rho.append(tr.challenge())
+            prover.challenge(rho[-1])
+        folded = prover.finish(len(full), K).tolist()
+        prover.attach_transcript(None)
+        if rank == 0:
+            from oracle import pyoracle as orc
+            tb = orc.Transcript("multi", d)
+            want = orc.prove(tb, n, statement, full, eq=eq, constants=constants, block_weights=bw, threads=0)
+            ok = rho == want[0] and folded == [want[2][nm] for nm in names] and tr.proof() == tb.proof()
+            results.append({"case": statement + " with %d blocks" % K, "n": n, "d": d, "ok": bool(ok)})
+        else:
+            results.append({"proof": tr.proof().hex(), "finals": folded})
     with open(out_file, "w") as f:
         json.dump(results, f)
     prover.close()

@@ -317,10 +317,17 @@ def test_abandoned_proof_does_not_block_the_next(prover):
     ("(- (expt t0 3) (* t0 t1))", ["t0", "t1"], True),
     ("(* t0 t1)", ["t0", "t1"], False),
     ("(+ (* 5 t1 t0) t0)", ["t0", "t1"], True),          # a listed statement
+    # an extension-field constant among the coefficients: its term is summed apart and multiplied at the end
+    ("(+ (* alpha t0 t1) (* 3 t1))", ["t0", "t1"], True),             # listed, two sums
+    ("(+ (* alpha t0 t1) (* 3 t1))", ["t0", "t1"], False),
+    ("(+ (* alpha t0 t1 t2) (* 7 t2))", ["t0", "t1", "t2"], True),    # listed, degree three
+    ("(+ (* alpha t0 t0) (* 2 t0 t1) -3)", ["t0", "t1"], True),       # the term table, two sums, a constant term
+    ("(* alpha t0 t0)", ["t0"], True),                                # the term table, one sum with the coefficient
 ])
 def test_small_value_rounds_match_folding(prover, d, statement, names, with_eq, monkeypatch):
     # reference tests/tests.lisp:374-395: the small-value rounds give the same proof as folding, byte for byte.
-    # Here they run for statements over base tables with base-field coefficients, large enough for split eq weights (n >= 22).
+    # Here they run for statements over base tables, large enough for split eq weights (n >= 22); unlike the reference's,
+    # they also take a statement with constants (at most one term with an extension-field coefficient).
     n = 22
     rng = np.random.default_rng(len(statement) + with_eq + d)
     tables = [(nm, rng.integers(0, P, size=1 << n, dtype=np.uint32)) for nm in names]
@@ -373,7 +380,7 @@ def chained():
     (4, 9, "(+ (* 7 t0 t1) t1 -3)", [0, 0]),
     (4, 3, "(* t0 t1)", [1, 0]),                                        # fewer rounds than the resident kernel's first
     (4, 21, "(+ (* t0 t3) (* t1 t2) (* alpha t2 t3))", [1, 1, 0, 0]),   # many-block launches: round 0 on the caller's tables, split weights
-    (8, 20, "(+ (* alpha t0 t1) (* 3 t1))", [1, 1]),                    # round 0 by the base-table kernel
+    (8, 20, "(+ (* alpha t0 t1) (* 3 t1))", [1, 1]),                    # base tables and an extension constant (two sums per grid point)
     (4, 22, "(* t0 t1 t2)", [1, 1, 1]),                                 # rounds 0 and 1 from one pass (host), the chain from round 2
     (4, 18, "(+ (* t0 t1) (* t1 t2) (* t2 t3) (* t3 t4) (* 3 t4 t0))", [1, 0, 0, 1, 0]),   # five tables: no resident kernel, the last fold alone
 ])
@@ -559,7 +566,8 @@ def test_degrees_five_to_eight(prover, d):
     ("(+ (* alpha t0 t1) (* 3 t1))", ["t0", "t1"]),        # base tables and an extension constant: two sums per point
     ("(+ (* t0 t1 t2) (* 7 t1))", ["t0", "t1", "t2"]),     # the reference's own base-table statement (tests/tests.lisp:333, 377)
 ])
-def test_base_table_statements_at_size(prover, d, statement, names):
+def test_base_table_statements_at_size(prover, d, statement, names, monkeypatch):
+    monkeypatch.setenv("SABLE_B200_SMALL_VALUES", "0")   # round 0 by the base-table kernel, a fold per round from round 1
     n = 22
     rng = np.random.default_rng(d + len(names))
     tables = [(nm, rng.integers(0, P, size=1 << n, dtype=np.uint32)) for nm in names]
