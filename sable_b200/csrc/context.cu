@@ -1127,10 +1127,21 @@ static int sv_round0(sc_ctx *ctx, uint32_t *sums) {
     if (sharded && ctx->use_post) ext_mul_host(D, a.post, ctx->post, a.post);   // this rank's eq weight
     a.partials = ctx->d_partials; a.counter = ctx->d_counter;
     a.st = ctx->st;
-    a.ngroups = ctx->base_groups;
-    memcpy(a.gcoef, ctx->gcoef, sizeof a.gcoef);
-    a.use_gcoef = a.ngroups > 1;
-    for (int c = 0; c < D; c++) if (ctx->gcoef[0][c] != (c == 0 ? R1 : 0u)) a.use_gcoef = 1;
+    {   // one sum per grid point while every coefficient is a base element (or rides in the final factor: a product); with a
+        // term whose coefficient is not, two: that term's products apart, multiplied by the coefficient at the end
+        bool ext_term = false;
+        for (int t = 0; t < ctx->st.nterms; t++) ext_term = ext_term || (ctx->st.terms[t].ckind == CK_EXT && ctx->st.terms[t].nf > 0);
+        if (ctx->shape == SHAPE_PRODUCT) ext_term = false;
+        a.ngroups = ext_term ? 2 : 1;
+        a.use_gcoef = ext_term ? 1 : 0;
+        memcpy(a.gcoef, ctx->gcoef, sizeof a.gcoef);
+        if (ext_term && ctx->base_groups == 1) {   // no term with a base coefficient beside it: its sum is the second all the same
+            memcpy(a.gcoef[1], ctx->gcoef[0], sizeof a.gcoef[1]);
+            memset(a.gcoef[0], 0, sizeof a.gcoef[0]);
+            a.gcoef[0][0] = R1;
+            for (int t = 0; t < a.st.nterms; t++) if (a.st.terms[t].ckind == CK_EXT) a.st.terms[t].group = 1;
+        }
+    }
     a.seq = ++ctx->seq;
     if (sharded) {
         int rc;
@@ -1212,10 +1223,11 @@ static int sv_round1(sc_ctx *ctx, uint32_t *sums) {
     return SC_OK;
 }
 
-// The last rounds run in one resident launch when the tables are small, there is one block of
-// weights, and nobody asked for per-round timing.  J: the round that would be its first.
+// The last rounds run in one resident launch when the tables (all their blocks together) are small and
+// nobody asked for per-round timing.  J: the round that would be its first.
 static bool tail_wanted(const sc_ctx *ctx, int j) {
-    if (ctx->tail_bits <= 0 || ctx->K != 1 || ctx->timing || ctx->ntables < 1 || ctx->nt_used > 4 || ctx->points > FAST_POINTS) return false;
+    if (ctx->tail_bits <= 0 || ctx->timing || ctx->ntables < 1 || ctx->nt_used > 4 || ctx->points > FAST_POINTS) return false;
+    if (ctx->ntables * ctx->K > ROUND_THREADS || ctx->ntables * ctx->K * ctx->D > TAIL_FINAL_WORDS) return false;   // one thread and D words per final entry
     if (ctx->n - j > TAIL_MAX_ROUNDS) return false;
     return ctx->tab[ctx->order[0]].cur_entries <= (1ull << ctx->tail_bits);
 }
@@ -1229,6 +1241,7 @@ static int tail_start(sc_ctx *ctx, int j, bool fold, bool chain, bool chain_firs
     memset(&a, 0, sizeof a);
     a.ntables = ctx->ntables;
     a.nrounds = ctx->n - j;
+    a.blocks = ctx->K;
     a.nofold = fold ? 0 : 1;
     u64 entries = 0;
     for (int k = 0; k < ctx->ntables; k++) {
@@ -1276,7 +1289,7 @@ static int tail_start(sc_ctx *ctx, int j, bool fold, bool chain, bool chain_firs
         for (int c = 0; c < 32; c++) slot[c] = 0;
         for (int c = 0; c < 8; c++) slot[40 + c] = 0;
     }
-    for (int c = 0; c < SC_MAX_TABLES * 8; c++) ((volatile u32 *)ctx->h_tail)[TAIL_FINALS + c] = 0;
+    for (int c = 0; c < ctx->ntables * ctx->K * D; c++) ((volatile u32 *)ctx->h_tail)[TAIL_FINALS + c] = 0;
     ((volatile u32 *)ctx->h_tail)[TAIL_STATUS] = 0;
     std::atomic_thread_fence(std::memory_order_seq_cst);
     CU(launch_tail(D, ctx->shape, ctx->points, ctx->nt_used, a, ctx->stream));
@@ -1654,7 +1667,7 @@ extern "C" int sc_finish(sc_ctx *ctx, uint32_t *folded) {
     int rc;
     if (ctx->tail_active) {   // the resident kernel folds by the last challenge and posts the final entries
         const auto t_in = std::chrono::steady_clock::now();
-        const bool ok = wait_here(ctx, ctx->h_tail + TAIL_FINALS, ctx->ntables * ctx->D);
+        const bool ok = wait_here(ctx, ctx->h_tail + TAIL_FINALS, ctx->ntables * ctx->K * ctx->D);
         // posting them was the launch's last act (its reads and writes of the tables are done, its status is written): no
         // need to wait for the stream to drain, whatever follows on it is ordered behind the launch anyway
         if (!ok) CU(cudaStreamSynchronize(ctx->stream));
@@ -1669,9 +1682,11 @@ extern "C" int sc_finish(sc_ctx *ctx, uint32_t *folded) {
             ctx->tail_active = false;
             ctx->chain_active = false;
             ctx->begun = false;
-            if (folded)
+            if (folded) {
+                const size_t KD = (size_t)ctx->K * ctx->D;   // per table: K entries
                 for (int k = 0; k < ctx->ntables; k++)
-                    for (int c = 0; c < ctx->D; c++) folded[(size_t)ctx->order[k] * ctx->D + c] = ctx->h_tail[TAIL_FINALS + (size_t)k * ctx->D + c] & ~TAIL_HERE;
+                    for (size_t c = 0; c < KD; c++) folded[(size_t)ctx->order[k] * KD + c] = ctx->h_tail[TAIL_FINALS + (size_t)k * KD + c] & ~TAIL_HERE;
+            }
             return SC_OK;
         }
         if (!tail_recover(ctx, ctx->tail_rounds)) {   // else: the last fold below, by the challenge it did not wait for

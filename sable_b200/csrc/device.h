@@ -234,13 +234,14 @@ bool small_values_supported(int D, int G, int nt);
 //   the device's own transcript instead: [32] posted = seq + k, [50] challenge posted, [52, 60) the challenge
 // word TAIL_STATUS of the buffer: 0 running, 1 finished, 2 gave up waiting, 3 told to stop;
 // word TAIL_STOP: the host sets it to seq to make the kernel return at its next poll;
-// the final entries (ntables * D words) start at word TAIL_FINALS, posted at TAIL_FINALS - 1.
+// the final entries (ntables * K * D words, table after table) start at word TAIL_FINALS, each word with TAIL_HERE set.
 constexpr int TAIL_MAX_ROUNDS = 16;
 constexpr int TAIL_SLOT_WORDS = 64;
 constexpr int TAIL_STATUS = TAIL_MAX_ROUNDS * TAIL_SLOT_WORDS;
 constexpr int TAIL_STOP = TAIL_STATUS + 1;
 constexpr int TAIL_FINALS = TAIL_STATUS + 16;
-constexpr int TAIL_WORDS = TAIL_FINALS + SC_MAX_TABLES * 8;
+constexpr int TAIL_FINAL_WORDS = 1024;           // room for the final entries: ntables * K * D words at most
+constexpr int TAIL_WORDS = TAIL_FINALS + TAIL_FINAL_WORDS;
 constexpr u32 TAIL_HERE = 0x80000000u;           // set in a word that has been written (elements are below p < 2^31)
 constexpr unsigned TAIL_POLL_LIMIT = 1500000u;   // polls of mapped host memory (about a microsecond each) before giving up
 struct TailRound {
@@ -254,6 +255,7 @@ struct TailArgs {
     uint8_t src_base[SC_MAX_TABLES];
     int ntables;
     int nrounds;
+    int blocks;                        // K: the tables are K blocks of entries, one after the other; one final entry per table and block
     int nofold;                        // 1: the launch's first round has no challenge to fold by: it sums the pairs of src as they lie (2 entries per pair)
     TailRound rd[TAIL_MAX_ROUNDS];
     u32 r[8];                          // the challenge of the round before the launch, Montgomery form

@@ -267,19 +267,20 @@ __global__ void __launch_bounds__(ROUND_THREADS) tail_kernel(const __grid_consta
         rm = eprep<D>(r);
         __syncthreads();
     }
-    // the last fold: one entry per table, posted to the host and left in the buffer the next round would read
+    // the last fold: one entry per table and block, posted to the host and left in the buffer the next round would read
     {
         const int folds = a.nrounds - a.nofold;   // folds done so far: the tables are in the caller's arrays still when there was none
         const int last = (folds - 1) & 1;
-        if (tid < a.ntables) {
+        if (tid < a.ntables * a.blocks) {
+            const int t = tid / a.blocks, b = tid % a.blocks;
             Ext<D> e0 = ezero<D>(), e1 = ezero<D>();
-            if (folds == 0 && a.src_base[tid]) { e0.v[0] = a.src[tid][0]; e1.v[0] = a.src[tid][1]; }
+            if (folds == 0 && a.src_base[t]) { e0.v[0] = a.src[t][2 * b]; e1.v[0] = a.src[t][2 * b + 1]; }
             else {
-                const u32 *e = folds == 0 ? a.src[tid] : a.buf[last][tid];
+                const u32 *e = (folds == 0 ? a.src[t] : a.buf[last][t]) + (size_t)2 * b * D;
                 e0 = load_ext<D>(e); e1 = load_ext<D>(e + D);
             }
             const Ext<D> f = eadd<D>(e0, emul<D>(esub<D>(e1, e0), rm));
-            store_ext<D>(a.buf[folds == 0 ? 0 : last ^ 1][tid], f);
+            store_ext<D>(a.buf[folds == 0 ? 0 : last ^ 1][t] + (size_t)b * D, f);
 #pragma unroll
             for (int c = 0; c < D; c++) st_sys(a.host + TAIL_FINALS + tid * D + c, f.v[c] | TAIL_HERE);
         }
