@@ -209,7 +209,7 @@ def gkr_bench(args):
     sampler = ClockSampler(0)
     sampler.start()
     mean, tr = timed(leaves, args.steps)
-    launches = (sum(p.launches for p in provers) - before) // args.steps
+    launches = sum(p.launches for p in provers) - before   # over the timed region, as in the sumcheck line
     e2e = None
     if not args.no_e2e:
         host = [(p.cpu().numpy().view(np.uint32), q.cpu().numpy().view(np.uint32)) for p, q in leaves]
