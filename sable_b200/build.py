@@ -15,7 +15,7 @@ HERE = os.path.dirname(os.path.abspath(__file__))
 CSRC = os.path.join(HERE, "csrc")
 OBJ = os.path.join(HERE, "build")
 LIB = os.path.join(HERE, "libsumcheck_b200.so")
-UNITS = ["round_d4.cu", "round_d8.cu", "round_base.cu", "round_tail.cu", "round_sv.cu", "round_d4w.cu", "round_d8w.cu", "round_d4h.cu", "round_d8h.cu", "aux_kernels.cu", "context.cu", "gkr.cu", "host.cpp", "domain.cpp"]
+UNITS = ["round_d4.cu", "round_d8.cu", "round_base.cu", "round_tail.cu", "round_sv.cu", "round_sv3.cu", "round_d4w.cu", "round_d8w.cu", "round_d4h.cu", "round_d8h.cu", "aux_kernels.cu", "context.cu", "gkr.cu", "host.cpp", "domain.cpp"]
 NVCC = os.environ.get("NVCC", "/usr/local/cuda/bin/nvcc")
 FLAGS = ["-gencode", "arch=compute_100a,code=sm_100a", "-std=c++17", "-O3", "-lineinfo", "-Xcompiler", "-fPIC",
          "-ccbin", "g++"] + os.environ.get("SC_NVCC_EXTRA", "").split()

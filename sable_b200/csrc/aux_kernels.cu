@@ -20,13 +20,14 @@ bool round_supported(int D, int points, int nt_used) {
 }
 cudaError_t launch_round(int D, int shape, int points, int nt_used, int fold, const RoundArgs &args, int grid, size_t smem, cudaStream_t stream) {
     if (fold == 2 && (points > 3 || nt_used > 3)) return cudaErrorInvalidValue;
+    if (fold == 3 && (points > 2 || nt_used > 3)) return cudaErrorInvalidValue;
     if (points > FAST_POINTS) {
-        if (fold == 2 || nt_used > 4) return cudaErrorInvalidValue;
+        if (fold >= 2 || nt_used > 4) return cudaErrorInvalidValue;
         return D == 4 ? launch_round_d4h(points, nt_used, fold, args, grid, smem, stream) : launch_round_d8h(points, nt_used, fold, args, grid, smem, stream);
     }
     if (nt_used > 4) {   // kernels exist for six and eight tables
         const int nt = nt_used <= 6 ? 6 : 8;
-        if (fold == 2) return cudaErrorInvalidValue;
+        if (fold >= 2) return cudaErrorInvalidValue;
         return D == 4 ? launch_round_d4w(points, nt, fold, args, grid, smem, stream) : launch_round_d8w(points, nt, fold, args, grid, smem, stream);
     }
     if (D == 4) return launch_round_d4(shape, points, nt_used, fold, args, grid, smem, stream);

@@ -163,9 +163,10 @@ struct sc_ctx {
 
     // the first two rounds from one pass over base tables (see SvArgs)
     bool sv_ok = false;
-    u32 sv_A[SV_MAX_WORDS];          // the accumulators, canonical
-    u32 sv_rho0[8];
-    u32 eq1[8];                      // eq element 1, canonical (the weight of variable 1 in round 0's message)
+    int sv_l0 = 2;                   // the rounds answered from the accumulators: 2, or 3 (degree at most two)
+    u32 sv_A[SV3_MAX_WORDS];         // the accumulators, canonical: G^l0 elements, index sum z_t G^t
+    u32 sv_rho[3][8];                // the challenges of those rounds
+    u32 sv_eq[3][8];                 // eq elements 1 and 2, canonical (the weights of the variables still open in those rounds' messages)
     u32 *h_sv = nullptr, *h_sv_dev = nullptr;
 
     // timing
@@ -342,9 +343,9 @@ extern "C" int sc_create(int device, sc_ctx **out) {
     if (!ok) { cudaGetLastError(); sc_destroy(ctx); return SC_ECUDA; }
     memset(ctx->h_tail, 0, TAIL_WORDS * 4);
     memset(ctx->h_out, 0, (MAX_PARTIAL_WORDS + 32) * 4);   // pinned memory comes back as an earlier context left it: its posted words must not be taken for ours
-    if (cudaHostAlloc(&ctx->h_sv, (SV_MAX_WORDS + 32) * 4, cudaHostAllocMapped) != cudaSuccess ||
+    if (cudaHostAlloc(&ctx->h_sv, (SV3_MAX_WORDS + 32) * 4, cudaHostAllocMapped) != cudaSuccess ||
         cudaHostGetDevicePointer(&ctx->h_sv_dev, ctx->h_sv, 0) != cudaSuccess) { cudaGetLastError(); sc_destroy(ctx); return SC_ECUDA; }
-    memset(ctx->h_sv, 0, (SV_MAX_WORDS + 32) * 4);
+    memset(ctx->h_sv, 0, (SV3_MAX_WORDS + 32) * 4);
     if (cudaMalloc(&ctx->d_tstate, B3_STATE_WORDS * 4) != cudaSuccess || cudaMemset(ctx->d_tstate, 0, B3_STATE_WORDS * 4) != cudaSuccess ||
         cudaMalloc(&ctx->d_chal, (size_t)CHAIN_MAX_ROUNDS * 16 * 4) != cudaSuccess ||
         cudaHostAlloc(&ctx->h_chain, (size_t)CHAIN_MAX_ROUNDS * CHAIN_SLOT_WORDS * 4, cudaHostAllocMapped) != cudaSuccess ||
@@ -786,8 +787,8 @@ extern "C" int sc_download_table(sc_ctx *ctx, int slot, uint32_t *host, uint64_t
     TableState &t = ctx->tab[slot];
     if (!t.t0) return fail(ctx, SC_ESTATE, "table %d was never uploaded", slot);
     if (ctx->tail_active || ctx->chain_active) return fail(ctx, SC_ESTATE, "the rounds are running on the device: the folded tables are not available");
-    if (ctx->begun && ctx->sv_ok && (ctx->j == 1 || ctx->j == 2))
-        return fail(ctx, SC_ESTATE, "the first two rounds ran from one pass over the tables: nothing is folded before round 2");
+    if (ctx->begun && ctx->sv_ok && ctx->j >= 1 && ctx->j <= ctx->sv_l0)
+        return fail(ctx, SC_ESTATE, "the first %d rounds ran from one pass over the tables: nothing is folded before round %d", ctx->sv_l0, ctx->sv_l0);
     cudaSetDevice(ctx->device);
     if (!ctx->begun) { t.cur = t.t0; t.cur_base = t.stride == 1; t.cur_entries = t.entries; t.cur_buf = -1; }
     if (entries) *entries = t.cur_entries;
@@ -1019,7 +1020,22 @@ extern "C" int sc_begin(sc_ctx *ctx, int n, const uint32_t *eq, int K, const uin
                   small_values_supported(D, ctx->points + 1, ctx->nt_used) && ctx->plan[1].logL >= 8;
         for (int s = 0; s < ctx->ntables && ok; s++) ok = ctx->tab[s].stride == 1;
         ctx->sv_ok = ok;
-        if (ok && eq) for (int c = 0; c < D; c++) ctx->eq1[c] = eq[D + c] % P;
+        // three rounds from the pass where the grid stays small (degree at most two: 27 points) and every coefficient is a
+        // base element, as the reference's choice goes (CHOOSE-SMALL-VALUE-KERNEL, src/sumcheck.lisp:450-455: the largest
+        // L0 up to 3 whose kernel fits); SABLE_B200_SMALL_VALUES=2 keeps it at two
+        bool ext_term = false;
+        for (int t = 0; t < ctx->st.nterms; t++) ext_term = ext_term || (ctx->st.terms[t].ckind == CK_EXT && ctx->st.terms[t].nf > 0);
+        if (ctx->shape == SHAPE_PRODUCT) ext_term = false;
+        ctx->sv_l0 = 2;
+        // (measured at n = 25-26, D = 4: three rounds against two are 1.77 / 1.76 ms for a product of two tables, 1.86 / 2.03 ms
+        // for a listed statement over two, 1.94 / 1.84 ms for a term table over three: so three tables stay at two unless
+        // SABLE_B200_SMALL_VALUES=3 asks)
+        const bool want3 = env && env[0] == '3' ? true : ctx->nt_used <= 2;
+        if (ok && want3 && !(env && env[0] == '2') && !ext_term && n >= 4 && ctx->gather_round > 3 && ctx->shape != SHAPE_LISTED + 1 &&
+            small_values3_supported(D, ctx->points + 1, ctx->nt_used) && ctx->plan[2].logL >= 8)
+            ctx->sv_l0 = 3;
+        memset(ctx->sv_eq, 0, sizeof ctx->sv_eq);
+        if (ok && eq) for (int v = 1; v < ctx->sv_l0; v++) for (int c = 0; c < D; c++) ctx->sv_eq[v][c] = eq[(size_t)v * D + c] % P;
     }
     ctx->begun = true;
     if (trace) {
@@ -1109,16 +1125,71 @@ EX ex_load(int D, const u32 *w) { EX o = {}; memcpy(o.v, w, 4 * (size_t)D); retu
 u32 fp_inv(u32 a) { u64 r = 1, x = a; for (u64 e = P - 2; e; e >>= 1) { if (e & 1) r = r * x % P; x = x * x % P; } return (u32)r; }
 }  // namespace
 
-// Round 0 of the small-value rounds: the pass over the tables, then g_0(X) = sum_u eq(r_1, u) A[X, u]
-// (SMALL-VALUE-SUMS with j = 0, src/sumcheck.lisp:481-494).
+// Round J < L0 of the small-value rounds from the accumulators A and the challenges so far (SMALL-VALUE-SUMS,
+// src/sumcheck.lisp:481-494): g_j(X) = sum_v sum_u L_v(rho) eq(r_(j+1..L0-1), u) A[v, X, u], v over {0..G-1}^j with the
+// Lagrange basis on the nodes 0 .. d at rho_0 .. rho_(j-1) (LAGRANGE-TENSOR, :463-474), u over {0,1}^(L0-1-j).
+static void sv_sums(sc_ctx *ctx, int j, uint32_t *sums) {
+    const int D = ctx->D, G = ctx->points + 1, d = ctx->points, L0 = ctx->sv_l0;
+    auto A = [&](int z) { return ex_load(D, ctx->sv_A + (size_t)z * D); };
+    std::vector<EX> tensor{ex_base(1)};                 // index sum v_t G^t
+    for (int t = 0; t < j; t++) {
+        const EX rho = ex_load(D, ctx->sv_rho[t]);
+        EX L[8];
+        for (int v = 0; v <= d; v++) {
+            EX num = ex_base(1);
+            u32 den = 1;
+            for (int k = 0; k <= d; k++) {
+                if (k == v) continue;
+                num = ex_mul(D, num, ex_sub(rho, ex_base((u32)k)));
+                den = (u32)(((u64)den * (u32)((v - k + (long long)P) % P)) % P);
+            }
+            L[v] = ex_scale(num, fp_inv(den));
+        }
+        std::vector<EX> next(tensor.size() * (size_t)G);
+        for (int v = 0; v < G; v++)
+            for (size_t w = 0; w < tensor.size(); w++) next[w + tensor.size() * (size_t)v] = ex_mul(D, tensor[w], L[v]);
+        tensor.swap(next);
+    }
+    std::vector<EX> eqs{ex_base(1)};                    // eq over the variables j+1 .. L0-1, bit t of u: variable j+1+t
+    std::vector<int> radix{0};                          // the grid index of u: its bits as base-G digits
+    for (int t = j + 1; t < L0; t++) {
+        EX w1 = ex_base(1), w0 = ex_base(1);
+        if (ctx->have_eq) { w1 = ex_load(D, ctx->sv_eq[t]); w0 = ex_sub(ex_base(1), w1); }
+        const size_t count = eqs.size();
+        int weight = 1;
+        for (int k = j + 1; k < t; k++) weight *= G;
+        eqs.resize(2 * count); radix.resize(2 * count);
+        for (size_t u = 0; u < count; u++) {
+            eqs[count + u] = ctx->have_eq ? ex_mul(D, eqs[u], w1) : eqs[u];
+            radix[count + u] = radix[u] + weight;
+            if (ctx->have_eq) eqs[u] = ex_mul(D, eqs[u], w0);
+        }
+    }
+    int gj = 1;
+    for (int t = 0; t < j; t++) gj *= G;
+    for (int xi = 0; xi < ctx->points; xi++) {
+        const int X = xi ? xi + 1 : 0;
+        EX g = ex_base(0);
+        for (size_t v = 0; v < tensor.size(); v++)
+            for (size_t u = 0; u < eqs.size(); u++) {
+                EX a = A((int)v + gj * X + gj * G * radix[u]);
+                if (ctx->have_eq) a = ex_mul(D, a, eqs[u]);
+                g = ex_add(g, j ? ex_mul(D, a, tensor[v]) : a);
+            }
+        memcpy(sums + (size_t)xi * D, g.v, 4 * (size_t)D);
+    }
+}
+
+// Round 0 of the small-value rounds: the pass over the tables, then the round's sums from the accumulators.
 static int sv_round0(sc_ctx *ctx, uint32_t *sums) {
-    const int D = ctx->D, G = ctx->points + 1, Z = G * G;
-    const RoundPlan &pl = ctx->plan[1];   // the weights of round 1 cover the variables 2 .. n-1: those of the blocks
+    const int D = ctx->D, G = ctx->points + 1, L0 = ctx->sv_l0, Z = L0 == 3 ? G * G * G : G * G;
+    const int flag_word = L0 == 3 ? SV3_FLAG : SV_FLAG;
+    const RoundPlan &pl = ctx->plan[L0 - 1];   // the weights of round L0 - 1 cover the variables L0 .. n-1: those of the blocks
     SvArgs a;
     memset(&a, 0, sizeof a);
     u64 bytes = 0;
     for (int k = 0; k < ctx->nt_used; k++) { a.src[k] = ctx->tab[ctx->order[k]].t0; bytes += ctx->tab[ctx->order[k]].entries * 4; }
-    a.nblocks = ctx->tab[ctx->order[0]].entries / 4;
+    a.nblocks = ctx->tab[ctx->order[0]].entries >> L0;
     a.logL = pl.logL; a.use_low = pl.use_low; a.use_high = pl.use_high;
     a.low = ctx->d_weights + pl.low_word; a.high = ctx->d_weights + pl.high_word;
     const bool sharded = ctx->world > 1;
@@ -1145,8 +1216,8 @@ static int sv_round0(sc_ctx *ctx, uint32_t *sums) {
     a.seq = ++ctx->seq;
     if (sharded) {
         int rc;
-        if (!ctx->d_sv && (rc = dev_alloc(ctx, (void **)&ctx->d_sv, SV_MAX_WORDS * 4))) return rc;
-        if (!ctx->d_gather && (rc = dev_alloc(ctx, (void **)&ctx->d_gather, (u64)ctx->world * SV_MAX_WORDS * 4))) return rc;
+        if (!ctx->d_sv && (rc = dev_alloc(ctx, (void **)&ctx->d_sv, SV3_MAX_WORDS * 4))) return rc;
+        if (!ctx->d_gather && (rc = dev_alloc(ctx, (void **)&ctx->d_gather, (u64)ctx->world * SV3_MAX_WORDS * 4))) return rc;
         a.out_dev = ctx->d_sv;
     } else {
         a.out_host = ctx->h_sv_dev;
@@ -1160,16 +1231,17 @@ static int sv_round0(sc_ctx *ctx, uint32_t *sums) {
         while (ctx->ev.size() < 2) { cudaEvent_t e; CU(cudaEventCreate(&e)); ctx->ev.push_back(e); }
         CU(cudaEventRecord(ctx->ev[0], ctx->stream));
     }
-    CU(launch_small_values(D, ctx->shape, G, ctx->nt_used, a, grid, ctx->stream));
+    if (L0 == 3) CU(launch_small_values3(D, ctx->shape, G, ctx->nt_used, a, grid, ctx->stream));
+    else CU(launch_small_values(D, ctx->shape, G, ctx->nt_used, a, grid, ctx->stream));
     ctx->launches++;
     if (ctx->timing) CU(cudaEventRecord(ctx->ev[1], ctx->stream));
     if (sharded) {   // every rank's accumulators, then their sum mod p
         ncclResult_t r = g_nccl.AllGather(ctx->d_sv, ctx->d_gather, (size_t)Z * D, NCCL_UINT32, ctx->comm, ctx->stream);
         if (r) return fail(ctx, SC_ECOMM, "ncclAllGather: %s", g_nccl.GetErrorString(r));
-        CU(launch_sum_ranks(ctx->d_gather, ctx->world, Z * D, ctx->d_sv, ctx->h_sv_dev, SV_FLAG, a.seq, ctx->stream));
+        CU(launch_sum_ranks(ctx->d_gather, ctx->world, Z * D, ctx->d_sv, ctx->h_sv_dev, flag_word, a.seq, ctx->stream));
         ctx->launches++;
     }
-    if (!wait_word(ctx, ctx->h_sv + SV_FLAG, a.seq)) {
+    if (!wait_word(ctx, ctx->h_sv + flag_word, a.seq)) {
         const bool aborted = sharded && !ctx->comm;
         CU(cudaStreamSynchronize(ctx->stream));
         return fail(ctx, aborted ? SC_ECOMM : SC_ECUDA, aborted ? "the exchange between the GPUs did not finish; the communicator was aborted" : "the small-value pass did not finish");
@@ -1181,45 +1253,20 @@ static int sv_round0(sc_ctx *ctx, uint32_t *sums) {
         ctx->stats.push_back(st);
     }
     memcpy(ctx->sv_A, ctx->h_sv, (size_t)Z * D * 4);
-    auto A = [&](int z) { return ex_load(D, ctx->sv_A + (size_t)z * D); };
-    EX w0 = ex_base(1), w1 = ex_base(1);
-    if (ctx->have_eq) { const EX r1 = ex_load(D, ctx->eq1); w1 = r1; w0 = ex_sub(ex_base(1), r1); }
-    for (int xi = 0; xi < ctx->points; xi++) {
-        const int X = xi ? xi + 1 : 0;
-        const EX g = ex_add(ex_mul(D, A(X), w0), ex_mul(D, A(X + G), w1));
-        memcpy(sums + (size_t)xi * D, g.v, 4 * (size_t)D);
-    }
+    sv_sums(ctx, 0, sums);
     ctx->have_r = false;
     ctx->j = 1;
     return SC_OK;
 }
 
-// Round 1: g_1(X) = sum_v L_v(rho_0) A[v, X], L_v the Lagrange basis on the nodes 0 .. d (LAGRANGE-TENSOR, :463-474).
-static int sv_round1(sc_ctx *ctx, uint32_t *sums) {
-    const int D = ctx->D, G = ctx->points + 1, d = ctx->points;
-    const EX rho = ex_load(D, ctx->r);
-    memcpy(ctx->sv_rho0, ctx->r, 4 * (size_t)D);
-    auto A = [&](int z) { return ex_load(D, ctx->sv_A + (size_t)z * D); };
-    EX L[8];
-    for (int v = 0; v <= d; v++) {
-        EX num = ex_base(1);
-        u32 den = 1;
-        for (int j = 0; j <= d; j++) {
-            if (j == v) continue;
-            num = ex_mul(D, num, ex_sub(rho, ex_base((u32)j)));
-            den = (u32)(((u64)den * (u32)((v - j + (long long)P) % P)) % P);
-        }
-        L[v] = ex_scale(num, fp_inv(den));
-    }
-    for (int xi = 0; xi < ctx->points; xi++) {
-        const int X = xi ? xi + 1 : 0;
-        EX g = ex_base(0);
-        for (int v = 0; v <= d; v++) g = ex_add(g, ex_mul(D, A(v + G * X), L[v]));
-        memcpy(sums + (size_t)xi * D, g.v, 4 * (size_t)D);
-    }
+// Rounds 1 .. L0 - 1: the challenge of the round before joins the others, the sums come from the accumulators.
+static int sv_round_next(sc_ctx *ctx, uint32_t *sums) {
+    const int j = ctx->j;
+    memcpy(ctx->sv_rho[j - 1], ctx->r, 4 * (size_t)ctx->D);
+    sv_sums(ctx, j, sums);
     if (ctx->timing) { sc_round_stat st; st.kernel_ms = 0; st.bytes = 0; st.pairs = 0; ctx->stats.push_back(st); }
     ctx->have_r = false;
-    ctx->j = 2;
+    ctx->j = j + 1;
     return SC_OK;
 }
 
@@ -1348,9 +1395,10 @@ struct RoundLaunch {
 // host transcript's hash state), does the transcript's part itself and posts to its slot of the chain's buffer.
 static int enqueue_round(sc_ctx *ctx, int j, bool fold, bool chain, bool chain_first, const u32 *state0, RoundLaunch *out) {
     const int D = ctx->D, W = ctx->points * D;
-    const bool bind2 = ctx->sv_ok && j == 2;   // round 2 reads the base tables and binds both challenges on the way in
+    const bool bind2 = ctx->sv_ok && j == ctx->sv_l0;   // the round after the small-value rounds reads the base tables and binds all their challenges on the way in
+    const int bind_bits = bind2 ? ctx->sv_l0 : 1;
     const bool local = ctx->world > 1 && j < ctx->gather_round;
-    const int shrink = bind2 ? 4 : 2;   // entries in per entry out of the fold
+    const int shrink = 1 << bind_bits;   // entries in per entry out of the fold
     const RoundPlan &pl = ctx->plan[j];
     int rc;
 
@@ -1378,11 +1426,19 @@ static int enqueue_round(sc_ctx *ctx, int j, bool fold, bool chain, bool chain_f
         if (chain && !chain_first) a.r_dev = ctx->d_chal + (size_t)(j - 1) * 16;
         else challenge_words(ctx, a.r);
     }
-    if (bind2) {   // eq(rho0 rho1, b): bit 0 of b pairs with rho0 (EQ-TABLE, src/field.lisp:354-363)
-        const EX r0 = ex_load(D, ctx->sv_rho0), r1 = ex_load(D, ctx->r);
-        const EX one = ex_base(1), n0 = ex_sub(one, r0), n1 = ex_sub(one, r1);
-        const EX w[4] = {ex_mul(D, n0, n1), ex_mul(D, r0, n1), ex_mul(D, n0, r1), ex_mul(D, r0, r1)};
-        for (int b = 0; b < 4; b++) for (int c = 0; c < D; c++) a.bind[b][c] = to_mont(w[b].v[c]);
+    if (bind2) {   // eq(rho_0 .. rho_(L0-1), b): bit t of b pairs with rho_t (EQ-TABLE, src/field.lisp:354-363); the last challenge is the pending one
+        std::vector<EX> w{ex_base(1)};
+        for (int t = 0; t < bind_bits; t++) {
+            const EX rt = ex_load(D, t + 1 < bind_bits ? ctx->sv_rho[t] : ctx->r);
+            const size_t count = w.size();
+            w.resize(2 * count);
+            for (size_t b = 0; b < count; b++) { w[count + b] = ex_mul(D, w[b], rt); w[b] = ex_sub(w[b], w[count + b]); }
+        }
+        for (size_t b = 0; b < w.size(); b++)
+            for (int c = 0; c < D; c++) {
+                if (bind_bits == 2) a.bind[b][c] = to_mont(w[b].v[c]);
+                else a.bind3[b][c] = to_mont(w[b].v[c]);
+            }
     }
     a.logL = pl.logL;
     a.use_low = pl.use_low; a.use_high = pl.use_high;
@@ -1451,7 +1507,7 @@ static int enqueue_round(sc_ctx *ctx, int j, bool fold, bool chain, bool chain_f
         memcpy(a.gcoef, ctx->gcoef, sizeof a.gcoef);
         CU(launch_round_base(D, ctx->shape, ctx->points, ctx->nt_used, a.ngroups, a, grid, smem, ctx->stream));
     } else {
-        CU(launch_round(D, ctx->shape, ctx->points, ctx->nt_used, bind2 ? 2 : (fold ? 1 : 0), a, grid, smem, ctx->stream));
+        CU(launch_round(D, ctx->shape, ctx->points, ctx->nt_used, bind2 ? bind_bits : (fold ? 1 : 0), a, grid, smem, ctx->stream));
     }
     ctx->launches++;
     if (ctx->timing) CU(cudaEventRecord(out->e1, ctx->stream));
@@ -1575,7 +1631,7 @@ extern "C" int sc_round(sc_ctx *ctx, uint32_t *sums) {
     if (ctx->chain_active) return chain_round(ctx, sums);
     if (ctx->tail_active) return tail_round(ctx, sums);
     if (ctx->sv_ok && j == 0) return sv_round0(ctx, sums);
-    if (ctx->sv_ok && j == 1) return sv_round1(ctx, sums);
+    if (ctx->sv_ok && j < ctx->sv_l0) return sv_round_next(ctx, sums);
     if (!round_supported(D, ctx->points, ctx->nt_used)) return fail(ctx, SC_EUNSUPPORTED, "no kernel for D=%d points=%d tables=%d", D, ctx->points, ctx->nt_used);
     int rc;
     if (chain_wanted(ctx)) {

@@ -138,6 +138,7 @@ struct RoundArgs {
     const u32 *dead;
     int chained;          // 1: the launch is part of a chain (out_dev has room for the launch number)
     u32 bind[4][8];       // FOLD = 2: eq(rho0 rho1, b), b < 4, Montgomery form: entry y of the bound table is sum_b bind[b] T[4y + b]
+    u32 bind3[8][8];      // FOLD = 3: eq(rho0 rho1 rho2, b), b < 8: entry y of the bound table is sum_b bind3[b] T[8y + b]
     int ngroups;
     u32 gcoef[2][8];      // Montgomery form
 };
@@ -223,6 +224,12 @@ constexpr int SV_MAX_WORDS = 128;  // G^2 D words: G <= 4, D <= 8
 constexpr int SV_FLAG = SV_MAX_WORDS;
 cudaError_t launch_small_values(int D, int shape, int G, int nt, const SvArgs &args, int grid, cudaStream_t stream);
 bool small_values_supported(int D, int G, int nt);
+// The same for the first three rounds (L0 = 3, degree at most two): blocks of eight entries, G^3 D words out, then the
+// word SV3_FLAG; nblocks counts blocks of eight, the weights are those of round 2.  One sum per grid point only.
+constexpr int SV3_MAX_WORDS = 256;  // G^3 D words: G <= 3, D <= 8
+constexpr int SV3_FLAG = SV3_MAX_WORDS;
+cudaError_t launch_small_values3(int D, int shape, int G, int nt, const SvArgs &args, int grid, cudaStream_t stream);
+bool small_values3_supported(int D, int G, int nt);
 
 // The last rounds in one launch.  Once the tables are small a round is all latency (launch,
 // completion, the trip to the host and back), so a single block runs every remaining round and

@@ -289,6 +289,26 @@ __global__ void __launch_bounds__(ROUND_THREADS, NT > 4 ? 1 : (D == 8 ? SC_MINBL
         }
         return o;
     };
+    // a block of eight base entries bound to three challenges at once: the eight products do not fit one 64-bit sum, two sums of four do
+    auto bound3 = [&](const u32 (&e8)[8]) {
+        Ext<D> o;
+#pragma unroll
+        for (int c = 0; c < D; c++) {
+            u64 lo4 = 0, hi4 = 0;
+#pragma unroll
+            for (int b = 0; b < 4; b++) { lo4 += (u64)a.bind3[b][c] * e8[b]; hi4 += (u64)a.bind3[4 + b][c] * e8[4 + b]; }
+            o.v[c] = fadd(redc4(lo4), redc4(hi4));
+        }
+        return o;
+    };
+    // the two blocks of eight base entries of pair i of table t, bound: entries 16 i .. 16 i + 15
+    auto bound3_pair = [&](const u32 *src, u64 i, Ext<D> &lo, Ext<D> &hi) {
+        const uint4 *p = reinterpret_cast<const uint4 *>(src) + 4 * i;
+        const uint4 w0 = __ldcs(p), w1 = __ldcs(p + 1), w2 = __ldcs(p + 2), w3 = __ldcs(p + 3);
+        const u32 b0[8] = {w0.x, w0.y, w0.z, w0.w, w1.x, w1.y, w1.z, w1.w}, b1[8] = {w2.x, w2.y, w2.z, w2.w, w3.x, w3.y, w3.z, w3.w};
+        lo = bound3(b0);
+        hi = bound3(b1);
+    };
     unsigned base_mask = 0;
 #pragma unroll
     for (int t = 0; t < NT; t++) base_mask |= (a.src_base[t] ? 1u : 0u) << t;
@@ -333,7 +353,9 @@ __global__ void __launch_bounds__(ROUND_THREADS, NT > 4 ? 1 : (D == 8 ? SC_MINBL
             // table (the entries of four tables at once would not fit the register file)
             constexpr bool HOIST = D == 4 && NT <= 4;
             auto load_table = [&](int t, Ext<D> (&et)[NE]) {
-                if (FOLD == 2) {
+                if (FOLD == 3) {
+                    // read where it is bound, below
+                } else if (FOLD == 2) {
                     const uint4 w0 = __ldcs(reinterpret_cast<const uint4 *>(a.src[t]) + 2 * i), w1 = __ldcs(reinterpret_cast<const uint4 *>(a.src[t]) + 2 * i + 1);
                     et[0].v[0] = w0.x; et[0].v[1] = w0.y; et[0].v[2] = w0.z; et[0].v[3] = w0.w;
                     et[1].v[0] = w1.x; et[1].v[1] = w1.y; et[1].v[2] = w1.z; et[1].v[3] = w1.w;
@@ -361,7 +383,15 @@ __global__ void __launch_bounds__(ROUND_THREADS, NT > 4 ? 1 : (D == 8 ? SC_MINBL
                 const bool tb = (base_mask >> t) & 1;
                 if (!HOIST) load_table(t, e[0]);
                 Ext<D> (&et)[NE] = e[HOIST ? t : 0];
-                if (FOLD == 2) {
+                if (FOLD == 3) {
+                    Ext<D> lo, hi;
+                    bound3_pair(a.src[t], i, lo, hi);
+                    store_ext<D>(a.dst[t] + (2 * i) * D, lo);
+                    store_ext<D>(a.dst[t] + (2 * i + 1) * D, hi);
+                    val[t] = lo;
+                    slope[t] = esub<D>(hi, lo);
+                    if (PTS == 2) slope[t] = eadd<D>(slope[t], hi);
+                } else if (FOLD == 2) {
                     const Ext<D> lo = bound(et[0]), hi = bound(et[1]);
                     store_ext<D>(a.dst[t] + (2 * i) * D, lo);
                     store_ext<D>(a.dst[t] + (2 * i + 1) * D, hi);
@@ -399,7 +429,14 @@ __global__ void __launch_bounds__(ROUND_THREADS, NT > 4 ? 1 : (D == 8 ? SC_MINBL
                 }
             }
             // tables beyond the statement's are only folded
-            if (FOLD == 2) {
+            if (FOLD == 3) {
+                for (int t = NT; t < a.ntables; t++) {
+                    Ext<D> lo, hi;
+                    bound3_pair(a.src[t], i, lo, hi);
+                    store_ext<D>(a.dst[t] + (2 * i) * D, lo);
+                    store_ext<D>(a.dst[t] + (2 * i + 1) * D, hi);
+                }
+            } else if (FOLD == 2) {
                 for (int t = NT; t < a.ntables; t++) {
                     const uint4 w0 = __ldcs(reinterpret_cast<const uint4 *>(a.src[t]) + 2 * i), w1 = __ldcs(reinterpret_cast<const uint4 *>(a.src[t]) + 2 * i + 1);
                     Ext<D> b0, b1;
@@ -549,6 +586,14 @@ static cudaError_t launch_round_dpns(int fold, const RoundArgs &args, int grid, 
         if constexpr (NT <= 3 && PTS <= 3 && SHAPE != SHAPE_GKR) {
             if (smem > 40 * 1024) cudaFuncSetAttribute(round_kernel<D, PTS, NT, 2, SHAPE>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
             round_kernel<D, PTS, NT, 2, SHAPE><<<grid, ROUND_THREADS, smem, stream>>>(args);
+        } else {
+            return cudaErrorInvalidValue;
+        }
+    } else if (fold == 3) {
+        // base tables bound to three challenges on the way in (after three small-value rounds: degree at most two)
+        if constexpr (NT <= 3 && PTS <= 2 && SHAPE != SHAPE_GKR) {
+            if (smem > 40 * 1024) cudaFuncSetAttribute(round_kernel<D, PTS, NT, 3, SHAPE>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+            round_kernel<D, PTS, NT, 3, SHAPE><<<grid, ROUND_THREADS, smem, stream>>>(args);
         } else {
             return cudaErrorInvalidValue;
         }

@@ -346,6 +346,40 @@ def test_small_value_rounds_match_folding(prover, d, statement, names, with_eq, 
     assert prover.launches - before == with_small_values + 1, "the small-value rounds did not run"
 
 
+@pytest.mark.parametrize("d", [4, 8])
+@pytest.mark.parametrize("statement,names,with_eq", [
+    ("(* t0 t1)", ["t0", "t1"], True),
+    ("(* t0 t1)", ["t0", "t1"], False),
+    ("(* 7 t1 t0)", ["t0", "u", "t1"], True),                         # a coefficient, a table outside the statement
+    ("t0", ["t0"], True),                                             # degree one: a grid of 2^3 points
+    ("(+ (* 5 t1 t0) t0)", ["t0", "t1"], True),                       # a listed statement
+    ("(+ (* t0 t0) (* 2 t1 t2) -3)", ["t0", "t1", "t2"], True),       # the term table, three tables
+    ("(+ (* t0 t0) (* 2 t1 t2) -3)", ["t0", "t1", "t2"], False),
+])
+def test_three_small_value_rounds_match_folding(prover, d, statement, names, with_eq, monkeypatch):
+    # degree at most two: the first three rounds come from one pass (L0 = 3, the reference's *SMALL-VALUE-ROUNDS*,
+    # src/sumcheck.lisp:339-342, 450-455), and round 3 binds the base tables to three challenges at once.  Same bytes as the
+    # oracle, as two small-value rounds, and as folding from round 0; one launch fewer each time.
+    n = 23
+    rng = np.random.default_rng(len(statement) + with_eq + d)
+    tables = [(nm, rng.integers(0, P, size=1 << n, dtype=np.uint32)) for nm in names]
+    eq = rand_ext(rng, d, n) if with_eq else None
+    monkeypatch.setenv("SABLE_B200_SMALL_VALUES", "3")   # three tables in the statement take two rounds unless asked (it is no faster there)
+    before = prover.launches
+    got, want, ta, tb = both(prover, d, n, statement, tables, eq=eq, threads=0)
+    assert_same(got, want, ta, tb)
+    three = prover.launches - before
+    counts = []
+    for mode in ("2", "0"):
+        monkeypatch.setenv("SABLE_B200_SMALL_VALUES", mode)
+        tc = sb.Transcript("par", d)
+        before = prover.launches
+        again = sb.prove(tc, n, statement, tables, eq=eq, prover=prover)
+        assert again == got and tc.proof() == ta.proof()
+        counts.append(prover.launches - before)
+    assert counts == [three + 1, three + 2], "three small-value rounds did not run"
+
+
 def test_download_gives_the_table_back_and_refuses_in_the_small_value_rounds(prover):
     d, n = 4, 22
     rng = np.random.default_rng(77)
