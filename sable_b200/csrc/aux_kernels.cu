@@ -229,7 +229,8 @@ __global__ void sum_ranks_kernel(const u32 *gathered, int world, int words, u32 
     }
 }
 cudaError_t launch_sum_ranks(const u32 *gathered, int world, int words, u32 *out_dev, u32 *out_host, int flag_word, u32 seq, cudaStream_t stream) {
-    sum_ranks_kernel<<<1, 64, 0, stream>>>(gathered, world, words, out_dev, out_host, flag_word, seq);
+    if (words > 256) return cudaErrorInvalidValue;   // one thread per word: a round's sums, or the small-value accumulators (at most SV3_MAX_WORDS)
+    sum_ranks_kernel<<<1, 256, 0, stream>>>(gathered, world, words, out_dev, out_host, flag_word, seq);
     return cudaGetLastError();
 }
 

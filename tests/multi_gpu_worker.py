@@ -25,6 +25,7 @@ CASES = [
     (4, 17, "(+ (* t0 t3) (* t1 t2) (* lam t2 t3))", [1, 1, 0, 0], ["lam"], True),   # sharded rounds before the gather
     (4, 23, "(* t0 t1 t2)", [1, 1, 1], [], True),   # large enough for the small-value rounds on every rank
     (4, 24, "(* t0 t1)", [1, 1], [], True),         # degree two: three small-value rounds on two ranks, two on four
+    (8, 23, "(* t0 t1 t2)", [1, 1, 1], [], True),   # 128 words of small-value accumulators per rank
 ]
 
 
