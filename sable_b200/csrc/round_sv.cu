@@ -4,9 +4,9 @@
 // Work split: a thread keeps one low index l of the split eq weights and walks the high indices h
 // of its block's share, reading block y = h L + l of every table (one 128-bit load per table;
 // neighbouring threads read neighbouring blocks).  Per block it adds w_high[h] F(z) into G^2 D
-// 64-bit sums, four blocks per reduction (four products below p^2 fit 64 bits, as in REDUCED-SUM,
-// src/field.lisp:213-218); the reduced sums wait in shared memory, and the low weight multiplies
-// once at the very end.  Blocks' rows are added by the last block to finish (no waiting).
+// 64-bit sums that are reduced once, at the end (the reference reduces once per four products, REDUCED-SUM,
+// src/field.lisp:213-218; here a sum's high word loses one p before every second block, which keeps it within
+// 64 bits: presub, field.cuh); the low weight multiplies once at the very end.  Blocks' rows are added by the last block to finish (no waiting).
 // The grid of G^2 points is cut along its second variable (blockIdx.y) so that a thread's sums fit its
 // registers: two rows per block at D = 4 (rows z1 < 2 are the entries' own rows), one row at D = 8 or with two groups.
 // The statement at a grid point is a product of the tables (SHAPE_PRODUCT), a listed statement resolved at
@@ -107,20 +107,9 @@ __global__ void __launch_bounds__(ROUND_THREADS, G > 2 ? 2 : 1) sv_kernel(const 
     for (int z = 0; z < Z; z++)
 #pragma unroll
         for (int c = 0; c < D; c++) acc[z][c] = 0;
-    for (int k = 0; k < W; k++) tot[k * ROUND_THREADS + tid] = 0;
-    int pending = 0;
-
-    auto reduce = [&]() {
-#pragma unroll
-        for (int z = 0; z < Z; z++)
-#pragma unroll
-            for (int c = 0; c < D; c++) {
-                u32 *slot = tot + (z * D + c) * ROUND_THREADS + tid;
-                *slot = fadd(*slot, redc4(acc[z][c]));
-                acc[z][c] = 0;
-            }
-        pending = 0;
-    };
+    // The 64-bit sums run on without a reduction: before every second block each sum's high word loses one p when it can
+    // (presub, field.cuh), which keeps a sum below p 2^32 there and below 2 p 2^32 after two more products: what redc4 takes.
+    bool second = false;
 
     // the next block's entries are asked for before this block's arithmetic starts
     uint4 next[NT];
@@ -184,11 +173,14 @@ __global__ void __launch_bounds__(ROUND_THREADS, G > 2 ? 2 : 1) sv_kernel(const 
             for (int t = 0; t < NT; t++) val[t] = g[t][z];
             const u32 f = statement(val);
 #pragma unroll
-            for (int c = 0; c < D; c++) acc[z][c] += (u64)hw[c] * f;
+            for (int c = 0; c < D; c++) acc[z][c] = (second ? presub(acc[z][c]) : acc[z][c]) + (u64)hw[c] * f;
         }
-        if (++pending == 4) reduce();
+        second = !second;
     }
-    if (pending) reduce();
+#pragma unroll
+    for (int z = 0; z < Z; z++)
+#pragma unroll
+        for (int c = 0; c < D; c++) tot[(z * D + c) * ROUND_THREADS + tid] = redc4(acc[z][c]);
 
     // the low weight, once per thread
     if (a.use_low) {
@@ -340,22 +332,7 @@ __global__ void __launch_bounds__(ROUND_THREADS, G > 2 ? 2 : 1) sv_groups_kernel
         for (int z = 0; z < Z; z++)
 #pragma unroll
             for (int c = 0; c < D; c++) acc[g][z][c] = 0;
-    for (int k = 0; k < W; k++) tot[k * ROUND_THREADS + tid] = 0;
-    int pending = 0;
-
-    auto reduce = [&]() {
-#pragma unroll
-        for (int g = 0; g < NG; g++)
-#pragma unroll
-            for (int z = 0; z < Z; z++)
-#pragma unroll
-                for (int c = 0; c < D; c++) {
-                    u32 *slot = tot + ((g * Z + z) * D + c) * ROUND_THREADS + tid;
-                    *slot = fadd(*slot, redc4(acc[g][z][c]));
-                    acc[g][z][c] = 0;
-                }
-        pending = 0;
-    };
+    bool second = false;   // the sums run on without a reduction, as in sv_kernel
 
     // the next block's entries are asked for before this block's arithmetic starts
     uint4 next[NT];
@@ -422,11 +399,16 @@ __global__ void __launch_bounds__(ROUND_THREADS, G > 2 ? 2 : 1) sv_groups_kernel
 #pragma unroll
             for (int g = 0; g < NG; g++)
 #pragma unroll
-                for (int c = 0; c < D; c++) acc[g][z][c] += (u64)hw[c] * f[g];
+                for (int c = 0; c < D; c++) acc[g][z][c] = (second ? presub(acc[g][z][c]) : acc[g][z][c]) + (u64)hw[c] * f[g];
         }
-        if (++pending == 4) reduce();
+        second = !second;
     }
-    if (pending) reduce();
+#pragma unroll
+    for (int g = 0; g < NG; g++)
+#pragma unroll
+        for (int z = 0; z < Z; z++)
+#pragma unroll
+            for (int c = 0; c < D; c++) tot[((g * Z + z) * D + c) * ROUND_THREADS + tid] = redc4(acc[g][z][c]);
 
     // the low weight, once per thread
     if (a.use_low) {

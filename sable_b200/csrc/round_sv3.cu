@@ -8,7 +8,7 @@
 // {0..G-1}^3 come by additions: variable 2 first (the plane z2 of this thread block: blockIdx.y), then variable 1,
 // then variable 0.  A thread block keeps the accumulators of one plane at D = 4 (G^2 points) and of one row of a plane
 // at D = 8 (G points), so that they fit the registers.  Per block of entries it adds w_high[h] F(z) into 64-bit sums,
-// four blocks per reduction; the low weight multiplies once at the very end; the last thread block to finish adds the
+// reduced once at the end; the low weight multiplies once at the very end; the last thread block to finish adds the
 // rows of partial sums.  One sum per grid point: every coefficient is a base element (a product's rides in the final factor).
 #include "round_kernel.cuh"
 
@@ -101,19 +101,9 @@ __global__ void __launch_bounds__(ROUND_THREADS, 2) sv3_kernel(const __grid_cons
     for (int z = 0; z < Z; z++)
 #pragma unroll
         for (int c = 0; c < D; c++) acc[z][c] = 0;
-    for (int k = 0; k < W; k++) tot[k * ROUND_THREADS + tid] = 0;
-    int pending = 0;
-    auto reduce = [&]() {
-#pragma unroll
-        for (int z = 0; z < Z; z++)
-#pragma unroll
-            for (int c = 0; c < D; c++) {
-                u32 *slot = tot + (z * D + c) * ROUND_THREADS + tid;
-                *slot = fadd(*slot, redc4(acc[z][c]));
-                acc[z][c] = 0;
-            }
-        pending = 0;
-    };
+    // The 64-bit sums run on without a reduction: before every second block each sum's high word loses one p when it can
+    // (presub, field.cuh), which keeps a sum below p 2^32 there and below 2 p 2^32 after two more products: what redc4 takes.
+    bool second = false;
     // v + k s for k = 0 .. G-1 at position k (k = 0: v, k = 1: w = v + s given, k = 2: w + s)
     auto at = [](u32 v, u32 w, int k) -> u32 {
         if (k == 0) return v;
@@ -156,11 +146,14 @@ __global__ void __launch_bounds__(ROUND_THREADS, 2) sv3_kernel(const __grid_cons
             for (int t = 0; t < NT; t++) val[t] = g[t][z];
             const u32 f = statement(val);
 #pragma unroll
-            for (int c = 0; c < D; c++) acc[z][c] += (u64)hw[c] * f;
+            for (int c = 0; c < D; c++) acc[z][c] = (second ? presub(acc[z][c]) : acc[z][c]) + (u64)hw[c] * f;
         }
-        if (++pending == 4) reduce();
+        second = !second;
     }
-    if (pending) reduce();
+#pragma unroll
+    for (int z = 0; z < Z; z++)
+#pragma unroll
+        for (int c = 0; c < D; c++) tot[(z * D + c) * ROUND_THREADS + tid] = redc4(acc[z][c]);
 
     if (a.use_low) {   // the low weight, once per thread
         const u32 *w = a.low + (size_t)l * 2 * D;
