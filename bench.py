@@ -407,7 +407,7 @@ def main():
             one_proof(resident)
         oms, _, olaunches, otr, oout = timed(resident, args.steps)
         prover.set_device_transcript(False)
-        other = {"transcript": "device (the last block of each round kernel hashes and draws the challenge; all rounds enqueued at once)",
+        other = {"transcript": "device (a one-block kernel behind each round kernel hashes the sums and draws the challenge; all rounds enqueued at once)",
                  "value": (1 << n) / (oms / args.steps * 1e-3) / 1e6, "unit": "Mentries/s", "ms_per_step": oms / args.steps,
                  "gpu_launches": olaunches, "same_proof": otr.proof() == proof_bytes and oout == out}
 
