@@ -265,7 +265,7 @@ def main():
     ap.add_argument("--cpu-n", type=int, default=24, help="n of the CPU sample")
     ap.add_argument("--verify", action="store_true", help="one proof at the config's own n on the device and on the CPU port (all host threads): the proof bytes must be equal")
     ap.add_argument("--transcript", default="host", choices=("host", "device"),
-                    help="device: the round kernels carry the BLAKE3 transcript on themselves and every round is enqueued at once (an option of the library; the default is the reference's host transcript)")
+                    help="device: a one-block kernel behind each round kernel carries the BLAKE3 transcript on and every round is enqueued at once (an option of the library; the default is the reference's host transcript)")
     ap.add_argument("--no-e2e", action="store_true")
     ap.add_argument("--no-cpu", action="store_true")
     ap.add_argument("--no-device-transcript", action="store_true", help="skip the second figure with the transcript on the device")

@@ -230,14 +230,14 @@ int sc_transcript_device_round(const sc_transcript *tr, const uint32_t *values, 
    the host's part is SEND of the sums and CHALLENGE (src/transcript.lisp:116-176): a launch, a wait and a hash
    per round, which is all a small round costs.  With sc_set_device_transcript(CTX, 1) -- or
    SABLE_B200_DEVICE_TRANSCRIPT=1 in the environment when the context is made -- and the proof's transcript
-   attached, the first sc_round of a proof enqueues EVERY round at once: the last block of each round kernel
-   sends its sums and draws the challenge itself (sequential BLAKE3 on the device, from a copy of the
+   attached, the first sc_round of a proof enqueues EVERY round at once: behind each round kernel a one-block kernel
+   sends the round's sums and draws the challenge (sequential BLAKE3 on the device, from a copy of the
    transcript's hash state), and the next launch folds by the challenge it finds in device memory.  The caller's
    loop stays as it is: sc_round returns each round's sums as they are posted, the caller sends them and draws
    the challenge on its own transcript, and sc_challenge checks that it is the device's (SC_ESTATE if not: the
    transcript was used for something else in between).  The proof bytes are the same.  With several GPUs every
-   rank hashes the same summed words, so nothing more crosses NVLink.  The small-value first rounds of a product
-   of base tables stay with the host; the chain starts after them.
+   rank hashes the same summed words, so nothing more crosses NVLink.  The small-value first rounds of a statement
+   over base tables stay with the host; the chain starts after them.
    sc_attach_transcript: TR (or NULL) is the host transcript of the proofs that follow on CTX; sc_prove attaches
    its own for the length of the call.  sc_attach_transcript_state: the same for a transcript that is not the
    library's own, such as the Lisp one: its B3S state -- chaining value, pending block as little-endian words, bytes

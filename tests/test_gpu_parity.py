@@ -419,7 +419,7 @@ def chained():
     (4, 18, "(+ (* t0 t1) (* t1 t2) (* t2 t3) (* t3 t4) (* 3 t4 t0))", [1, 0, 0, 1, 0]),   # five tables: no resident kernel, the last fold alone
 ])
 def test_device_transcript_gives_the_same_proof(chained, d, n, statement, kinds):
-    # the last block of every round kernel hashes the round's sums (BLAKE3 on the device) and draws the challenge the
+    # behind every round kernel a one-block kernel hashes the round's sums (BLAKE3 on the device) and draws the challenge the
     # next launch folds by; the host replays the transcript afterwards and checks.  Same bytes as the oracle.
     rng = np.random.default_rng(n)
     tables = [("t%d" % t, rng.integers(0, P, size=1 << n, dtype=np.uint32) if k else rand_ext(rng, d, 1 << n)) for t, k in enumerate(kinds)]
