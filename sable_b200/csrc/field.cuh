@@ -142,6 +142,25 @@ template <int D> SCF_HD Ext<D> emul(const Ext<D> &a, const ExtM<D> &b) {
     }
     return o;
 }
+// a b without the reductions: per coordinate the 64-bit sum of products (below 2 p 2^32), which redc4 turns into the
+// coordinate; such sums can be added up first (presub on the way) and reduced once
+template <int D> struct ExtRaw { u64 v[D]; };
+template <int D> SCF_HD ExtRaw<D> emul_raw(const Ext<D> &a, const ExtM<D> &b) {
+    ExtRaw<D> o;
+#pragma unroll
+    for (int e = 0; e < D; e++) {
+        u64 acc = 0;
+#pragma unroll
+        for (int i = 0; i < D; i++) {
+            if (i >= 4 && (i & 1) == 0) acc = presub(acc);
+            const int j = (e - i + D) % D;
+            const u32 bj = (i > e) ? b.t[brev<D>(j)] : b.v[brev<D>(j)];
+            acc += (u64)a.v[brev<D>(i)] * bj;
+        }
+        o.v[brev<D>(e)] = acc;
+    }
+    return o;
+}
 // a1 b1 + a2 b2 with one reduction per coordinate
 template <int D> SCF_HD Ext<D> emul2(const Ext<D> &a1, const ExtM<D> &b1, const Ext<D> &a2, const ExtM<D> &b2) {
     Ext<D> o;

@@ -324,8 +324,22 @@ __global__ void __launch_bounds__(ROUND_THREADS, NT > 4 ? 1 : (D == 8 ? SC_MINBL
 #pragma unroll
     for (int x = 0; x < PTS; x++) { total[x] = ezero<D>(); inner[x] = ezero<D>(); }
     u64 cur_h = ~0ull;
+    // Round 0 with low weights (LAZY): the products with the low weight are summed over a run of pairs before they are
+    // reduced (64-bit sums, one p off the high word of both sides before each addition keeps them below 2 p 2^32)
+    constexpr bool LAZY = FOLD == 0 && D == 4 && NT <= 4 && PTS <= 2;   // where the wider sums fit the registers
+    u64 inner64[LAZY ? PTS : 1][D];
+#pragma unroll
+    for (int x = 0; x < (LAZY ? PTS : 1); x++)
+#pragma unroll
+        for (int c = 0; c < D; c++) inner64[x][c] = 0;
 
     auto flush = [&]() {   // total += high[h] * inner  (src/sumcheck.lisp:256-257)
+        if (LAZY && a.use_low) {
+#pragma unroll
+            for (int x = 0; x < PTS; x++)
+#pragma unroll
+                for (int c = 0; c < D; c++) { inner[x].v[c] = redc4(inner64[LAZY ? x : 0][c]); inner64[LAZY ? x : 0][c] = 0; }
+        }
         if (a.use_high) {
             Ext<D> hw = *reinterpret_cast<const Ext<D> *>(a.high + cur_h * D);
             ExtM<D> hm = eprep<D>(hw);
@@ -493,6 +507,18 @@ __global__ void __launch_bounds__(ROUND_THREADS, NT > 4 ? 1 : (D == 8 ? SC_MINBL
                     f = eval_listed<D, S, FOLD == 0>(a.st, reinterpret_cast<const Ext<D>(&)[S::NT]>(val), FOLD ? 0u : base_mask, &fbase);
                 }
                 else f = eval_statement<D, NT, FOLD == 0>(a.st, val, FOLD ? 0u : base_mask, &fbase);
+                if (LAZY && a.use_low) {
+                    if (fbase) {   // a base value times the weight: D base products (EXT-SCALE, src/sumcheck.lisp:246), unreduced
+                        const u32 fb = f.v[0];
+#pragma unroll
+                        for (int c = 0; c < D; c++) inner64[LAZY ? x : 0][c] = presub(inner64[LAZY ? x : 0][c]) + (u64)lw.v[c] * fb;
+                    } else {
+                        const ExtRaw<D> raw = emul_raw<D>(f, lw);
+#pragma unroll
+                        for (int c = 0; c < D; c++) inner64[LAZY ? x : 0][c] = presub(inner64[LAZY ? x : 0][c]) + presub(raw.v[c]);
+                    }
+                    continue;
+                }
                 if (a.use_low) {
                     if (!FOLD && fbase) {   // a base value times the weight: D base products (EXT-SCALE, src/sumcheck.lisp:246)
                         const u32 fb = f.v[0];
