@@ -1027,8 +1027,8 @@ extern "C" int sc_begin(sc_ctx *ctx, int n, const uint32_t *eq, int K, const uin
         for (int t = 0; t < ctx->st.nterms; t++) ext_term = ext_term || (ctx->st.terms[t].ckind == CK_EXT && ctx->st.terms[t].nf > 0);
         if (ctx->shape == SHAPE_PRODUCT) ext_term = false;
         ctx->sv_l0 = 2;
-        // (measured at n = 25-26, D = 4: three rounds against two are 1.77 / 1.76 ms for a product of two tables, 1.86 / 2.03 ms
-        // for a listed statement over two, 1.94 / 1.84 ms for a term table over three: so three tables stay at two unless
+        // (measured at n = 25-26, D = 4: three rounds against two are 1.54 / 1.66 ms for a product of two tables, 1.79 / 1.91 ms
+        // for a listed statement over two, 1.77 / 1.77 ms for a term table over three: so three tables stay at two unless
         // SABLE_B200_SMALL_VALUES=3 asks)
         const bool want3 = env && env[0] == '3' ? true : ctx->nt_used <= 2;
         if (ok && want3 && !(env && env[0] == '2') && !ext_term && n >= 4 && ctx->gather_round > 3 && ctx->shape != SHAPE_LISTED + 1 &&
@@ -1224,7 +1224,7 @@ static int sv_round0(sc_ctx *ctx, uint32_t *sums) {
     }
     const u32 lchunks = (1u << a.logL) / ROUND_THREADS;
     const u64 NH = a.nblocks >> a.logL;
-    u64 nhg = std::max<u64>(1, (u64)ctx->sms / lchunks);
+    u64 nhg = std::max<u64>(1, (u64)small_values_grid_x(D, G, a.ngroups, L0, ctx->sms) / lchunks);   // one wave of thread blocks
     if (nhg > NH) nhg = NH;
     const int grid = (int)(lchunks * nhg);
     if (ctx->timing) {

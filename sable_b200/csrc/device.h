@@ -230,6 +230,7 @@ constexpr int SV3_MAX_WORDS = 256;  // G^3 D words: G <= 3, D <= 8
 constexpr int SV3_FLAG = SV3_MAX_WORDS;
 cudaError_t launch_small_values3(int D, int shape, int G, int nt, const SvArgs &args, int grid, cudaStream_t stream);
 bool small_values3_supported(int D, int G, int nt);
+int small_values_grid_x(int D, int G, int ngroups, int l0, int sms);   // thread blocks along x that fill the GPU once (the grid's y is the kernels' own)
 
 // The last rounds in one launch.  Once the tables are small a round is all latency (launch,
 // completion, the trip to the host and back), so a single block runs every remaining round and

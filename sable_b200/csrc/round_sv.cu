@@ -251,7 +251,7 @@ __global__ void __launch_bounds__(ROUND_THREADS, G > 2 ? 2 : 1) sv_kernel(const 
 template <int D, int NG> __host__ __device__ constexpr int sv_rows() { return D == 4 && NG == 1 ? 2 : 1; }
 
 template <int D, int G, int NT, int SHAPE, int NG>
-__global__ void __launch_bounds__(ROUND_THREADS, G > 2 ? 2 : 1) sv_groups_kernel(const __grid_constant__ SvArgs a) {
+__global__ void __launch_bounds__(ROUND_THREADS, G > 2 ? (D == 4 && G == 3 ? 3 : 2) : 1) sv_groups_kernel(const __grid_constant__ SvArgs a) {
     constexpr int ROWS1 = sv_rows<D, NG>();       // rows of the grid (values of z1) a block handles, at most
     constexpr int Z = G * ROWS1, W = NG * Z * D;  // this block's share of the accumulators
     constexpr int WONE = G * G * D;               // one group's accumulators
@@ -538,6 +538,15 @@ template <int D> static cudaError_t launch_sv_d(int shape, int G, int nt, int ng
         }
     }
     return cudaErrorInvalidValue;
+}
+// The thread blocks along x a pass is launched with.  The kernels cut the grid of points over blockIdx.y; one block along x per
+// SM gives them one or two full waves of thread blocks, except for three rounds at D = 4, where a plane of the grid per thread
+// block (G of them, two blocks per SM) fills the GPU once with 2 / G blocks along x per SM (measured: 444 blocks on 296 places
+// ran a wave and a half).
+int small_values_grid_x(int D, int G, int ngroups, int l0, int sms) {
+    (void)ngroups;
+    if (l0 == 3 && D == 4) { const int x = sms * 2 / G; return x > 0 ? x : 1; }
+    return sms;
 }
 // G = points + 1 grid values per variable: degree at most three, at most three tables in the statement
 bool small_values_supported(int D, int G, int nt) { return (D == 4 || D == 8) && nt >= 1 && nt <= 3 && G >= 2 && G <= 4; }
