@@ -972,13 +972,28 @@ extern "C" int sc_begin(sc_ctx *ctx, int n, const uint32_t *eq, int K, const uin
     std::vector<WeightDesc> &descs = ctx->stage_descs;
     descs.clear();
     u64 words = 0, total_entries = 0;
+    // A statement over base tables may take its first rounds from one pass (below): that pass walks the weights of round 1
+    // (or 2) with one thread per low weight, 256 to a thread block, and wants the thread blocks to divide the SMs evenly:
+    // 2^10 low weights are four thread blocks' worth (148 = 4 x 37), 2^11 would leave four SMs idle.  Any split gives the same sums.
+    bool pass_candidate = ctx->sv_statement && K == 1 && !ctx->force_generic;
+    for (int s = 0; s < ctx->ntables && pass_candidate; s++) pass_candidate = ctx->tab[s].stride == 1;
+    int pass_round = 1;   // the round whose weights the pass would walk: 2 where three rounds are likely (decided below)
+    {
+        const char *env = getenv("SABLE_B200_SMALL_VALUES");
+        bool ext_term = false;
+        for (int t = 0; t < ctx->st.nterms; t++) ext_term = ext_term || (ctx->st.terms[t].ckind == CK_EXT && ctx->st.terms[t].nf > 0);
+        if (ctx->shape == SHAPE_PRODUCT) ext_term = false;
+        const bool want3 = env && env[0] == '3' ? true : ctx->nt_used <= 2;
+        if (want3 && !(env && env[0] == '2') && !ext_term && ctx->points <= 2 && ctx->shape != SHAPE_LISTED + 1) pass_round = 2;
+    }
     for (int j = 0; j < n; j++) {
         RoundPlan &pl = ctx->plan[j];
         const bool local = j < gather_round;         // before the gather
         const int end = local ? nloc : n;            // eq variables of this stage end here
         const int v = end - 1 - j;
         const int blocks = K;                         // every block in every round: with several GPUs each rank holds its slice of each
-        const int a = split_bits(D, v);
+        int a = split_bits(D, v);
+        if (pass_candidate && j == pass_round && a > 10) a = 10;   // (the round after it, which binds the tables, is faster with 2^11)
         pl.logL = a;
         pl.use_low = eq && a > 0;
         const bool has_bw = block_weights != nullptr;
